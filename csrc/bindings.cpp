@@ -1,0 +1,178 @@
+// Python bindings: thin adapters from torch tensors to the C entry points. They run on the
+// current CUDA stream of the tensor's device, never allocate on the hot path except where a
+// result tensor is returned, and raise with the library's own error text.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "common/host.h"
+#include "elementwise/elementwise.h"
+#include "gemm/gemm.h"
+
+namespace {
+
+void check(int rc, const char* what) {
+  if (rc != 0) {
+    TORCH_CHECK(false, what, " failed (", rc, "): ", pico_last_error());
+  }
+}
+
+cudaStream_t stream_of(const at::Tensor& t) {
+  return at::cuda::getCurrentCUDAStream(t.device().index()).stream();
+}
+
+const void* cptr(const c10::optional<at::Tensor>& t) {
+  return t.has_value() && t->defined() ? t->data_ptr() : nullptr;
+}
+void* mptr(const c10::optional<at::Tensor>& t) {
+  return t.has_value() && t->defined() ? t->data_ptr() : nullptr;
+}
+
+// D = op(A) op(B) with explicit geometry so that views (row slices, transposes expressed
+// through the *_mn_major flags, column slices through ld) need no copies.
+void gemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& D, int64_t M, int64_t N, int64_t K,
+          int64_t lda, int64_t ldb, int64_t ldd, bool a_mn_major, bool b_mn_major, int64_t out_mode,
+          int64_t max_ctas) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && D.is_cuda(), "gemm: CUDA tensors required");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
+              "gemm: bf16 operands required");
+  TORCH_CHECK((out_mode == 0) == (D.scalar_type() == at::kBFloat16), "gemm: output dtype/mode mismatch");
+  c10::cuda::CUDAGuard guard(A.device());
+  check(pico_gemm_bf16(A.data_ptr(), B.data_ptr(), D.data_ptr(), (int)M, (int)N, (int)K, (int)lda,
+                       (int)ldb, (int)ldd, a_mn_major, b_mn_major, (int)out_mode, (int)max_ctas,
+                       stream_of(A)),
+        "gemm");
+}
+
+void rmsnorm_fwd(const at::Tensor& x, const c10::optional<at::Tensor>& residual, const at::Tensor& w,
+                 at::Tensor& y, const c10::optional<at::Tensor>& h_out,
+                 const c10::optional<at::Tensor>& rstd, int64_t rows, int64_t H, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check(pico_rmsnorm_fwd(x.data_ptr(), cptr(residual), w.data_ptr(), y.data_ptr(), mptr(h_out),
+                         (float*)mptr(rstd), (int)rows, (int)H, (float)eps, stream_of(x)),
+        "rmsnorm_fwd");
+}
+
+int64_t rmsnorm_bwd_num_partials() { return pico_rmsnorm_bwd_num_partials(); }
+
+void rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& h, const at::Tensor& w, const at::Tensor& rstd,
+                 const c10::optional<at::Tensor>& dres, at::Tensor& dh, at::Tensor& dw_partial,
+                 const c10::optional<at::Tensor>& dw_f32, const c10::optional<at::Tensor>& dw_bf16,
+                 bool accumulate, int64_t rows, int64_t H) {
+  c10::cuda::CUDAGuard guard(dy.device());
+  TORCH_CHECK(dw_partial.numel() >= pico_rmsnorm_bwd_num_partials() * H, "rmsnorm_bwd: scratch too small");
+  check(pico_rmsnorm_bwd(dy.data_ptr(), h.data_ptr(), w.data_ptr(), (const float*)rstd.data_ptr(),
+                         cptr(dres), dh.data_ptr(), (float*)dw_partial.data_ptr(),
+                         (float*)mptr(dw_f32), mptr(dw_bf16), accumulate, (int)rows, (int)H,
+                         stream_of(dy)),
+        "rmsnorm_bwd");
+}
+
+void rope_inplace(at::Tensor& x, int64_t row_stride, int64_t rows, int64_t seq, int64_t pos_offset,
+                  int64_t nheads, int64_t d, const at::Tensor& cos, const at::Tensor& sin, int64_t sign) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat, "rope: fp32 tables");
+  TORCH_CHECK(pos_offset + seq <= cos.size(0), "rope: position table too short");
+  check(pico_rope_inplace(x.data_ptr(), row_stride, (int)rows, (int)seq, (int)pos_offset, (int)nheads,
+                          (int)d, (const float*)cos.data_ptr(), (const float*)sin.data_ptr(),
+                          (int)sign, stream_of(x)),
+        "rope");
+}
+
+void swiglu_fwd(const at::Tensor& gu, int64_t ld_gu, at::Tensor& y, int64_t rows, int64_t I) {
+  c10::cuda::CUDAGuard guard(gu.device());
+  check(pico_swiglu_fwd(gu.data_ptr(), ld_gu, y.data_ptr(), (int)rows, (int)I, stream_of(gu)), "swiglu_fwd");
+}
+void swiglu_bwd(const at::Tensor& dy, const at::Tensor& gu, int64_t ld_gu, at::Tensor& dgu,
+                int64_t ld_dgu, int64_t rows, int64_t I) {
+  c10::cuda::CUDAGuard guard(gu.device());
+  check(pico_swiglu_bwd(dy.data_ptr(), gu.data_ptr(), ld_gu, dgu.data_ptr(), ld_dgu, (int)rows, (int)I,
+                        stream_of(gu)),
+        "swiglu_bwd");
+}
+
+void ce_stats(const at::Tensor& logits, int64_t ldl, const at::Tensor& targets, at::Tensor& stats,
+              int64_t rows, int64_t V, int64_t vocab_start) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(targets.scalar_type() == at::kLong && stats.scalar_type() == at::kFloat, "ce: dtypes");
+  check(pico_ce_stats(logits.data_ptr(), ldl, (const int64_t*)targets.data_ptr(),
+                      (float*)stats.data_ptr(), (int)rows, (int)V, (int)vocab_start, stream_of(logits)),
+        "ce_stats");
+}
+void ce_loss_grad(const at::Tensor& logits, int64_t ldl, const at::Tensor& targets,
+                  const at::Tensor& stats, const c10::optional<at::Tensor>& loss,
+                  const c10::optional<at::Tensor>& dlogits, int64_t ldd, double grad_scale,
+                  int64_t rows, int64_t V, int64_t vocab_start) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  check(pico_ce_loss_grad(logits.data_ptr(), ldl, (const int64_t*)targets.data_ptr(),
+                          (const float*)stats.data_ptr(), (float*)mptr(loss), mptr(dlogits), ldd,
+                          (float)grad_scale, (int)rows, (int)V, (int)vocab_start, stream_of(logits)),
+        "ce_loss_grad");
+}
+
+void adamw(const c10::optional<at::Tensor>& p, const c10::optional<at::Tensor>& master, at::Tensor& g,
+           at::Tensor& m, at::Tensor& v, int64_t n, double lr, double beta1, double beta2, double eps,
+           double wd, double bc1, double bc2, double grad_scale, bool zero_grad) {
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat &&
+                  v.scalar_type() == at::kFloat, "adamw: fp32 grads and states");
+  check(pico_adamw(mptr(p), (float*)mptr(master), (float*)g.data_ptr(), (float*)m.data_ptr(),
+                   (float*)v.data_ptr(), n, (float)lr, (float)beta1, (float)beta2, (float)eps,
+                   (float)wd, (float)bc1, (float)bc2, (float)grad_scale, zero_grad, stream_of(g)),
+        "adamw");
+}
+
+void embedding_fwd(const at::Tensor& W, const at::Tensor& ids, at::Tensor& out, int64_t rows, int64_t H,
+                   int64_t Vlocal, int64_t vocab_start) {
+  c10::cuda::CUDAGuard guard(W.device());
+  TORCH_CHECK(ids.scalar_type() == at::kLong, "embedding: int64 ids");
+  check(pico_embedding_fwd(W.data_ptr(), (const int64_t*)ids.data_ptr(), out.data_ptr(), (int)rows,
+                           (int)H, (int)Vlocal, (int)vocab_start, stream_of(W)),
+        "embedding_fwd");
+}
+void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& dW, int64_t rows, int64_t H,
+                   int64_t Vlocal, int64_t vocab_start) {
+  c10::cuda::CUDAGuard guard(dout.device());
+  TORCH_CHECK(dW.scalar_type() == at::kFloat, "embedding_bwd: fp32 accumulator");
+  check(pico_embedding_bwd(dout.data_ptr(), (const int64_t*)ids.data_ptr(), (float*)dW.data_ptr(),
+                           (int)rows, (int)H, (int)Vlocal, (int)vocab_start, stream_of(dout)),
+        "embedding_bwd");
+}
+
+void accumulate_bf16_into_f32(const at::Tensor& src, at::Tensor& dst, int64_t n) {
+  c10::cuda::CUDAGuard guard(src.device());
+  check(pico_accumulate_bf16_into_f32(src.data_ptr(), (float*)dst.data_ptr(), n, stream_of(src)),
+        "accumulate");
+}
+
+void fill_u32(at::Tensor& dst, int64_t value, int64_t n_words) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  check(pico_fill_u32(dst.data_ptr(), (uint32_t)value, n_words, stream_of(dst)), "fill");
+}
+
+// Returns the 8 status words after synchronising (word 0 != 0 means a kernel gave up a wait).
+std::vector<int64_t> status_fetch() {
+  int out[8] = {0};
+  pico_status_fetch(out);
+  return std::vector<int64_t>(out, out + 8);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd_num_partials", &rmsnorm_bwd_num_partials);
+  m.def("rope_inplace", &rope_inplace);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("ce_stats", &ce_stats);
+  m.def("ce_loss_grad", &ce_loss_grad);
+  m.def("adamw", &adamw);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("accumulate_bf16_into_f32", &accumulate_bf16_into_f32);
+  m.def("fill_u32", &fill_u32);
+  m.def("status_fetch", &status_fetch);
+}

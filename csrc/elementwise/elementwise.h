@@ -1,0 +1,72 @@
+// C entry points of the memory-bound kernels (normalisation, rotary embedding, SwiGLU,
+// cross-entropy, AdamW, embedding, fp8 block quantisation). Device pointers throughout;
+// 0 on success, message in pico_last_error() otherwise. bf16 tensors are passed as void*.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- RMSNorm ---------------------------------------------------------------------------
+// h = x (+ residual); y = h * rsqrt(mean(h^2)+eps) * w.  h_out (optional) receives h when a
+// residual is given. rstd (optional) receives the per-row statistic for the backward.
+int pico_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out,
+                     float* rstd, int rows, int H, float eps, cudaStream_t stream);
+// Rows of fp32 scratch (each H wide) that pico_rmsnorm_bwd needs in dw_partial.
+int pico_rmsnorm_bwd_num_partials(void);
+// dh = d(norm)/dh (+ dres);  dw (fp32 and/or bf16, = or +=) = sum_rows dy*h*rstd.
+int pico_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd,
+                     const void* dres, void* dh, float* dw_partial, float* dw_f32, void* dw_bf16,
+                     int accumulate, int rows, int H, cudaStream_t stream);
+
+// ---- RoPE (half-split, in place) ---------------------------------------------------------
+// x: rows x (nheads*d) with `row_stride` elements between rows; position of row r is
+// pos_offset + (r % seq). cos/sin: fp32 [max_pos, d/2]. sign=+1 forward, -1 backward.
+int pico_rope_inplace(void* x, int64_t row_stride, int rows, int seq, int pos_offset, int nheads,
+                      int d, const float* cos, const float* sin, int sign, cudaStream_t stream);
+
+// ---- SwiGLU ------------------------------------------------------------------------------
+// gu: [rows, 2*I] (gate | up, row stride ld_gu); y[rows, I] = silu(gate) * up
+int pico_swiglu_fwd(const void* gu, int64_t ld_gu, void* y, int rows, int I, cudaStream_t stream);
+// dgu[rows, 2*I] from dy[rows, I] and the saved gu
+int pico_swiglu_bwd(const void* dy, const void* gu, int64_t ld_gu, void* dgu, int64_t ld_dgu,
+                    int rows, int I, cudaStream_t stream);
+
+// ---- cross entropy on a vocabulary shard ---------------------------------------------------
+// stats[row] = {max_j l[row,j], sum_j exp(l - max), l[row,target] or 0 if target is not in
+// [vocab_start, vocab_start+V)}. logits bf16 [rows, V] with row stride ldl.
+int pico_ce_stats(const void* logits, int64_t ldl, const int64_t* targets, float* stats, int rows,
+                  int V, int vocab_start, cudaStream_t stream);
+// Given the (already reduced over shards) stats: loss[row] = log(sum) + max - target_logit and,
+// when dlogits != NULL, dlogits = (softmax - onehot) * grad_scale (may alias logits).
+int pico_ce_loss_grad(const void* logits, int64_t ldl, const int64_t* targets, const float* stats,
+                      float* loss, void* dlogits, int64_t ldd, float grad_scale, int rows, int V,
+                      int vocab_start, cudaStream_t stream);
+
+// ---- AdamW over flat buffers ----------------------------------------------------------------
+// p (bf16) / master (fp32, optional) / g (fp32) / m, v (fp32), n elements. Decoupled weight
+// decay as torch.optim.AdamW. g is multiplied by grad_scale first and zeroed afterwards when
+// zero_grad != 0.
+int pico_adamw(void* p_bf16, float* master, float* g, float* m, float* v, int64_t n, float lr,
+               float beta1, float beta2, float eps, float weight_decay, float bias_corr1,
+               float bias_corr2, float grad_scale, int zero_grad, cudaStream_t stream);
+
+// ---- embedding -------------------------------------------------------------------------------
+// out[row] = W[ids[row]-vocab_start] or 0 when the id is outside this vocabulary shard.
+int pico_embedding_fwd(const void* W, const int64_t* ids, void* out, int rows, int H, int Vlocal,
+                       int vocab_start, cudaStream_t stream);
+// dW[ids[row]-vocab_start] += dout[row] (fp32 accumulation)
+int pico_embedding_bwd(const void* dout, const int64_t* ids, float* dW, int rows, int H, int Vlocal,
+                       int vocab_start, cudaStream_t stream);
+
+// ---- misc ---------------------------------------------------------------------------------
+// dst_f32 += src_bf16 (n elements); used to fold bf16 gradients into fp32 accumulators.
+int pico_accumulate_bf16_into_f32(const void* src, float* dst, int64_t n, cudaStream_t stream);
+// writes a buffer larger than L2 (cache flush between timed iterations)
+int pico_fill_u32(void* dst, uint32_t value, int64_t n_words, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,119 @@
+"""Bias-free linear layers on the tcgen05 GEMM.
+
+``linear(x, w)`` computes ``x @ w.T`` like ``F.linear``. On bf16 CUDA tensors forward, dgrad
+and wgrad all run on ``csrc/gemm/gemm_bf16_sm100.cu`` without transposed copies (the kernel
+reads K-major and MN-major operands). When the weight carries an fp32 ``main_grad`` buffer the
+wgrad GEMM accumulates straight into it (TMA reduce-add epilogue) — the bucket accumulation the
+reference does with a separate ``main_grad.add_(grad)`` per parameter
+(picotron/data_parallel/data_parallel.py:143) — and autograd sees no weight gradient.
+
+Reference: picotron/model.py:160-162,232,258,285 (F.linear call sites).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import count_launch, ext, use_kernels
+
+
+def linear_ref(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return F.linear(x, w)
+
+
+def _rows(x: torch.Tensor) -> int:
+    return x.numel() // x.shape[-1]
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, max_ctas: int = 0,
+            out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ b[N,K].T  (both K-contiguous; row strides may exceed K)."""
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+    mode = 0 if out.dtype == torch.bfloat16 else 1
+    ext().gemm(a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0), False, False, mode, max_ctas)
+    count_launch()
+    return out
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ b[K,N]  (b is N-contiguous)."""
+    M, K = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=torch.bfloat16)
+    mode = 0 if out.dtype == torch.bfloat16 else 1
+    ext().gemm(a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0), False, True, mode, max_ctas)
+    count_launch()
+    return out
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+            max_ctas: int = 0) -> torch.Tensor:
+    """out[M,N] (+)= a[K,M].T @ b[K,N]. ``accumulate`` needs an fp32 ``out``."""
+    K, M = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=torch.bfloat16)
+    if accumulate:
+        assert out.dtype == torch.float32
+        mode = 2
+    else:
+        mode = 0 if out.dtype == torch.bfloat16 else 1
+    ext().gemm(a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0), True, True, mode, max_ctas)
+    count_launch()
+    return out
+
+
+def _as_2d(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16 != 0:
+        x2 = x2.contiguous()
+    return x2
+
+
+def _gemm_ok(*dims: int) -> bool:
+    # TMA needs 16-byte aligned pitches: every contiguous extent a multiple of 8 bf16
+    return all(d % 8 == 0 for d in dims)
+
+
+def wgrad_into(weight: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):
+    """Weight gradient of y = x @ w.T. Accumulates into ``weight.main_grad`` (fp32) when the
+    parameter has one and returns None; otherwise returns the bf16 gradient."""
+    main_grad = getattr(weight, "main_grad", None)
+    if main_grad is not None:
+        gemm_tn(dy2, x2, out=main_grad, accumulate=True)
+        hook = getattr(weight, "grad_ready_hook", None)
+        if hook is not None:
+            hook()
+        return None
+    return gemm_tn(dy2, x2)
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = _as_2d(x)
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        y = gemm_nt(x2, w)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _as_2d(dy)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_nn(dy2, w).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dw = wgrad_into(w, dy2, x2)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    if use_kernels(x, w) and _gemm_ok(x.shape[-1], w.shape[0]):
+        return _LinearFn.apply(x, w)
+    return linear_ref(x, w)
