@@ -1,0 +1,358 @@
+"""Headline benchmark: training throughput (tokens/s, MFU) of the SmolLM-1.7B-shaped Llama
+(24 layers, hidden 2048, 32 heads, FFN 8192, vocab 49152; seq 2048, micro-batch 4, 8 gradient
+accumulation steps, AdamW lr 3e-4, bf16, random init N(0, 0.02), seeded uniform tokens) on N
+GPUs of one node.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
+    python bench.py --impl reference ...     # the unmodified reference package from baseline/_ref
+
+Layouts (all with sequence parallelism, vocabulary-parallel cross entropy and ZeRO-1 where the
+axis exists): 1 GPU = no parallelism, 2 = TP2, 4 = TP4, 8 = DP2 x TP4.
+
+Two measurements per run, both as max over ranks:
+* ``value``: K optimizer steps timed with CUDA events on the device, micro-batches already
+  resident on the GPU (kernel-only view)
+* ``e2e``: the same K steps driven through ``TrainEngine.train_step()`` with every
+  micro-batch copied from pinned host memory and the step's loss read back to the host
+
+The working set of a step (3.4 GB of parameters, several GB of activations) is far larger
+than the 126 MB L2, so no explicit flush runs between iterations. Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from types import SimpleNamespace
+
+import torch
+import torch.distributed as dist
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+MODEL = dict(name="HuggingFaceTB/SmolLM-1.7B", hidden_size=2048, intermediate_size=8192, num_hidden_layers=24,
+             num_attention_heads=32, num_key_value_heads=32, vocab_size=49152, max_position_embeddings=2048,
+             rms_norm_eps=1e-5, rope_theta=10000.0)
+SEQ, MBS, GRAD_ACC, LR = 2048, 4, 8, 3e-4
+LAYOUTS = {1: dict(tp=1, dp=1), 2: dict(tp=2, dp=1), 4: dict(tp=4, dp=1), 8: dict(tp=4, dp=2)}
+PUBLISHED_MFU_PERCENT = 50.0          # "nearly 50%" SmolLM-1.7B on 8 x H100 (reference README.md:7)
+H100_PEAK = 989.5e12                  # constant of the reference's MFU formula
+
+
+def num_params(m=MODEL) -> float:
+    h, i, L, v = m["hidden_size"], m["intermediate_size"], m["num_hidden_layers"], m["vocab_size"]
+    kv = m["num_key_value_heads"] * (h // m["num_attention_heads"])
+    per_layer = h * h * 2 + 2 * h * kv + 3 * h * i + 2 * h
+    return float(L * per_layer + 2 * v * h + h)
+
+
+def flops_per_token() -> float:
+    return 6.0 * num_params() + 12.0 * MODEL["num_hidden_layers"] * MODEL["hidden_size"] * SEQ
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this process's GPU with nvidia-smi while the
+    timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.proc, self.path = None, None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons, smax = [], set(), None
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 8:
+                    continue
+                try:
+                    clocks.append(float(parts[0]))
+                    smax = float(parts[1])
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if clocks:
+            clocks.sort()
+            out.update(sm_mhz=clocks[len(clocks) // 2], sm_max_mhz=smax, reasons=sorted(reasons),
+                       samples=len(clocks))
+        return out
+
+
+def setup_distributed(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == n_gpus, f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    torch.cuda.set_device(local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("LOCAL_RANK", "0")
+    if not dist.is_initialized():
+        dist.init_process_group(backend="nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", local_rank))
+    return rank, local_rank, world
+
+
+def timed(fn, steps: int, device) -> float:
+    """Milliseconds for ``steps`` calls of fn, CUDA events bracketed by barrier + synchronize,
+    max over ranks."""
+    dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([start.elapsed_time(end)], device=device, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def result_line(args, layout, world, ms_total, e2e_ms_total, h2d, d2h, clocks, launches, impl, extra=None):
+    tokens_per_step = MBS * SEQ * GRAD_ACC * layout["dp"]
+    ms_per_step = ms_total / args.steps
+    value = tokens_per_step / (ms_per_step / 1e3)
+    per_gpu = value / world
+    fpt = flops_per_token()
+    from picotron_b200.utils import measured_peak_flops
+    line = {
+        "metric": "training throughput, SmolLM-1.7B (tokens/s, whole job)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(per_gpu * fpt / H100_PEAK * 100.0 / PUBLISHED_MFU_PERCENT, 4),
+        "dtype": "bf16", "data": "synthetic seeded uniform tokens, random-init N(0,0.02) weights",
+        "impl": impl,
+        "mfu_percent_h100_constant": round(per_gpu * fpt / H100_PEAK * 100.0, 2),
+        "mfu_percent_b200_measured_peak": round(per_gpu * fpt / measured_peak_flops() * 100.0, 2),
+        "config": {"model": "SmolLM-1.7B-shaped Llama (24L h2048 32h ffn8192 v49152)",
+                   "global_batch": MBS * GRAD_ACC * layout["dp"], "seq_len": SEQ, "micro_batch": MBS,
+                   "grad_accum": GRAD_ACC, "optimizer": "AdamW lr 3e-4",
+                   "parallelism": f"dp{layout['dp']}xtp{layout['tp']}"
+                                  + ("+sp+vocab_ce" if layout["tp"] > 1 else "")
+                                  + ("+zero1" if layout["dp"] > 1 else ""),
+                   "l2": "per-step working set (GBs of parameters and activations) exceeds the 126 MB L2; no explicit flush",
+                   "vs_baseline_note": "per-GPU MFU by the reference formula (H100 constant) / published ~50% MFU on 8xH100"},
+        "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
+                   "reasons": clocks.get("reasons", [])},
+        "e2e": {"value": round(tokens_per_step / (e2e_ms_total / args.steps / 1e3), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+    }
+    if extra:
+        line.update(extra)
+    return line
+
+
+# ------------------------------------------------------------------------------------------ ours
+def run_ours(args):
+    rank, local_rank, world = setup_distributed(args.gpus)
+    device = torch.device("cuda", local_rank)
+    layout = LAYOUTS[world]
+    from picotron_b200 import ops
+    from picotron_b200.engine import TrainEngine
+    cfg = {
+        "distributed": dict(tp_size=layout["tp"], dp_size=layout["dp"], sequence_parallel=layout["tp"] > 1,
+                            vocab_parallel_ce=layout["tp"] > 1, zero_stage=1 if layout["dp"] > 1 else 0),
+        "model": dict(MODEL, init_std=0.02, dtype="bfloat16"),
+        "training": dict(seed=1234, learning_rate=LR, seq_length=SEQ, micro_batch_size=MBS,
+                         gradient_accumulation_steps=GRAD_ACC, num_samples=1 << 16),
+        "dataset": dict(name="synthetic"),
+    }
+    engine = TrainEngine(cfg, device=device)
+    g = torch.Generator().manual_seed(99 + engine.pgm.dp_rank)
+    resident = [(torch.randint(0, MODEL["vocab_size"], (MBS, SEQ), generator=g).to(device),
+                 torch.randint(0, MODEL["vocab_size"], (MBS, SEQ), generator=g).to(device))
+                for _ in range(GRAD_ACC)]
+
+    def device_step():
+        engine.train_step(device_batches=resident)
+
+    last = {}
+
+    def e2e_step():
+        last["loss"] = float(engine.train_step().item())
+
+    for _ in range(args.warmup):
+        device_step()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    l0 = ops.launches()
+    ms = timed(device_step, args.steps, device)
+    launches = ops.launches() - l0
+    clocks = sampler.stop() if sampler else {}
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps, device)
+    ops.check_status("bench")
+    h2d = GRAD_ACC * 2 * MBS * SEQ * 8      # input_ids + target_ids, int64, per rank
+    d2h = 4                                  # the fp32 step loss
+    if rank == 0:
+        print(json.dumps(result_line(args, layout, world, ms, e2e_ms, h2d, d2h, clocks, launches, "picotron_b200",
+                                     {"final_loss": last.get("loss")})), flush=True)
+    dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------- reference
+def run_reference(args):
+    ref_root = os.path.join(REPO, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "picotron")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/picotron is not installed"}))
+        return
+    try:
+        rank, local_rank, world = setup_distributed(args.gpus)
+        device = torch.device("cuda", local_rank)
+        layout = LAYOUTS[world]
+        os.environ["FLASH_ATTEN"] = "1"
+        os.environ["DEVICE"] = "cuda"
+        os.environ["DTYPE"] = "bfloat16"
+        sys.path.insert(0, ref_root)
+        import torch.nn.functional as F
+        import picotron.process_group_manager as rpgm
+        from picotron.model import Llama as RefLlama
+        from picotron.tensor_parallel.tensor_parallel import apply_tensor_parallel as ref_apply_tp
+        from picotron.tensor_parallel.tp_communications import vocab_parallel_cross_entropy as ref_vce
+        from picotron.data_parallel.zero import DataParallelZero as RefZero, ShardedOptimizer as RefSharded
+        from picotron.utils import set_all_seed
+
+        rpgm.setup_process_group_manager(tp_size=layout["tp"], cp_size=1, pp_size=1, dp_size=layout["dp"], ep_size=1)
+        pg = rpgm.process_group_manager
+        set_all_seed(1234)
+        mcfg = SimpleNamespace(**{k: v for k, v in MODEL.items() if k != "name"}, num_experts=1)
+        model = RefLlama(mcfg)
+        tp = layout["tp"]
+        if tp > 1:
+            ref_apply_tp(model, sequence_parallel=True, vocab_parallel_ce=True)
+        with torch.no_grad():
+            for p in model.parameters():          # N(0, 0.02) like our arm (norm weights stay 1)
+                if p.dim() > 1:
+                    p.normal_(0.0, 0.02)
+        model.to(torch.bfloat16).to(device)
+        if layout["dp"] > 1:
+            dp_model = RefZero(model, stage=1)
+            optimizer = RefSharded(dp_model, torch.optim.AdamW, lr=LR)
+        else:
+            dp_model = model
+            optimizer = torch.optim.AdamW(model.parameters(), lr=LR)
+        norm_params = [p for n, p in model.named_parameters() if "layernorm" in n or "final_norm" in n]
+
+        g = torch.Generator().manual_seed(99 + pg.dp_rank)
+
+        def host_batch():
+            rows = torch.randint(0, MODEL["vocab_size"], (MBS, SEQ + 1), generator=g)
+            return rows[:, :-1].contiguous().pin_memory(), rows[:, 1:].contiguous().pin_memory()
+
+        resident = [tuple(t.to(device) for t in host_batch()) for _ in range(GRAD_ACC)]
+
+        def micro_batch(inp, tgt, last):
+            if layout["dp"] > 1:
+                dp_model.require_backward_grad_sync = last
+            logits = dp_model(input_ids=inp)
+            b, s = inp.shape
+            logits = logits.view(b * s, -1)
+            if tp > 1:
+                loss = ref_vce(logits.float(), tgt.reshape(-1)).mean() / GRAD_ACC
+            else:
+                loss = F.cross_entropy(logits, tgt.reshape(-1), reduction="mean") / GRAD_ACC
+            loss.backward()
+            return loss
+
+        def finish_step():
+            if tp > 1:   # sequence-parallel norm gradients, as the reference's own TP benchmark does
+                for p in norm_params:
+                    if p.grad is not None:
+                        dist.all_reduce(p.grad, group=pg.tp_group)
+            optimizer.step()
+            optimizer.zero_grad()
+
+        def device_step():
+            for i, (inp, tgt) in enumerate(resident):
+                micro_batch(inp, tgt, i == GRAD_ACC - 1)
+            finish_step()
+
+        last = {}
+
+        def e2e_step():
+            acc = 0.0
+            for i in range(GRAD_ACC):
+                inp, tgt = host_batch()
+                loss = micro_batch(inp.to(device), tgt.to(device), i == GRAD_ACC - 1)
+                acc += loss.item()                 # the reference's train_step reads every micro-batch loss
+            finish_step()
+            last["loss"] = acc
+
+        for _ in range(args.warmup):
+            device_step()
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        ms = timed(device_step, args.steps, device)
+        clocks = sampler.stop() if sampler else {}
+        for _ in range(max(1, args.warmup // 2)):
+            e2e_step()
+        e2e_ms = timed(e2e_step, args.steps, device)
+        h2d = GRAD_ACC * 2 * MBS * SEQ * 8
+        d2h = GRAD_ACC * 4
+        if rank == 0:
+            print(json.dumps(result_line(args, layout, world, ms, e2e_ms, h2d, d2h, clocks, 0, "reference",
+                                         {"final_loss": last.get("loss")})), flush=True)
+        dist.destroy_process_group()
+    except Exception as exc:  # the reference could not run on this stack: say why, exit 0
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference",
+                              "unavailable": f"{type(exc).__name__}: {str(exc).splitlines()[0][:300] if str(exc) else ''}"}),
+                  flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    assert args.gpus in LAYOUTS, f"--gpus must be one of {sorted(LAYOUTS)}"
+    args.warmup = max(3, args.warmup)   # never time a cold run
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,258 @@
+"""Training engine: builds the parallel model from a config and runs optimizer steps.
+
+This is the programmatic form of ``train.py`` (and what ``bench.py`` times): topology ->
+model -> tensor / pipeline / context / data parallel wrappers -> optimizer -> ``train_step``.
+It follows the order of the reference trainer (train.py:254-289: TP, then PP, then CP, then
+dtype/device, then DP) and wires in what the reference leaves as library code: sequence
+parallelism, vocabulary-parallel cross entropy, ZeRO, interleaved 1F1B and ZB-V.
+
+Two gradient paths exist, split by device exactly like the ops:
+
+* CUDA/bf16 ("flat" path): parameters and fp32 gradients live in one flat buffer each
+  (``ParamStore``); weight-gradient GEMMs accumulate into it, the data-parallel reduction is a
+  reduce-scatter (ZeRO-1) or all-reduce of that buffer and AdamW is one kernel over this rank's
+  shard followed by an all-gather of the updated parameters.
+* CPU/fp32 (plumbing path, gloo): ordinary autograd ``.grad`` with the ``DataParallelBucket`` /
+  ``DataParallelZero`` wrappers and ``torch.optim.AdamW``, as the reference does.
+"""
+from __future__ import annotations
+
+import contextlib
+from types import SimpleNamespace
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import process_group_manager as pgm
+from .config import load_config, model_config_from
+from .data import MicroBatchDataLoader
+from .models.llama import Llama
+from .ops import adamw as adamw_ops
+from .ops import cross_entropy as ce_ops
+from .param_store import ParamStore
+from .parallel.dist_utils import group_rank, group_size
+
+
+def _dtype_of(cfg, device) -> torch.dtype:
+    if device.type != "cuda" or cfg["distributed"]["use_cpu"]:
+        return torch.float32
+    return {"bfloat16": torch.bfloat16, "float32": torch.float32}[cfg["model"].get("dtype", "bfloat16")]
+
+
+def loss_fn(model, logits, targets) -> torch.Tensor:
+    """Mean token loss from the model output: dense logits, or vocabulary-sharded logits when
+    the lm head keeps them sharded (``vocab_parallel_ce``)."""
+    if getattr(model, "vocab_parallel_ce", False) and group_size(getattr(model, "tp_group", None)) > 1:
+        g = model.tp_group
+        start = group_rank(g) * logits.shape[-1]
+        return ce_ops.cross_entropy(logits, targets, vocab_start=start, group=g).mean()
+    return ce_ops.cross_entropy(logits, targets).mean()
+
+
+class FlatOptimizer:
+    """AdamW on the flat buffers of a ParamStore, optionally sharded over a data-parallel group
+    (ZeRO-1: reduce-scatter gradients, update the local shard, all-gather parameters)."""
+
+    def __init__(self, store: ParamStore, lr, weight_decay=0.01, betas=(0.9, 0.999), eps=1e-8, dp_group=None,
+                 zero_stage: int = 0, sp_grad_params=None, tp_group=None, expert_store=None):
+        self.store, self.dp_group, self.zero_stage = store, dp_group, zero_stage
+        self.dp_size = group_size(dp_group)
+        self.dp_rank = group_rank(dp_group)
+        self.sp_grad_params = list(sp_grad_params or [])
+        self.tp_group = tp_group
+        n = store.numel
+        if self.zero_stage >= 1 and self.dp_size > 1:
+            assert n % self.dp_size == 0
+            shard = n // self.dp_size
+            lo = self.dp_rank * shard
+            self.shard_params = store.flat_params[lo:lo + shard]
+            self.shard_grads = store.flat_grads[lo:lo + shard]
+        else:
+            self.shard_params, self.shard_grads = store.flat_params, store.flat_grads
+        self.adam = adamw_ops.FlatAdamW(self.shard_params, self.shard_grads, lr=lr, betas=betas, eps=eps,
+                                        weight_decay=weight_decay)
+
+    def reduce_sequence_parallel_grads(self):
+        """Norm weights see only a sequence shard under sequence parallelism: sum their gradients
+        over the TP group (the reference does this only in its tests,
+        tests/test_tp_sequence_parallel.py:151-152)."""
+        if not self.sp_grad_params or group_size(self.tp_group) == 1:
+            return
+        flat = torch.cat([p.main_grad.reshape(-1) for p in self.sp_grad_params])
+        dist.all_reduce(flat, group=self.tp_group)
+        off = 0
+        for p in self.sp_grad_params:
+            p.main_grad.copy_(flat[off:off + p.numel()].view_as(p.main_grad))
+            off += p.numel()
+
+    def step(self, grad_scale: float = 1.0):
+        self.reduce_sequence_parallel_grads()
+        st = self.store
+        if self.dp_size > 1:
+            if self.zero_stage >= 1:
+                dist.reduce_scatter_tensor(self.shard_grads, st.flat_grads, group=self.dp_group)
+            else:
+                dist.all_reduce(st.flat_grads, group=self.dp_group)
+        self.adam.step(grad_scale=grad_scale / self.dp_size, zero_grad=False)
+        st.flat_grads.zero_()
+        if self.dp_size > 1 and self.zero_stage >= 1:
+            dist.all_gather_into_tensor(st.flat_params, self.shard_params, group=self.dp_group)
+
+    def zero_grad(self):
+        self.store.flat_grads.zero_()
+
+    def state_dict(self):
+        return self.adam.state_dict()
+
+    def load_state_dict(self, sd):
+        self.adam.load_state_dict(sd)
+
+
+class TrainEngine:
+    def __init__(self, cfg, device: Optional[torch.device] = None):
+        cfg = load_config(cfg)
+        self.cfg = cfg
+        d, t = cfg["distributed"], cfg["training"]
+        if device is None:
+            device = torch.device("cpu") if d["use_cpu"] or not torch.cuda.is_available() \
+                else torch.device("cuda", torch.cuda.current_device())
+        self.device = device
+        self.dtype = _dtype_of(cfg, device)
+        m = pgm.process_group_manager
+        if m is None or (m.tp_world_size, m.cp_world_size, m.pp_world_size, m.dp_world_size, m.ep_world_size) != \
+                (d["tp_size"], d["cp_size"], d["pp_size"], d["dp_size"], d["ep_size"]):
+            m = pgm.setup_process_group_manager(d["tp_size"], d["cp_size"], d["pp_size"], d["dp_size"], d["ep_size"])
+        self.pgm = m
+        self.model_config = model_config_from(cfg)
+        torch.manual_seed(t["seed"])
+        self.data_loader = MicroBatchDataLoader(
+            micro_batch_size=t["micro_batch_size"], seq_length=t["seq_length"], dataset_name=cfg["dataset"]["name"],
+            tokenizer_name=cfg["model"]["name"], grad_acc_steps=t["gradient_accumulation_steps"],
+            num_samples=t["num_samples"], vocab_size=self.model_config.vocab_size, seed=t["seed"],
+            subset_name=cfg["dataset"].get("subset_name"), split=cfg["dataset"].get("split", "train"),
+            num_proc=cfg["dataset"].get("num_proc", 1),
+            dp_world_size=m.dp_world_size * (m.ep_world_size if d["ep_as_dp"] else 1),
+            dp_rank=m.dp_rank * (m.ep_world_size if d["ep_as_dp"] else 1) + (m.ep_rank if d["ep_as_dp"] else 0))
+        self.tokens_per_step = self.data_loader.global_batch_size * t["seq_length"]
+        self._build_model()
+        self._build_optimizer()
+        self.trained_steps = 0
+        self.trained_tokens = 0
+
+    # ------------------------------------------------------------------------------ build
+    def _build_model(self):
+        from .parallel.tensor_parallel import apply_tensor_parallel
+        d = self.cfg["distributed"]
+        m = self.pgm
+        build_device = self.device if self.device.type == "cuda" else torch.device("cpu")
+        with torch.device(build_device):
+            model = Llama(self.model_config)
+        if m.tp_world_size > 1:
+            with torch.device(build_device):
+                apply_tensor_parallel(model, async_tp=d["async_tp"], sequence_parallel=d["sequence_parallel"],
+                                      vocab_parallel_ce=d["vocab_parallel_ce"], overlap_comm=d["overlap_comm"])
+        if m.pp_world_size > 1:
+            from .parallel.pipeline_parallel import wrap_pipeline
+            model = wrap_pipeline(model, self.model_config, d["pp_engine"], d["num_virtual_stages"])
+        if m.cp_world_size > 1:
+            from .parallel.context_parallel import apply_context_parallel
+            apply_context_parallel(model, attention=d["cp_attention"])
+        model.to(self.dtype).to(self.device)
+        self.model = model
+        self.flat = self.device.type == "cuda" and self.dtype == torch.bfloat16
+        self.store = ParamStore(model, pad_to_multiple=max(1, self._grad_group_size())) if self.flat else None
+
+    def _grad_group(self):
+        m = self.pgm
+        if self.cfg["distributed"]["ep_as_dp"] and m.ep_world_size > 1:
+            return m.dense_dp_group
+        return m.cp_dp_group
+
+    def _grad_group_size(self):
+        m = self.pgm
+        n = m.cp_dp_world_size
+        if self.cfg["distributed"]["ep_as_dp"]:
+            n *= m.ep_world_size
+        return n
+
+    def _build_optimizer(self):
+        t, d = self.cfg["training"], self.cfg["distributed"]
+        m = self.pgm
+        if self.flat:
+            sp_params = [p for p in self.model.parameters() if getattr(p, "sequence_parallel_grad", False)]
+            self.optimizer = FlatOptimizer(self.store, lr=t["learning_rate"], weight_decay=t["weight_decay"],
+                                           dp_group=self._grad_group() if self._grad_group_size() > 1 else None,
+                                           zero_stage=d["zero_stage"], sp_grad_params=sp_params,
+                                           tp_group=m.tp_group)
+            self.dp_model = self.model
+            return
+        from .parallel.data_parallel import DataParallelBucket, DataParallelNaive
+        from .parallel.zero import DataParallelZero, ShardedOptimizer
+        self.dp_model = self.model
+        if self._grad_group_size() > 1:
+            if d["zero_stage"] >= 1 or d["dp_engine"] == "zero":
+                self.dp_model = DataParallelZero(self.model, stage=max(1, d["zero_stage"]), group=self._grad_group())
+                self.optimizer = ShardedOptimizer(self.dp_model, torch.optim.AdamW, lr=t["learning_rate"],
+                                                  weight_decay=t["weight_decay"])
+                return
+            cls = DataParallelNaive if d["dp_engine"] == "naive" else DataParallelBucket
+            self.dp_model = cls(self.model, group=self._grad_group())
+        self.optimizer = torch.optim.AdamW(self.model.parameters(), lr=t["learning_rate"],
+                                           weight_decay=t["weight_decay"])
+
+    # ------------------------------------------------------------------------------ step
+    def _sync_context(self, last: bool):
+        dp = self.dp_model
+        if hasattr(dp, "require_backward_grad_sync"):
+            dp.require_backward_grad_sync = last
+        return contextlib.nullcontext()
+
+    def train_step(self, device_batches=None) -> torch.Tensor:
+        """One optimizer step over ``gradient_accumulation_steps`` micro-batches. Returns the mean
+        loss as a 0-d tensor on the device (no host sync).
+
+        ``device_batches``: optional list of ``(input_ids, target_ids)`` already on the device,
+        one per micro-batch, used instead of the data loader (kernel-only timing)."""
+        m = self.pgm
+        dl = self.data_loader
+        ga = dl.grad_acc_steps
+        if m.pp_world_size > 1:
+            from .parallel.pipeline_parallel import run_pipeline_step
+            loss = run_pipeline_step(self, device_batches)
+        else:
+            loss = torch.zeros((), device=self.device, dtype=torch.float32)
+            for i in range(ga):
+                if device_batches is not None:
+                    input_ids, target_ids = device_batches[i]
+                else:
+                    batch = next(dl)
+                    input_ids = batch["input_ids"].to(self.device, non_blocking=True)
+                    target_ids = batch["target_ids"].to(self.device, non_blocking=True)
+                self._sync_context(i == ga - 1)
+                logits = self.dp_model(input_ids=input_ids)
+                mb_loss = loss_fn(self.model, logits, target_ids) / ga
+                aux = self._aux_loss()
+                total = mb_loss + aux / ga if aux is not None else mb_loss
+                total.backward()
+                loss += mb_loss.detach().float()
+        self._optimizer_step()
+        self.trained_steps += 1
+        self.trained_tokens += self.tokens_per_step
+        return loss
+
+    def _aux_loss(self):
+        if getattr(self.model_config, "num_experts", 1) > 1:
+            from .parallel.expert_parallel import collect_aux_loss
+            return collect_aux_loss(self.model)
+        return None
+
+    def _optimizer_step(self):
+        if self.flat:
+            self.optimizer.step()
+        else:
+            self.optimizer.step()
+            self.optimizer.zero_grad()
+            if hasattr(self.dp_model, "reset"):
+                self.dp_model.reset()

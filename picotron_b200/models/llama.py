@@ -1,0 +1,283 @@
+"""Llama-style decoder-only transformer.
+
+Same module tree and state-dict names as picotron/model.py:356-402 —
+``embedding``, ``decoder_layers.{i}.{input_layernorm, attention.{q,k,v,out}_proj,
+post_attention_layernorm, mlp.{up,gate,down}_proj}``, ``final_norm``, ``final_proj`` — with
+pre-norm sequential blocks or the parallel transformer block (``config.parallel_block``:
+``x + Attn(LN(x)) + MLP(LN(x))`` with a single norm, model.py:319-329), SwiGLU or MoE
+feed-forward (``config.num_experts > 1``), grouped-query attention and half-split RoPE.
+
+Design differences from the reference:
+* the model never reads the environment or a global topology in ``forward``: parallel layers
+  carry their group, the attention backend is an attribute (``attention.core``) that
+  ``apply_context_parallel`` swaps, RoPE tables are built once per model
+* q/k/v and gate/up share their input collective and, on the GPU, the residual add is folded
+  into the following RMSNorm
+* GQA is not expanded before attention
+* hot ops dispatch to the hand-written kernels in ``picotron_b200.ops``
+"""
+from __future__ import annotations
+
+from typing import Iterator, Optional
+
+import torch
+import torch.nn as nn
+
+from ..ops import attention as attn_ops
+from ..ops import embedding as emb_ops
+from ..ops import norm as norm_ops
+from ..ops import rope as rope_ops
+from ..ops import swiglu as swiglu_ops
+from ..parallel.tensor_parallel import Linear, multi_linear
+
+
+class RMSNorm(nn.Module):
+    """x * rsqrt(mean(x^2) + eps) * weight with fp32 statistics (picotron/model.py:96-115)."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-5):
+        super().__init__()
+        self.eps = eps
+        self.hidden_size = hidden_size
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+        # under sequence parallelism every TP rank sees a different sequence shard, so this
+        # weight's gradient must be summed over the TP group before the optimizer step
+        self.weight.sequence_parallel_grad = False
+
+    def reset_parameters(self):
+        if self.weight.device.type != "meta":
+            nn.init.ones_(self.weight)
+
+    def forward(self, x, residual=None):
+        if residual is None:
+            return norm_ops.rmsnorm(x, self.weight, self.eps)
+        return norm_ops.add_rmsnorm(x, residual, self.weight, self.eps)
+
+
+LlamaRMSNorm = RMSNorm
+
+
+class Embedding(nn.Module):
+    def __init__(self, num_embeddings: int, embedding_dim: int, init_std=None):
+        super().__init__()
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.init_std = init_std
+        self.weight = nn.Parameter(torch.empty(num_embeddings, embedding_dim))
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        if self.weight.device.type != "meta":
+            nn.init.normal_(self.weight, mean=0.0, std=self.init_std if self.init_std is not None else 1.0)
+
+    def forward(self, input_ids):
+        return emb_ops.embedding(input_ids, self.weight, 0)
+
+
+class FinalProjection(Linear):
+    """The lm head: hidden -> vocabulary logits."""
+
+
+def _local_attention(q, k, v, causal, sm_scale=None):
+    return attn_ops.attention(q, k, v, causal, sm_scale)
+
+
+class Attention(nn.Module):
+    def __init__(self, config, layer_idx: int):
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        self.num_heads = config.num_attention_heads
+        self.num_key_values = config.num_key_value_heads
+        self.head_dim = self.hidden_size // self.num_heads
+        self.num_local_heads = self.num_heads          # divided by apply_tensor_parallel
+        self.num_local_kv_heads = self.num_key_values
+        std = getattr(config, "init_std", None)
+        self.q_proj = Linear(config.hidden_size, self.num_heads * self.head_dim, std)
+        self.k_proj = Linear(config.hidden_size, self.num_key_values * self.head_dim, std)
+        self.v_proj = Linear(config.hidden_size, self.num_key_values * self.head_dim, std)
+        self.out_proj = Linear(config.hidden_size, config.hidden_size, std)
+        self.layer_idx = layer_idx
+        #: callable (q, k, v, causal) -> out on [b, s, heads, d] tensors; context parallelism
+        #: replaces it with ring or Ulysses attention
+        self.core = _local_attention
+
+    def reset_parameters(self):
+        for m in (self.q_proj, self.k_proj, self.v_proj, self.out_proj):
+            m.reset_parameters()
+
+    def qkv(self, x, rope):
+        b = x.shape[0]
+        q, k, v = multi_linear([self.q_proj, self.k_proj, self.v_proj], x)
+        s = q.shape[1]  # full sequence under sequence parallelism
+        q = q.view(b, s, self.num_local_heads, self.head_dim)
+        k = k.view(b, s, self.num_local_kv_heads, self.head_dim)
+        v = v.view(b, s, self.num_local_kv_heads, self.head_dim)
+        q = rope.apply(q)
+        k = rope.apply(k)
+        return q, k, v
+
+    def forward(self, x, rope, out_addend=None):
+        q, k, v = self.qkv(x, rope)
+        b, s = q.shape[0], q.shape[1]
+        out = self.core(q, k, v, True)
+        out = out.reshape(b, s, self.num_local_heads * self.head_dim)
+        if out_addend is not None:
+            return self.out_proj(out, out_addend)
+        return self.out_proj(out)
+
+
+class MLP(nn.Module):
+    """SwiGLU feed-forward: down(silu(gate(x)) * up(x)) (picotron/model.py:236-258)."""
+
+    is_moe = False
+
+    def __init__(self, config, intermediate_size: Optional[int] = None):
+        super().__init__()
+        inter = intermediate_size if intermediate_size is not None else config.intermediate_size
+        std = getattr(config, "init_std", None)
+        self.up_proj = Linear(config.hidden_size, inter, std)
+        self.gate_proj = Linear(config.hidden_size, inter, std)
+        self.down_proj = Linear(inter, config.hidden_size, std)
+
+    def reset_parameters(self):
+        for m in (self.up_proj, self.gate_proj, self.down_proj):
+            m.reset_parameters()
+
+    def hidden(self, x):
+        return swiglu_ops.swiglu(multi_linear([self.gate_proj, self.up_proj], x, cat=True))
+
+    def forward(self, x):
+        return self.down_proj(self.hidden(x))
+
+
+class RotaryTables:
+    """cos/sin tables shared by all layers of a model, plus this rank's position offset
+    (non-zero under context parallelism, where rank r holds positions [r*s_local, (r+1)*s_local))."""
+
+    def __init__(self, max_positions: int, head_dim: int, theta: float):
+        self.max_positions, self.head_dim, self.theta = max_positions, head_dim, theta
+        self.pos_offset = 0
+        self._cache = {}
+
+    def tables(self, device, dtype):
+        key = (str(device), dtype)
+        t = self._cache.get(key)
+        if t is None:
+            cos, sin = rope_ops.get_cos_sin(self.max_positions, self.head_dim, self.theta, device=device,
+                                            dtype=torch.float32)
+            t = (cos, sin, rope_ops.rope_tables_for_kernel(cos, sin))
+            self._cache[key] = t
+        return t
+
+    def apply(self, x):
+        cos, sin, half = self.tables(x.device, x.dtype)
+        return rope_ops.apply_rope(x, cos, sin, self.pos_offset, tables=half)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, config, layer_idx: int):
+        super().__init__()
+        self.parallel_block = bool(getattr(config, "parallel_block", False))
+        self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.attention = Attention(config, layer_idx)
+        if getattr(config, "num_experts", 0) and config.num_experts > 1:
+            from ..parallel.expert_parallel import MoELayer
+            self.mlp = MoELayer(config)
+        else:
+            self.mlp = MLP(config)
+        if not self.parallel_block:
+            self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.layer_idx = layer_idx
+        self.sequence_parallel = False
+        self.tp_group = None
+
+    def reset_parameters(self):
+        self.input_layernorm.reset_parameters()
+        self.attention.reset_parameters()
+        self.mlp.reset_parameters()
+        if not self.parallel_block:
+            self.post_attention_layernorm.reset_parameters()
+
+    def norms(self):
+        out = [self.input_layernorm]
+        if not self.parallel_block:
+            out.append(self.post_attention_layernorm)
+        return out
+
+    def configure_tensor_parallel(self, sequence_parallel: bool, group):
+        """Called by apply_tensor_parallel after the projections were swapped."""
+        self.sequence_parallel = sequence_parallel
+        self.tp_group = group
+        for n in self.norms():
+            n.weight.sequence_parallel_grad = sequence_parallel
+        fused_ptb = self.parallel_block and sequence_parallel and not getattr(self.mlp, "is_moe", False)
+        overlap = getattr(self.attention.out_proj, "overlap_comm", False)
+        attn, mlp = self.attention, self.mlp
+        if fused_ptb and not overlap:
+            # one shared all-gather in, one reduce-scatter of the attn+mlp partial sums out; the
+            # projections run without collectives of their own
+            for m in (attn.q_proj, attn.k_proj, attn.v_proj, attn.out_proj, mlp.gate_proj, mlp.up_proj,
+                      mlp.down_proj):
+                m.raw = True
+        elif fused_ptb:
+            # chunked overlap: q/k/v and gate/up each ride a ring all-gather; the MLP partial sum
+            # is folded into the out-projection's pipelined reduce-scatter
+            mlp.down_proj.raw = True
+        self.fused_ptb = fused_ptb
+        self.ptb_overlap = fused_ptb and overlap
+
+    def forward(self, x, rope):
+        if self.parallel_block:
+            return self._forward_parallel(x, rope)
+        a = self.attention(self.input_layernorm(x), rope)
+        y, h = self.post_attention_layernorm(a, residual=x)
+        return h + self.mlp(y)
+
+    def _forward_parallel(self, x, rope):
+        from ..parallel import sequence_parallel as sp
+        n = self.input_layernorm(x)
+        if getattr(self, "fused_ptb", False):
+            if self.ptb_overlap:
+                mlp_partial = self.mlp(n)  # un-reduced [b, s, h] partial sum (down_proj is raw)
+                return x + self.attention(n, rope, out_addend=mlp_partial)
+            ng = sp.GatherFromSequenceParallelRegion.apply(n, self.tp_group)
+            partial = self.attention(ng, rope) + self.mlp(ng)
+            return x + sp.ReduceScatterToSequenceParallelRegion.apply(partial, self.tp_group)
+        return x + self.attention(n, rope) + self.mlp(n)
+
+
+class Llama(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        assert config.hidden_size % config.num_attention_heads == 0
+        assert config.num_attention_heads % config.num_key_value_heads == 0
+        self.config = config
+        self.vocab_size = config.vocab_size
+        self.hidden_size = config.hidden_size
+        self.num_layers = config.num_hidden_layers
+        std = getattr(config, "init_std", None)
+        self.embedding = Embedding(config.vocab_size, config.hidden_size, std)
+        self.decoder_layers = nn.ModuleList([DecoderLayer(config, i) for i in range(config.num_hidden_layers)])
+        self.final_norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.final_proj = FinalProjection(config.hidden_size, config.vocab_size, std)
+        self.rope = RotaryTables(config.max_position_embeddings, config.hidden_size // config.num_attention_heads,
+                                 getattr(config, "rope_theta", 500000.0))
+        self.sequence_parallel = False
+        self.vocab_parallel_ce = False
+        self.tp_group = None
+
+    def decoder_layers_iter(self) -> Iterator[DecoderLayer]:
+        layers = self.decoder_layers
+        return iter(layers.values()) if isinstance(layers, nn.ModuleDict) else iter(layers)
+
+    def reset_parameters(self):
+        self.embedding.reset_parameters()
+        for layer in self.decoder_layers_iter():
+            layer.reset_parameters()
+        self.final_norm.reset_parameters()
+        self.final_proj.reset_parameters()
+
+    def forward(self, input_ids, position_ids=None, hidden_states=None):
+        x = self.embedding(input_ids)
+        for layer in self.decoder_layers_iter():
+            x = layer(x, self.rope)
+        x = self.final_norm(x)
+        return self.final_proj(x)

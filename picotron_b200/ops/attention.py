@@ -1,0 +1,86 @@
+"""Scaled dot-product attention in the ``[batch, seq, heads, head_dim]`` layout.
+
+``attention(q, k, v, causal)`` accepts grouped-query inputs (fewer K/V heads than Q heads)
+without materialising the repeated heads that picotron/model.py:197-202 creates.
+``attention_block(q, k, v, causal)`` additionally returns the log-sum-exp per (batch, head,
+query) so partial results over different key blocks can be merged exactly — the building
+block of ring attention (picotron/context_parallel/context_parallel.py:240-290).
+``merge_attention_blocks`` is that merge (context_parallel.py:293-323), written with
+``logaddexp`` instead of the sigmoid/logsigmoid pair.
+
+Everything here is differentiable through ordinary autograd (the block form uses explicit
+matmuls so it runs on CPU/gloo); the CUDA fast path for whole-sequence attention is selected
+in ``attention``.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def _expand_kv(k: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """[b, s, kvh, d] -> [b, s, n_heads, d] by repeating each KV head for its query group."""
+    kvh = k.shape[2]
+    if kvh == n_heads:
+        return k
+    rep = n_heads // kvh
+    return k[:, :, :, None, :].expand(-1, -1, -1, rep, -1).reshape(k.shape[0], k.shape[1], n_heads, k.shape[3])
+
+
+def attention_ref(q, k, v, causal: bool, sm_scale: float | None = None) -> torch.Tensor:
+    """fp32-accumulating reference. q: [b, sq, H, d], k/v: [b, sk, Hkv, d] -> [b, sq, H, d]."""
+    out, _ = attention_block(q, k, v, causal, sm_scale)
+    return out
+
+
+def attention_block(q, k, v, causal: bool, sm_scale: float | None = None, q_offset: int = 0,
+                    k_offset: int = 0):
+    """Attention of q against one block of keys, returning (out, lse).
+
+    ``q_offset`` / ``k_offset`` are the global positions of the first query / key; with
+    ``causal`` a query at global position i sees keys at global positions <= i. Rows that see
+    no key get out = 0 and lse = -inf. lse has shape [b, H, sq] (fp32).
+    """
+    b, sq, H, d = q.shape
+    sk = k.shape[1]
+    scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(d)
+    kf = _expand_kv(k, H)
+    vf = _expand_kv(v, H)
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.float(), kf.float()) * scale
+    if causal:
+        qi = torch.arange(sq, device=q.device)[:, None] + q_offset
+        ki = torch.arange(sk, device=q.device)[None, :] + k_offset
+        scores = scores.masked_fill(ki > qi, float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)  # [b, H, sq]
+    safe_lse = torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)
+    p = torch.exp(scores - safe_lse[..., None])
+    p = torch.where(torch.isinf(lse)[..., None], torch.zeros_like(p), p)
+    out = torch.einsum("bhqk,bkhd->bqhd", p, vf.float())
+    return out.to(q.dtype), lse
+
+
+def merge_attention_blocks(out, lse, blk_out, blk_lse):
+    """Exact merge of two partial attention results over disjoint key sets.
+
+    out/blk_out: [b, s, H, d]; lse/blk_lse: [b, H, s] fp32. Returns (out, lse) with out fp32.
+    """
+    if out is None:
+        return blk_out.float(), blk_lse
+    new_lse = torch.logaddexp(lse, blk_lse)
+    safe = torch.where(torch.isinf(new_lse), torch.zeros_like(new_lse), new_lse)
+    w_old = torch.exp(lse - safe).transpose(1, 2).unsqueeze(-1)      # [b, s, H, 1]
+    w_new = torch.exp(blk_lse - safe).transpose(1, 2).unsqueeze(-1)
+    return out.float() * w_old + blk_out.float() * w_new, new_lse
+
+
+def attention(q, k, v, causal: bool = True, sm_scale: float | None = None) -> torch.Tensor:
+    """Whole-sequence attention. q: [b, s, H, d]; k, v: [b, s, Hkv, d] -> [b, s, H, d]."""
+    if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
+        # library flash kernel (cuDNN / FlashAttention through SDPA), GQA handled natively
+        H, kvh = q.shape[2], k.shape[2]
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                           is_causal=causal, scale=sm_scale, enable_gqa=(H != kvh))
+        return o.transpose(1, 2)
+    return attention_ref(q, k, v, causal, sm_scale)

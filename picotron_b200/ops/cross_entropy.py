@@ -30,8 +30,9 @@ def combine_stats(stats: torch.Tensor, group) -> torch.Tensor:
     if group is None or dist.get_world_size(group) == 1:
         return stats
     world = dist.get_world_size(group)
-    gathered = torch.empty((world,) + tuple(stats.shape), device=stats.device, dtype=stats.dtype)
-    dist.all_gather_into_tensor(gathered, stats.contiguous(), group=group)
+    flat = torch.empty((world * stats.shape[0],) + tuple(stats.shape[1:]), device=stats.device, dtype=stats.dtype)
+    dist.all_gather_into_tensor(flat, stats.contiguous(), group=group)
+    gathered = flat.view((world,) + tuple(stats.shape))
     m = gathered[..., 0].max(dim=0).values
     s = (gathered[..., 1] * torch.exp(gathered[..., 0] - m)).sum(dim=0)
     t = gathered[..., 2].sum(dim=0)

@@ -117,3 +117,96 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if use_kernels(x, w) and _gemm_ok(x.shape[-1], w.shape[0]):
         return _LinearFn.apply(x, w)
     return linear_ref(x, w)
+
+
+# ---------------------------------------------------------------------------------------------
+# several projections of one input
+# ---------------------------------------------------------------------------------------------
+class WeightSet:
+    """The weights of projections that share an input: either separate parameters or one fused
+    ``[sum(out_i), in]`` view over parameters stored back to back (see ``param_store``)."""
+
+    def __init__(self, params, fused_weight=None, fused_main_grad=None):
+        self.params = list(params)
+        self.fused_weight = fused_weight
+        self.fused_main_grad = fused_main_grad
+        self.splits = [p.shape[0] for p in self.params]
+
+    @staticmethod
+    def of(mods) -> "WeightSet":
+        fused = getattr(mods[0], "_fused_group", None)
+        if fused is not None and len(fused.mods) == len(mods) and all(a is b for a, b in zip(fused.mods, mods)):
+            return WeightSet([m.weight for m in mods], fused.weight, fused.main_grad)
+        return WeightSet([m.weight for m in mods])
+
+    @property
+    def out_features(self) -> int:
+        return sum(self.splits)
+
+
+def project_all(x2: torch.Tensor, ws: WeightSet) -> torch.Tensor:
+    """x2[M,K] -> [M, sum(out_i)]; one GEMM when fused, else one per weight into column slices."""
+    M = x2.shape[0]
+    if ws.fused_weight is not None:
+        return gemm_nt(x2, ws.fused_weight)
+    out = torch.empty((M, ws.out_features), device=x2.device, dtype=x2.dtype)
+    col = 0
+    for w in ws.params:
+        gemm_nt(x2, w, out=out[:, col:col + w.shape[0]])
+        col += w.shape[0]
+    return out
+
+
+def backward_all(dy2: torch.Tensor, x2: torch.Tensor, ws: WeightSet, need_dx: bool = True):
+    """Returns (dx2 or None, [grad per param or None when accumulated into main_grad])."""
+    dx = None
+    if ws.fused_weight is not None:
+        if need_dx:
+            dx = gemm_nn(dy2, ws.fused_weight)
+        if ws.fused_main_grad is not None:
+            gemm_tn(dy2, x2, out=ws.fused_main_grad, accumulate=True)
+            for p in ws.params:
+                hook = getattr(p, "grad_ready_hook", None)
+                if hook is not None:
+                    hook()
+            return dx, [None] * len(ws.params)
+        dw = gemm_tn(dy2, x2)
+        return dx, list(dw.split(ws.splits, dim=0))
+    grads = []
+    col = 0
+    for w in ws.params:
+        dyi = dy2[:, col:col + w.shape[0]]
+        col += w.shape[0]
+        if need_dx:
+            part = gemm_nn(dyi, w)
+            dx = part if dx is None else dx.add_(part)
+        grads.append(wgrad_into(w, dyi, x2))
+    return dx, grads
+
+
+class _MultiLinearFn(torch.autograd.Function):
+    """y = x @ cat(weights).T as one output tensor; parameters are passed so that autograd runs
+    the backward (and with it the main_grad accumulation) even when x needs no gradient."""
+
+    @staticmethod
+    def forward(ctx, x, ws, *params):
+        x2 = _as_2d(x)
+        ctx.ws = ws
+        ctx.x_shape = x.shape
+        ctx.save_for_backward(x2)
+        return project_all(x2, ws).view(*x.shape[:-1], ws.out_features)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        dy2 = _as_2d(dy)
+        dx, grads = backward_all(dy2, x2, ctx.ws, need_dx=ctx.needs_input_grad[0])
+        return (dx.view(ctx.x_shape) if dx is not None else None, None, *grads)
+
+
+def multi_linear_cat(x: torch.Tensor, mods) -> torch.Tensor:
+    """Concatenated outputs ``[..., sum(out_i)]`` of bias-free projections sharing the input x."""
+    ws = WeightSet.of(mods)
+    if use_kernels(x, ws.params[0]) and _gemm_ok(x.shape[-1], *ws.splits):
+        return _MultiLinearFn.apply(x, ws, *ws.params)
+    return torch.cat([linear_ref(x, w) for w in ws.params], dim=-1)

@@ -1,0 +1,84 @@
+"""Tensor parallelism on CPU/gloo against the single-process model: every TP mode (plain,
+async, sequence parallel, vocabulary-parallel CE, chunked overlap, parallel block) must give
+the single-process loss and gradients (sliced the same way as the weights) within 2e-4 in fp32
+— the tolerance of the reference's tests/test_tp_sequence_parallel.py:183."""
+import types
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from distributed_helpers import run_distributed
+
+
+def tiny_config(**kw):
+    cfg = dict(hidden_size=64, num_attention_heads=8, num_key_value_heads=4, intermediate_size=176,
+               vocab_size=128, num_hidden_layers=2, max_position_embeddings=32, rms_norm_eps=1e-5,
+               rope_theta=10000.0, parallel_block=False)
+    cfg.update(kw)
+    return types.SimpleNamespace(**cfg)
+
+
+def shard_like(full: torch.Tensor, local_shape, rank: int, world: int) -> torch.Tensor:
+    """Slice ``full`` along the (single) dimension in which the local tensor is smaller."""
+    if tuple(full.shape) == tuple(local_shape):
+        return full
+    for d, (f, l) in enumerate(zip(full.shape, local_shape)):
+        if f != l:
+            assert f == l * world
+            return full.narrow(d, rank * l, l)
+    raise AssertionError
+
+
+def _tp_worker(rank, world, mode, parallel_block):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.engine import loss_fn
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.parallel.tensor_parallel import apply_tensor_parallel
+
+    pgm.setup_process_group_manager(tp_size=world, cp_size=1, pp_size=1, dp_size=1)
+    cfg = tiny_config(parallel_block=parallel_block)
+    torch.manual_seed(7)
+    ref = Llama(cfg)
+    ref_sd = {k: v.clone() for k, v in ref.state_dict().items()}
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, cfg.vocab_size, (2, 16), generator=g)
+    tgt = torch.randint(0, cfg.vocab_size, (2, 16), generator=g)
+    ref_loss = torch.nn.functional.cross_entropy(ref(ids).view(-1, cfg.vocab_size), tgt.view(-1))
+    ref_loss.backward()
+    ref_grads = {n: p.grad.clone() for n, p in ref.named_parameters()}
+
+    flags = dict(plain={}, async_tp=dict(async_tp=True), sp=dict(sequence_parallel=True),
+                 vocab_ce=dict(vocab_parallel_ce=True), sp_vocab_ce=dict(sequence_parallel=True, vocab_parallel_ce=True),
+                 sp_overlap=dict(sequence_parallel=True, overlap_comm=True))[mode]
+    torch.manual_seed(7)
+    model = Llama(cfg)
+    apply_tensor_parallel(model, **flags)
+    sd = model.state_dict()
+    model.load_state_dict({k: shard_like(ref_sd[k], v.shape, rank, world).clone() for k, v in sd.items()})
+    logits = model(ids)
+    loss = loss_fn(model, logits, tgt)
+    loss.backward()
+    if flags.get("sequence_parallel"):
+        for p in model.parameters():
+            if getattr(p, "sequence_parallel_grad", False):
+                dist.all_reduce(p.grad, group=pgm.get_pgm().tp_group)
+    assert abs(loss.item() - ref_loss.item()) < 2e-4, (mode, loss.item(), ref_loss.item())
+    for n, p in model.named_parameters():
+        want = shard_like(ref_grads[n], p.shape, rank, world)
+        err = (p.grad - want).abs().max().item()
+        assert err < 2e-4, (mode, n, err)
+
+
+@pytest.mark.parametrize("mode", ["plain", "async_tp", "sp", "vocab_ce", "sp_vocab_ce", "sp_overlap"])
+def test_tp2_matches_single_process(mode):
+    run_distributed(_tp_worker, 2, mode, False)
+
+
+@pytest.mark.parametrize("mode", ["plain", "sp", "sp_overlap", "sp_vocab_ce"])
+def test_tp2_parallel_block(mode):
+    run_distributed(_tp_worker, 2, mode, True)
+
+
+def test_tp4_sequence_parallel():
+    run_distributed(_tp_worker, 4, "sp_vocab_ce", False)
