@@ -116,6 +116,8 @@ class _LinearFn(torch.autograd.Function):
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if use_kernels(x, w) and _gemm_ok(x.shape[-1], w.shape[0]):
         return _LinearFn.apply(x, w)
+    if _ZB_MODE and torch.is_grad_enabled():
+        return _LinearRefFn.apply(x, w)
     return linear_ref(x, w)
 
 
@@ -209,4 +211,111 @@ def multi_linear_cat(x: torch.Tensor, mods) -> torch.Tensor:
     ws = WeightSet.of(mods)
     if use_kernels(x, ws.params[0]) and _gemm_ok(x.shape[-1], *ws.splits):
         return _MultiLinearFn.apply(x, ws, *ws.params)
-    return torch.cat([linear_ref(x, w) for w in ws.params], dim=-1)
+    return torch.cat([linear(x, w) for w in ws.params], dim=-1)
+
+
+# ---------------------------------------------------------------------------------------------
+# zero-bubble support: weight gradients split off from the backward pass
+# ---------------------------------------------------------------------------------------------
+_ZB_MODE = False          # linears use the deferrable autograd functions also on the torch path
+_DEFER_QUEUE = None       # list collecting weight-gradient closures while a "B" action runs
+
+
+def set_zero_bubble(enabled: bool) -> None:
+    """While enabled, every bias-free linear routes its backward through code that can postpone
+    the weight gradient (the role of the globally patched ``nn.Linear.forward`` and
+    ``_DeferredLinear`` in picotron/pipeline_parallel/pipeline_parallel.py:21-54)."""
+    global _ZB_MODE
+    _ZB_MODE = enabled
+
+
+class defer_wgrad:
+    """Context manager: weight gradients of linears whose backward runs inside are not computed
+    but queued; ``run_deferred(queue)`` computes them later (the W action of a zero-bubble
+    schedule)."""
+
+    def __enter__(self):
+        global _DEFER_QUEUE
+        self.prev = _DEFER_QUEUE
+        self.queue = []
+        _DEFER_QUEUE = self.queue
+        return self.queue
+
+    def __exit__(self, *exc):
+        global _DEFER_QUEUE
+        _DEFER_QUEUE = self.prev
+        return False
+
+
+def run_deferred(queue) -> None:
+    for fn in queue:
+        fn()
+    queue.clear()
+
+
+def _accumulate_grad(p: torch.Tensor, g: torch.Tensor) -> None:
+    main_grad = getattr(p, "main_grad", None)
+    if main_grad is not None and p.is_cuda:
+        main_grad.add_(g)
+    elif p.grad is None:
+        p.grad = g.to(p.dtype)
+    else:
+        p.grad = p.grad + g.to(p.dtype)
+
+
+class _LinearRefFn(torch.autograd.Function):
+    """Torch-path linear (any device / dtype) with a deferrable weight gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return F.linear(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx = dy.matmul(w) if ctx.needs_input_grad[0] else None
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        if _DEFER_QUEUE is not None:
+            _DEFER_QUEUE.append(lambda: _accumulate_grad(w, dy2.t().matmul(x2)))
+            return dx, None
+        return dx, dy2.t().matmul(x2)
+
+
+_plain_wgrad_into = wgrad_into
+_plain_backward_all = backward_all
+
+
+def wgrad_into(weight, dy2, x2):  # noqa: F811  (deferral-aware wrapper)
+    if _DEFER_QUEUE is not None:
+        def later():
+            g = _plain_wgrad_into(weight, dy2, x2)
+            if g is not None:
+                _accumulate_grad(weight, g)
+        _DEFER_QUEUE.append(later)
+        return None
+    return _plain_wgrad_into(weight, dy2, x2)
+
+
+def backward_all(dy2, x2, ws, need_dx=True):  # noqa: F811  (deferral-aware wrapper)
+    if _DEFER_QUEUE is None:
+        return _plain_backward_all(dy2, x2, ws, need_dx)
+    dx = None
+    if need_dx:
+        if ws.fused_weight is not None:
+            dx = gemm_nn(dy2, ws.fused_weight)
+        else:
+            col = 0
+            for w in ws.params:
+                part = gemm_nn(dy2[:, col:col + w.shape[0]], w)
+                col += w.shape[0]
+                dx = part if dx is None else dx.add_(part)
+
+    def later():
+        _, grads = _plain_backward_all(dy2, x2, ws, need_dx=False)
+        for p, g in zip(ws.params, grads):
+            if g is not None:
+                _accumulate_grad(p, g)
+    _DEFER_QUEUE.append(later)
+    return dx, [None] * len(ws.params)

@@ -56,6 +56,15 @@ class _DataParallelBase(nn.Module):
             self.require_backward_grad_sync = prev
 
 
+    def sync_all(self):
+        """Average every gradient over the group now. Used when gradients were produced outside
+        the hooks' view (deferred weight gradients of the zero-bubble schedules)."""
+        for p in self.module.parameters():
+            if p.requires_grad and p.grad is not None and self.world_size > 1:
+                dist.all_reduce(p.grad, op=dist.ReduceOp.SUM, group=self.group)
+                p.grad /= self.world_size
+
+
 class DataParallelNaive(_DataParallelBase):
     """All-reduce every gradient as soon as it has been accumulated, then divide by the group size."""
 
@@ -111,3 +120,15 @@ class DataParallelBucket(_DataParallelBase):
 
     def reset(self):
         self.bucket_manager.reset()
+
+    def sync_all(self):
+        bm = self.bucket_manager
+        for p in bm.params:
+            if p.grad is not None:      # late gradients that bypassed the accumulation hook
+                p.main_grad.add_(p.grad.data)
+                p.grad = None
+        if self.world_size > 1:
+            dist.all_reduce(bm.grad_data, group=self.group)
+            bm.grad_data /= self.world_size
+        for p in bm.params:
+            p.grad = p.main_grad.to(p.dtype)

@@ -67,6 +67,15 @@ class DataParallelZero(nn.Module):
     def reset(self):
         pass
 
+    def sync_all(self):
+        for p in self.module.parameters():
+            if p.requires_grad and p.grad is not None:
+                if self.world_size > 1:
+                    dist.all_reduce(p.grad, op=dist.ReduceOp.SUM, group=self.group)
+                    p.grad /= self.world_size
+                if self.stage >= 2 and not self.owns(p):
+                    p.grad = None
+
     # --- gradients ---------------------------------------------------------------------------
     def _grad_hook(self, p):
         if self.stage == 3:

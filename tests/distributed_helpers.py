@@ -29,7 +29,7 @@ def _worker(rank, world_size, port, fn, args, errors):
             dist.destroy_process_group()
 
 
-def run_distributed(fn, world_size: int, *args, timeout: float = 240.0):
+def run_distributed(fn, world_size: int, *args, timeout: float = 120.0):
     """Run fn(rank, world_size, *args) on ``world_size`` gloo ranks; raise if any rank fails."""
     ctx = mp.get_context("spawn")
     errors = ctx.Queue()
