@@ -1,0 +1,173 @@
+// Device code of the RMSNorm kernels, shared by the launchers in norm.cu and by the
+// allocation-free entry point in norm_noalloc.cu.
+#pragma once
+#include <cuda_bf16.h>
+
+namespace pico {
+
+constexpr int kNormThreads = 256;
+constexpr int kMaxVec = 8;  // vectors of 8 bf16 per thread kept in registers: H <= 16384
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < kNormThreads / 32) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int rows, int H,
+                   float eps) {
+  __shared__ float red[kNormThreads / 32];
+  const int nvec = H / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + (size_t)row * H) : nullptr;
+    float vals[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        unpack8(xr[v], vals[i]);
+        if (rr) {
+          float r[8];
+          unpack8(rr[v], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
+          // the summed stream is rounded to bf16 before it is normalised, as an unfused
+          // add followed by a norm would do
+          uint4 hv = pack8(vals[i]);
+          unpack8(hv, vals[i]);
+          if (h_out) reinterpret_cast<uint4*>(h_out + (size_t)row * H)[v] = hv;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float wv[8], o[8];
+        unpack8(reinterpret_cast<const uint4*>(w)[v], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wv[j];
+        reinterpret_cast<uint4*>(y + (size_t)row * H)[v] = pack8(o);
+      }
+    }
+  }
+}
+
+// dw partials: dw_partial[blockIdx.x][H] fp32
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dh,
+                   float* __restrict__ dw_partial, int rows, int H) {
+  __shared__ float red[kNormThreads / 32];
+  const int nvec = H / 8;
+  float dw_acc[NV][8];
+  float wv[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[i][j] = 0.f;
+    if (v < nvec) unpack8(reinterpret_cast<const uint4*>(w)[v], wv[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rstd = rstd_in[row];
+    float g[NV][8], hv[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float d[8];
+        unpack8(reinterpret_cast<const uint4*>(dy + (size_t)row * H)[v], d);
+        unpack8(reinterpret_cast<const uint4*>(h + (size_t)row * H)[v], hv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          g[i][j] = d[j] * wv[i][j];
+          dot += g[i][j] * hv[i][j];
+          dw_acc[i][j] += d[j] * hv[i][j] * rstd;
+        }
+      }
+    }
+    dot = block_sum(dot, red);
+    const float c = dot / (float)H * rstd * rstd * rstd;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * g[i][j] - hv[i][j] * c;
+        if (dres) {
+          float r[8];
+          unpack8(reinterpret_cast<const uint4*>(dres + (size_t)row * H)[v], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        reinterpret_cast<uint4*>(dh + (size_t)row * H)[v] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      float4* out = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * H + (size_t)v * 8);
+      out[0] = make_float4(dw_acc[i][0], dw_acc[i][1], dw_acc[i][2], dw_acc[i][3]);
+      out[1] = make_float4(dw_acc[i][4], dw_acc[i][5], dw_acc[i][6], dw_acc[i][7]);
+    }
+  }
+}
+
+// dw[H] (=|+=) sum_p partial[p][H]; fixed summation order (deterministic)
+static __global__ void colsum_kernel(const float* __restrict__ partial, int nparts, int H,
+                              float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16,
+                              int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * H + c];
+  if (out_f32) out_f32[c] = accumulate ? out_f32[c] + s : s;
+  if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + s : s);
+}
+
+}  // namespace pico
