@@ -84,3 +84,38 @@ def attention(q, k, v, causal: bool = True, sm_scale: float | None = None) -> to
                                            is_causal=causal, scale=sm_scale, enable_gqa=(H != kvh))
         return o.transpose(1, 2)
     return attention_ref(q, k, v, causal, sm_scale)
+
+
+def attention_block_backward(dout, q, k, v, out, lse, causal: bool, sm_scale: float | None = None,
+                             q_offset: int = 0, k_offset: int = 0):
+    """Gradients of one key block's contribution given the *final* (merged) ``out`` and ``lse``.
+
+    With P = exp(S - lse) the probabilities under the global normaliser, dV = P^T dO,
+    dS = P * (dO V^T - rowsum(dO * O)), dQ = dS K * scale, dK = dS^T Q * scale
+    (picotron/context_parallel/context_parallel.py:262-290). Returns fp32 (dq, dk, dv) with dk/dv
+    in the un-expanded K/V head layout.
+    """
+    b, sq, H, d = q.shape
+    sk, kvh = k.shape[1], k.shape[2]
+    scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(d)
+    kf, vf = _expand_kv(k, H).float(), _expand_kv(v, H).float()
+    qf, dof = q.float(), dout.float()
+    scores = torch.einsum("bqhd,bkhd->bhqk", qf, kf) * scale
+    if causal:
+        qi = torch.arange(sq, device=q.device)[:, None] + q_offset
+        ki = torch.arange(sk, device=q.device)[None, :] + k_offset
+        scores = scores.masked_fill(ki > qi, float("-inf"))
+    safe_lse = torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)
+    p = torch.exp(scores - safe_lse[..., None])
+    p = torch.where(torch.isinf(lse)[..., None], torch.zeros_like(p), p)
+    dv = torch.einsum("bhqk,bqhd->bkhd", p, dof)
+    dp = torch.einsum("bqhd,bkhd->bhqk", dof, vf)
+    delta = (dof * out.float()).sum(-1).transpose(1, 2)  # [b, H, sq]
+    ds = p * (dp - delta[..., None])
+    dq = torch.einsum("bhqk,bkhd->bqhd", ds, kf) * scale
+    dk = torch.einsum("bhqk,bqhd->bkhd", ds, qf) * scale
+    if kvh != H:
+        rep = H // kvh
+        dk = dk.view(b, sk, kvh, rep, d).sum(3)
+        dv = dv.view(b, sk, kvh, rep, d).sum(3)
+    return dq, dk, dv

@@ -1,0 +1,68 @@
+"""DeepSpeed-Ulysses context parallelism: trade the sequence shard for a head shard with an
+all-to-all, run ordinary attention over the full sequence on ``heads / cp`` heads, and trade
+back (picotron/context_parallel/ulysses.py:39-111).
+
+The all-to-all uses the single-buffer collective, which also exists on gloo, and K/V are sent
+with their own head count whenever it divides by the CP size (the reference always sends the
+GQA-expanded heads).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import process_group_manager as pgm
+from ..ops import attention as attn_ops
+from .dist_utils import group_size
+
+
+def _all_to_all(x: torch.Tensor, scatter_dim: int, gather_dim: int, group) -> torch.Tensor:
+    """Split ``x`` along ``scatter_dim`` into one piece per rank, exchange, concatenate the
+    received pieces along ``gather_dim``."""
+    n = group_size(group)
+    if n == 1:
+        return x
+    assert x.shape[scatter_dim] % n == 0
+    # bring the scatter dim to the front as [n, chunk, ...] so the exchange is one flat buffer
+    parts = x.reshape(*x.shape[:scatter_dim], n, x.shape[scatter_dim] // n, *x.shape[scatter_dim + 1:])
+    send = parts.movedim(scatter_dim, 0).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv.view(n, -1), send.view(n, -1), group=group)
+    # recv[j] is rank j's piece: concatenate along gather_dim (positions shifted by the moved dim)
+    pieces = recv.unbind(0)
+    return torch.cat(pieces, dim=gather_dim)
+
+
+class _SeqAllToAll(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scatter_dim, gather_dim, group):
+        ctx.scatter_dim, ctx.gather_dim, ctx.group = scatter_dim, gather_dim, group
+        return _all_to_all(x, scatter_dim, gather_dim, group)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return _all_to_all(grad.contiguous(), ctx.gather_dim, ctx.scatter_dim, ctx.group), None, None, None
+
+
+def ulysses_attention_bshd(q, k, v, causal: bool = True, sm_scale=None, group=None):
+    """q: [b, s/cp, H, d]; k, v: [b, s/cp, Hkv, d] -> [b, s/cp, H, d]."""
+    group = group if group is not None else pgm.get_pgm().cp_group
+    n = group_size(group)
+    if n == 1:
+        return attn_ops.attention(q, k, v, causal, sm_scale)
+    H, kvh = q.shape[2], k.shape[2]
+    assert H % n == 0, f"Ulysses needs the local head count ({H}) divisible by the CP size ({n})"
+    if kvh % n != 0:
+        k, v = attn_ops._expand_kv(k, H), attn_ops._expand_kv(v, H)
+    # [b, s/cp, H, d] -> scatter heads (dim 2), gather sequence (dim 1) -> [b, s, H/cp, d]
+    qg = _SeqAllToAll.apply(q, 2, 1, group)
+    kg = _SeqAllToAll.apply(k, 2, 1, group)
+    vg = _SeqAllToAll.apply(v, 2, 1, group)
+    out = attn_ops.attention(qg, kg, vg, causal, sm_scale)
+    return _SeqAllToAll.apply(out, 1, 2, group)
+
+
+def ulysses_attention(q, k, v, is_causal, group=None):
+    """Reference-layout entry point on ``[b, heads, s_local, d]`` tensors."""
+    out = ulysses_attention_bshd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal, None, group)
+    return out.transpose(1, 2)
