@@ -1,0 +1,71 @@
+"""Fixed-capacity expert dispatch: every (rank, expert) pair handles exactly ``C`` rows per
+round, so every buffer of the MoE layer has a static shape whatever the router does
+(GShard / Switch style; behaviour of picotron/expert_parallel/capacity_moe.py:33-173).
+
+* ``C = max(1, int(factor * T * k / E + 0.999))``
+* a routed row's slot is its position in its expert's queue (row order); rows with slot >= C
+  are dropped (``dropless=False``) or handled in later rounds (``dropless=True``): the number of
+  rounds is ``ceil(max_count / C)`` capped by ``max_rounds`` and maximised over the EP group so all
+  ranks issue the same collectives, empty rounds included
+* the exchange is an equal-split all-to-all of ``L*C`` rows per peer; received rows are viewed
+  ``[L, ep*C, d]`` and each expert runs on its fixed batch (padding rows are zero and a bias-free
+  SwiGLU maps zero to zero)
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import ep_communications as epc
+
+
+def compute_capacity(num_tokens: int, top_k: int, num_experts: int, factor: float) -> int:
+    return max(1, int(factor * num_tokens * top_k / num_experts + 0.999))
+
+
+def slot_assignment(expert_idx: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """slot[i] = number of earlier rows routed to the same expert as row i."""
+    order = torch.argsort(expert_idx, stable=True)
+    counts = torch.bincount(expert_idx, minlength=num_experts)
+    starts = torch.cumsum(counts, 0) - counts
+    sorted_expert = expert_idx[order]
+    pos = torch.arange(order.numel(), device=expert_idx.device) - starts[sorted_expert]
+    slot = torch.empty_like(pos)
+    slot[order] = pos
+    return slot
+
+
+def capacity_moe(layer, routed, expert_idx, weights, token_idx, num_tokens: int, capacity: int, dropless: bool,
+                 max_rounds: int):
+    """Returns (y [T, d] gate-weighted and summed per token, fraction of routed rows dropped)."""
+    E, L, ep, d = layer.num_experts, layer.num_local_experts, layer.ep_world_size, routed.shape[1]
+    C = capacity
+    slot = slot_assignment(expert_idx, E)
+    rounds = 1
+    if dropless:
+        max_count = torch.bincount(expert_idx, minlength=E).max()
+        need = torch.clamp((max_count + C - 1) // C, min=1, max=max_rounds).to(torch.int64)
+        if ep > 1:
+            dist.all_reduce(need, op=dist.ReduceOp.MAX, group=layer.ep_group)
+        rounds = int(need.item())
+    y = torch.zeros((num_tokens, d), device=routed.device, dtype=routed.dtype)
+    equal = [L * C] * ep
+    for r in range(rounds):
+        sel = torch.nonzero((slot >= r * C) & (slot < (r + 1) * C)).squeeze(1)
+        idx = expert_idx[sel] * C + (slot[sel] - r * C)
+        buf = torch.zeros((E * C, d), device=routed.device, dtype=routed.dtype).index_add(0, idx, routed[sel])
+        if ep > 1:
+            if layer.ep_fp8_dispatch:
+                recv = epc.all_to_all_fp8(buf, equal, equal, layer.ep_group, layer.ep_fp8_granularity)
+            else:
+                recv = epc.all_to_all(buf, equal, equal, layer.ep_group)
+        else:
+            recv = buf
+        x = recv.view(ep, L, C, d).transpose(0, 1).reshape(L, ep * C, d)
+        out = torch.stack([layer.local_experts[l](x[l]) for l in range(L)])
+        back = out.view(L, ep, C, d).transpose(0, 1).reshape(ep * L * C, d)
+        if ep > 1:
+            back = epc.all_to_all(back, equal, equal, layer.ep_group)
+        y = y.index_add(0, token_idx[sel], back[idx] * weights[sel].unsqueeze(-1))
+    dropped = (slot >= rounds * C).float().mean()
+    return y, dropped
