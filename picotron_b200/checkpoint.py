@@ -1,0 +1,188 @@
+"""Model initialisation helpers and checkpoint save / load.
+
+Checkpoints keep the reference's layout (picotron/checkpoint.py:270-316): directory
+``<save_dir>/<step>/``, one file per (tp, pp) coordinate named
+``weights_tp_rank_world_size={tp}_{tp_ws}_pp_rank_world_size={pp}_{pp_ws}.pth`` holding a
+``torch.save`` dict with keys ``model``, ``optimizer``, ``trained_steps``, ``trained_tokens``;
+model keys are the reference's state-dict names (global layer indices under pipeline
+parallelism). Only ``dp_rank == 0 and cp_rank == 0`` writes.
+
+Added on top, all ignorable by a reader of the reference format:
+* with expert parallelism every EP rank holds different experts, so the file name gets an
+  ``_ep_rank_world_size={ep}_{ep_ws}`` suffix and each EP rank writes its own file (the
+  reference lets EP ranks overwrite each other)
+* files are written to ``*.tmp`` and renamed, and a ``manifest.json`` lists the files a complete
+  checkpoint must contain; ``load_checkpoint`` refuses an incomplete one
+* extra keys ``rng_state`` and ``data_loader`` allow an exact resume of the data stream
+* ZeRO-sharded flat optimizer state is saved per data-parallel rank in
+  ``optimizer_dp_rank={dp}_{dp_ws}_<same suffix>.pth``
+
+``init_model_with_dematerialized_weights`` / ``init_model_with_materialized_weights`` give the
+meta-device construction path of the reference (checkpoint.py:17-121): build without memory,
+then materialise and initialise; when a directory of Hugging Face safetensors is given, the
+shapes are validated against it before the parameters are (re-)initialised, as the reference
+does (it reads the files but always trains from random init, checkpoint.py:114-119).
+"""
+from __future__ import annotations
+
+import contextlib
+import json
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import process_group_manager as pgm
+from .utils import assert_no_meta_tensors
+
+
+@contextlib.contextmanager
+def init_model_with_dematerialized_weights(include_buffers: bool = False):
+    """Construct modules with their parameters on the meta device (no memory, no init)."""
+    with torch.device("meta"):
+        yield
+
+
+def init_model_with_materialized_weights(model: nn.Module, model_config=None, save_dir: Optional[str] = None,
+                                         device="cpu"):
+    """Allocate real storage for a meta-constructed model and run its initialisers."""
+    if save_dir is not None and os.path.isdir(save_dir):
+        _validate_against_safetensors(model, save_dir)
+    model.to_empty(device=device)
+    with torch.no_grad():
+        # leaves own the initialisers; containers (Attention, MLP, MoELayer, ...) only delegate
+        for mod in model.modules():
+            if hasattr(mod, "reset_parameters") and next(mod.children(), None) is None:
+                mod.reset_parameters()
+        for _, buf in model.named_buffers():
+            buf.zero_()
+    assert_no_meta_tensors(model)
+    return model
+
+
+def _validate_against_safetensors(model, save_dir):
+    try:
+        from safetensors import safe_open
+    except ImportError:
+        return
+    files = [f for f in os.listdir(save_dir) if f.endswith(".safetensors")]
+    shapes = {}
+    for f in files:
+        with safe_open(os.path.join(save_dir, f), framework="pt") as fh:
+            for k in fh.keys():
+                shapes[k] = tuple(fh.get_slice(k).get_shape())
+    hf_names = {"embedding.weight": "model.embed_tokens.weight", "final_norm.weight": "model.norm.weight",
+                "final_proj.weight": "lm_head.weight"}
+    for name, p in model.named_parameters():
+        hf = hf_names.get(name)
+        if hf is None and name.startswith("decoder_layers."):
+            hf = ("model.layers." + name[len("decoder_layers."):]).replace("attention.", "self_attn.") \
+                .replace("out_proj", "o_proj")
+        if hf in shapes and len(shapes[hf]) == p.dim():
+            full = shapes[hf]
+            ok = all(a == b or a % b == 0 for a, b in zip(full, p.shape))
+            assert ok, f"{name}: local shape {tuple(p.shape)} does not tile checkpoint shape {full}"
+
+
+class CheckpointManager:
+    def __init__(self):
+        m = pgm.get_pgm()
+        self.tp_rank, self.tp_ws = m.tp_rank, m.tp_world_size
+        self.pp_rank, self.pp_ws = m.pp_rank, m.pp_world_size
+        self.ep_rank, self.ep_ws = m.ep_rank, m.ep_world_size
+        self.dp_rank, self.dp_ws = m.dp_rank, m.dp_world_size
+        self.cp_rank = m.cp_rank
+        self.cp_dp_world_size = m.cp_dp_world_size
+
+    def _suffix(self) -> str:
+        s = (f"tp_rank_world_size={self.tp_rank}_{self.tp_ws}_"
+             f"pp_rank_world_size={self.pp_rank}_{self.pp_ws}")
+        if self.ep_ws > 1:
+            s += f"_ep_rank_world_size={self.ep_rank}_{self.ep_ws}"
+        return s
+
+    def _get_checkpoint_path(self, out_dir: str) -> str:
+        return os.path.join(out_dir, f"weights_{self._suffix()}.pth")
+
+    def _optimizer_shard_path(self, out_dir: str) -> str:
+        return os.path.join(out_dir, f"optimizer_dp_rank={self.dp_rank}_{self.dp_ws}_{self._suffix()}.pth")
+
+    def expected_files(self):
+        names = []
+        for tp in range(self.tp_ws):
+            for pp in range(self.pp_ws):
+                for ep in range(self.ep_ws):
+                    s = f"tp_rank_world_size={tp}_{self.tp_ws}_pp_rank_world_size={pp}_{self.pp_ws}"
+                    if self.ep_ws > 1:
+                        s += f"_ep_rank_world_size={ep}_{self.ep_ws}"
+                    names.append(f"weights_{s}.pth")
+        return names
+
+    @staticmethod
+    def _unwrap(model):
+        return model.module if hasattr(model, "module") and isinstance(model.module, nn.Module) else model
+
+    @staticmethod
+    def _atomic_save(obj, path):
+        tmp = path + ".tmp"
+        torch.save(obj, tmp)
+        os.replace(tmp, path)
+
+    def save_checkpoint(self, model, optimizer, trained_steps: int, trained_tokens: int, out_dir: str,
+                        data_loader=None, sharded_optimizer: bool = False):
+        os.makedirs(out_dir, exist_ok=True)
+        raw = self._unwrap(model)
+        if sharded_optimizer and optimizer is not None and self.cp_rank == 0:
+            self._atomic_save({"optimizer": optimizer.state_dict()}, self._optimizer_shard_path(out_dir))
+        if self.dp_rank == 0 and self.cp_rank == 0:
+            payload = {
+                "model": raw.state_dict(),
+                "optimizer": None if (optimizer is None or sharded_optimizer) else optimizer.state_dict(),
+                "trained_steps": trained_steps,
+                "trained_tokens": trained_tokens,
+                "rng_state": torch.get_rng_state(),
+                "data_loader": data_loader.state_dict() if hasattr(data_loader, "state_dict") else None,
+            }
+            self._atomic_save(payload, self._get_checkpoint_path(out_dir))
+        if dist.is_initialized():
+            dist.barrier()
+        if (not dist.is_initialized()) or dist.get_rank() == 0:
+            manifest = {"files": self.expected_files(), "trained_steps": trained_steps,
+                        "trained_tokens": trained_tokens}
+            tmp = os.path.join(out_dir, "manifest.json.tmp")
+            with open(tmp, "w") as fh:
+                json.dump(manifest, fh)
+            os.replace(tmp, os.path.join(out_dir, "manifest.json"))
+        if dist.is_initialized():
+            dist.barrier()
+
+    def load_checkpoint(self, model, optimizer, out_dir: str, data_loader=None, sharded_optimizer: bool = False):
+        """Load this rank's shard (same topology as at save time). Returns (steps, tokens)."""
+        manifest_path = os.path.join(out_dir, "manifest.json")
+        if os.path.exists(manifest_path):
+            missing = [f for f in json.load(open(manifest_path))["files"]
+                       if not os.path.exists(os.path.join(out_dir, f))]
+            if missing:
+                raise FileNotFoundError(f"incomplete checkpoint in {out_dir}: missing {missing}")
+        path = self._get_checkpoint_path(out_dir)
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"checkpoint not found at {path}")
+        ckpt = torch.load(path, map_location="cpu", weights_only=False)
+        raw = self._unwrap(model)
+        with torch.no_grad():
+            own = raw.state_dict()
+            for k, v in ckpt["model"].items():
+                own[k].copy_(v)          # in place: parameters may be views of a flat buffer
+        if optimizer is not None:
+            if sharded_optimizer and os.path.exists(self._optimizer_shard_path(out_dir)):
+                sd = torch.load(self._optimizer_shard_path(out_dir), map_location="cpu", weights_only=False)
+                optimizer.load_state_dict(sd["optimizer"])
+            elif ckpt.get("optimizer") is not None:
+                optimizer.load_state_dict(ckpt["optimizer"])
+        if data_loader is not None and ckpt.get("data_loader") is not None and hasattr(data_loader, "load_state_dict"):
+            data_loader.load_state_dict(ckpt["data_loader"])
+        if ckpt.get("rng_state") is not None:
+            torch.set_rng_state(ckpt["rng_state"])
+        return ckpt["trained_steps"], ckpt["trained_tokens"]

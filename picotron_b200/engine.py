@@ -159,6 +159,12 @@ class TrainEngine:
         if m.cp_world_size > 1:
             from .parallel.context_parallel import apply_context_parallel
             apply_context_parallel(model, attention=d["cp_attention"])
+        # (re-)initialise in canonical module order from the configured seed: tensor-parallel
+        # layers draw the full master weight and keep their slice, so a TP run starts from
+        # exactly the weights of the single-device run (reference: checkpoint.py:114-119)
+        torch.manual_seed(self.cfg["training"]["seed"])
+        with torch.no_grad():
+            model.reset_parameters()
         model.to(self.dtype).to(self.device)
         self.model = model
         self.flat = self.device.type == "cuda" and self.dtype == torch.bfloat16
@@ -241,6 +247,25 @@ class TrainEngine:
         self.trained_steps += 1
         self.trained_tokens += self.tokens_per_step
         return loss
+
+    @property
+    def optimizer_is_sharded(self) -> bool:
+        """True when each data-parallel rank holds a different slice of the optimizer state."""
+        if self.flat:
+            return self.optimizer.zero_stage >= 1 and self.optimizer.dp_size > 1
+        return hasattr(self.optimizer, "dp")
+
+    def average_loss(self, loss) -> float:
+        """Mean of the step loss over the ranks that computed it on different data (CP x DP, and
+        EP when it acts as data parallelism); other ranks receive the value of the last pipeline
+        stage's replica group. One host read."""
+        t = loss.detach().float().reshape(1).clone() if torch.is_tensor(loss) else \
+            torch.tensor([float(loss)], device=self.device)
+        n = self._grad_group_size()
+        if n > 1 and self.pgm.pp_is_last_stage:
+            dist.all_reduce(t, group=self._grad_group())
+            t /= n
+        return float(t.item())
 
     def _aux_loss(self):
         if getattr(self.model_config, "num_experts", 1) > 1:

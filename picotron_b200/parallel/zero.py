@@ -97,12 +97,28 @@ class DataParallelZero(nn.Module):
             self._full_nbytes[p] = p.data.untyped_storage().nbytes()
             if not self.owns(p):
                 p.data.untyped_storage().resize_(0)
-        for mod in self.module.modules():
-            own = [p for p in mod.parameters(recurse=False) if p.requires_grad]
+        for unit in self._units(self.module):
+            own = [p for p in unit.parameters() if p.requires_grad]
             if not own:
                 continue
-            mod.register_forward_pre_hook(lambda m, a, ps=own: self._gather(ps))
-            mod.register_forward_hook(lambda m, a, out, ps=own: self._after_forward(ps, out))
+            unit.register_forward_pre_hook(lambda m, a, ps=own: self._gather(ps))
+            unit.register_forward_hook(lambda m, a, out, ps=own: self._after_forward(ps, out))
+
+    @staticmethod
+    def _units(root):
+        """Gather/free granularity: the children of the root (the elements of list/dict containers
+        individually) — for a Llama: embedding, each decoder layer, final norm, lm head. A unit's
+        parameters are materialised together because inner modules may read each other's weights
+        without going through ``__call__`` (fused q/k/v and gate/up projections)."""
+        units = []
+        for child in root.children():
+            if isinstance(child, (nn.ModuleList, nn.ModuleDict, nn.Sequential)):
+                units.extend(child.children())
+            else:
+                units.append(child)
+        if any(True for _ in root.parameters(recurse=False)) or not units:
+            units = [root]
+        return units
 
     def _gather(self, ps):
         for p in ps:
