@@ -5,9 +5,13 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstring>
+
 #include "common/host.h"
 #include "elementwise/elementwise.h"
+#include "fused/tp_comm.h"
 #include "gemm/gemm.h"
+#include "runtime/symm.h"
 
 namespace {
 
@@ -150,6 +154,113 @@ void fill_u32(at::Tensor& dst, int64_t value, int64_t n_words) {
   check(pico_fill_u32(dst.data_ptr(), (uint32_t)value, n_words, stream_of(dst)), "fill");
 }
 
+// ---------------------------------------------------------------------------------------------
+// symmetric memory + fused tensor-parallel communication
+// ---------------------------------------------------------------------------------------------
+PicoPeerTable table_of(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(ptrs.size() <= PICO_MAX_PEERS, "at most ", PICO_MAX_PEERS, " peers");
+  PicoPeerTable t;
+  for (int i = 0; i < PICO_MAX_PEERS; ++i)
+    t.ptr[i] = i < (int)ptrs.size() ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return t;
+}
+
+std::pair<int64_t, py::bytes> symm_alloc(int64_t nbytes) {
+  void* p = nullptr;
+  unsigned char h[64];
+  check(pico_symm_alloc((size_t)nbytes, &p, h), "symm_alloc");
+  return {reinterpret_cast<int64_t>(p), py::bytes(reinterpret_cast<const char*>(h), 64)};
+}
+
+int64_t symm_open(const std::string& handle) {
+  TORCH_CHECK(handle.size() == 64, "IPC handle must be 64 bytes");
+  void* p = nullptr;
+  check(pico_symm_open(reinterpret_cast<const unsigned char*>(handle.data()), &p), "symm_open");
+  return reinterpret_cast<int64_t>(p);
+}
+
+void symm_close(int64_t ptr) { pico_symm_close(reinterpret_cast<void*>(ptr)); }
+void symm_free(int64_t ptr) { pico_symm_free(reinterpret_cast<void*>(ptr)); }
+
+// A uint8 tensor over device memory owned elsewhere (no deleter).
+at::Tensor tensor_from_ptr(int64_t ptr, int64_t nbytes, int64_t device_index) {
+  auto opts = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, (c10::DeviceIndex)device_index);
+  return at::from_blob(reinterpret_cast<void*>(ptr), {nbytes}, opts);
+}
+
+void signal_peers(const std::vector<int64_t>& flag_ptrs, int64_t world, int64_t my_rank, int64_t slot,
+                  int64_t epoch) {
+  check(pico_signal_peers(table_of(flag_ptrs), (int)world, (int)my_rank, (int)slot, (uint32_t)epoch,
+                          at::cuda::getCurrentCUDAStream().stream()),
+        "signal_peers");
+}
+
+void wait_flags(int64_t local_flags, int64_t world, int64_t slot, int64_t epoch, int64_t timeout_ms) {
+  check(pico_wait_flags(reinterpret_cast<const uint32_t*>(local_flags), (int)world, (int)slot,
+                        (uint32_t)epoch, (uint32_t)timeout_ms, at::cuda::getCurrentCUDAStream().stream()),
+        "wait_flags");
+}
+
+void push_rows(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs,
+               const std::vector<int64_t>& flag_ptrs, int64_t world, int64_t my_rank, int64_t rows,
+               int64_t cols, int64_t slot, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kBFloat16, "push_rows: contiguous bf16");
+  check(pico_push_rows(src.data_ptr(), table_of(dst_ptrs), table_of(flag_ptrs), (int)world, (int)my_rank,
+                       (int)rows, (int)cols, (int)slot, (uint32_t)epoch, stream_of(src)),
+        "push_rows");
+}
+
+void rmsnorm_fwd_push(const at::Tensor& x, const c10::optional<at::Tensor>& residual, const at::Tensor& w,
+                      const c10::optional<at::Tensor>& y_local, const c10::optional<at::Tensor>& h_out,
+                      const c10::optional<at::Tensor>& rstd, const std::vector<int64_t>& dst_ptrs,
+                      const std::vector<int64_t>& flag_ptrs, int64_t world, int64_t my_rank, int64_t rows,
+                      int64_t H, double eps, int64_t slot, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check(pico_rmsnorm_fwd_push(x.data_ptr(), cptr(residual), w.data_ptr(), mptr(y_local), mptr(h_out),
+                              (float*)mptr(rstd), table_of(dst_ptrs), table_of(flag_ptrs), (int)world,
+                              (int)my_rank, (int)rows, (int)H, (float)eps, (int)slot, (uint32_t)epoch,
+                              stream_of(x)),
+        "rmsnorm_fwd_push");
+}
+
+void slot_sum(const at::Tensor& staging, int64_t world, int64_t rows, int64_t cols,
+              const c10::optional<at::Tensor>& addend, at::Tensor& out, int64_t local_flags, int64_t slot,
+              int64_t epoch, int64_t timeout_ms) {
+  c10::cuda::CUDAGuard guard(out.device());
+  check(pico_slot_sum(staging.data_ptr(), (int)world, (int)rows, (int)cols, cptr(addend), out.data_ptr(),
+                      reinterpret_cast<const uint32_t*>(local_flags), (int)slot, (uint32_t)epoch,
+                      (uint32_t)timeout_ms, stream_of(out)),
+        "slot_sum");
+}
+
+// GEMM with collective fusion; see PicoGemmComm in gemm/gemm.h.
+void gemm_ex(const at::Tensor& A, const at::Tensor& B, const c10::optional<at::Tensor>& D, int64_t M,
+             int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldd, bool a_mn_major, bool b_mn_major,
+             int64_t out_mode, int64_t max_ctas, int64_t a_flags, int64_t a_slot, int64_t a_epoch,
+             int64_t a_rows_per_block, int64_t a_skip_block, const std::vector<int64_t>& d_ptrs,
+             int64_t d_rows_per_block, int64_t m_rotate_rows, int64_t timeout_ms) {
+  c10::cuda::CUDAGuard guard(A.device());
+  PicoGemmComm c;
+  memset(&c, 0, sizeof(c));
+  c.a_flags = reinterpret_cast<const unsigned int*>(a_flags);
+  c.a_slot = (int)a_slot;
+  c.a_epoch = (unsigned int)a_epoch;
+  c.a_rows_per_block = (int)a_rows_per_block;
+  c.a_skip_block = (int)a_skip_block;
+  c.d_num_dest = (int)d_ptrs.size();
+  c.d_rows_per_block = (int)d_rows_per_block;
+  TORCH_CHECK(d_ptrs.size() <= 8, "gemm_ex: at most 8 destinations");
+  for (size_t i = 0; i < d_ptrs.size(); ++i) c.d_ptrs[i] = reinterpret_cast<void*>(d_ptrs[i]);
+  c.m_rotate_rows = (int)m_rotate_rows;
+  c.timeout_ms = (unsigned int)timeout_ms;
+  void* dptr = D.has_value() && D->defined() ? D->data_ptr() : nullptr;
+  TORCH_CHECK(dptr != nullptr || !d_ptrs.empty(), "gemm_ex: no output");
+  check(pico_gemm_bf16_ex(A.data_ptr(), B.data_ptr(), dptr, (int)M, (int)N, (int)K, (int)lda, (int)ldb,
+                          (int)ldd, a_mn_major, b_mn_major, (int)out_mode, (int)max_ctas, &c, stream_of(A)),
+        "gemm_ex");
+}
+
 // Returns the 8 status words after synchronising (word 0 != 0 means a kernel gave up a wait).
 std::vector<int64_t> status_fetch() {
   int out[8] = {0};
@@ -175,4 +286,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("accumulate_bf16_into_f32", &accumulate_bf16_into_f32);
   m.def("fill_u32", &fill_u32);
   m.def("status_fetch", &status_fetch);
+  m.def("symm_alloc", &symm_alloc);
+  m.def("symm_open", &symm_open);
+  m.def("symm_close", &symm_close);
+  m.def("symm_free", &symm_free);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+  m.def("signal_peers", &signal_peers);
+  m.def("wait_flags", &wait_flags);
+  m.def("push_rows", &push_rows);
+  m.def("rmsnorm_fwd_push", &rmsnorm_fwd_push);
+  m.def("slot_sum", &slot_sum);
+  m.def("gemm_ex", &gemm_ex);
 }

@@ -1,0 +1,231 @@
+#include "tp_comm.h"
+
+#include <cuda_bf16.h>
+
+#include "../common/host.h"
+#include "../elementwise/norm_kernels.cuh"
+#include "../runtime/flags.cuh"
+
+namespace pico {
+
+// Grid-wide completion: the last CTA to finish raises the flags. `counter` is a device word that
+// returns to zero after each use.
+__device__ __forceinline__ void raise_flags_when_grid_done(unsigned int* counter, PicoPeerTable flags,
+                                                           int world, int my_rank, int slot,
+                                                           uint32_t epoch) {
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(counter, 1u) + 1u;
+    last = (done == gridDim.x);
+    if (last) *counter = 0;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(flag_word(flags.ptr[threadIdx.x], slot, my_rank), epoch);
+  }
+}
+
+__global__ void push_rows_kernel(const uint4* __restrict__ src, PicoPeerTable dst, PicoPeerTable flags,
+                                 int world, int my_rank, int64_t nvec, int slot, uint32_t epoch,
+                                 unsigned int* counter) {
+  const int64_t base = (int64_t)my_rank * nvec;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    for (int r = 0; r < world; ++r) reinterpret_cast<uint4*>(dst.ptr[r])[base + i] = v;
+  }
+  raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_push_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y_local,
+                        __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out,
+                        PicoPeerTable dst, PicoPeerTable flags, int world, int my_rank, int rows, int H,
+                        float eps, int slot, uint32_t epoch, unsigned int* counter) {
+  __shared__ float red[kNormThreads / 32];
+  const int nvec = H / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + (size_t)row * H) : nullptr;
+    float vals[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        unpack8(xr[v], vals[i]);
+        if (rr) {
+          float r[8];
+          unpack8(rr[v], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
+          uint4 hv = pack8(vals[i]);
+          unpack8(hv, vals[i]);
+          if (h_out) reinterpret_cast<uint4*>(h_out + (size_t)row * H)[v] = hv;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    const size_t grow = (size_t)my_rank * rows + row;  // row in the gathered tensor
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float wv[8], o[8];
+        unpack8(reinterpret_cast<const uint4*>(w)[v], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wv[j];
+        const uint4 packed = pack8(o);
+        if (y_local) reinterpret_cast<uint4*>(y_local + (size_t)row * H)[v] = packed;
+        for (int r = 0; r < world; ++r)
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.ptr[r]) + grow * H)[v] = packed;
+      }
+    }
+  }
+  raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
+}
+
+__global__ void slot_sum_kernel(const uint4* __restrict__ staging, int world, int64_t nvec,
+                                const uint4* __restrict__ addend, uint4* __restrict__ out,
+                                const uint32_t* local_flags, int slot, uint32_t epoch,
+                                uint64_t timeout_ns, int* status) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + threadIdx.x, epoch, timeout_ns, status,
+                      700 + threadIdx.x))
+      ok = 0;
+  }
+  __syncthreads();
+  if (!ok) return;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float acc[8];
+    unpack8(staging[i], acc);
+    for (int s = 1; s < world; ++s) {
+      float f[8];
+      unpack8(staging[(int64_t)s * nvec + i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    if (addend) {
+      float f[8];
+      unpack8(addend[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    out[i] = pack8(acc);
+  }
+}
+
+constexpr int kMaxDev = 64;
+unsigned int* g_counters[kMaxDev] = {nullptr};
+
+// One zero-initialised word per device for the "last CTA" detection; created on first use.
+static unsigned int* grid_counter() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  if (!g_counters[dev]) {
+    unsigned int* p = nullptr;
+    if (cudaMalloc(&p, 64 * sizeof(unsigned int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 64 * sizeof(unsigned int));
+    g_counters[dev] = p;
+  }
+  return g_counters[dev];
+}
+
+}  // namespace pico
+
+using namespace pico;
+
+static int check_world(const char* what, int world, int slot) {
+  if (world < 1 || world > PICO_MAX_PEERS || slot < 0 || slot >= PICO_FLAG_SLOTS) {
+    pico_host::set_error("%s: world %d / flag slot %d out of range", what, world, slot);
+    return -2;
+  }
+  return 0;
+}
+
+extern "C" int pico_push_rows(const void* src, PicoPeerTable dst, PicoPeerTable flags, int world,
+                              int my_rank, int rows, int cols, int slot, uint32_t epoch,
+                              cudaStream_t stream) {
+  if (int rc = check_world("push_rows", world, slot)) return rc;
+  const int64_t n = (int64_t)rows * cols;
+  if (n % 8 != 0) {
+    pico_host::set_error("push_rows: rows*cols must be a multiple of 8");
+    return -2;
+  }
+  unsigned int* counter = grid_counter();
+  if (!counter) return -1;
+  const int64_t nvec = n / 8;
+  int grid = (int)((nvec + 255) / 256);
+  const int cap = pico_host::num_sms() * 4;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  push_rows_kernel<<<grid, 256, 0, stream>>>((const uint4*)src, dst, flags, world, my_rank, nvec, slot,
+                                             epoch, counter);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) pico_host::set_error("push_rows: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+extern "C" int pico_rmsnorm_fwd_push(const void* x, const void* residual, const void* w, void* y_local,
+                                     void* h_out, float* rstd, PicoPeerTable dst, PicoPeerTable flags,
+                                     int world, int my_rank, int rows, int H, float eps, int slot,
+                                     uint32_t epoch, cudaStream_t stream) {
+  if (int rc = check_world("rmsnorm_fwd_push", world, slot)) return rc;
+  if (H % 8 != 0 || H > kNormThreads * 8 * 4) {
+    pico_host::set_error("rmsnorm_fwd_push: hidden size %d must be a multiple of 8 and <= %d", H,
+                         kNormThreads * 8 * 4);
+    return -2;
+  }
+  unsigned int* counter = grid_counter();
+  if (!counter) return -1;
+  const int cap = pico_host::num_sms() * 8;
+  const int grid = rows < cap ? rows : cap;
+  const int need = (H / 8 + kNormThreads - 1) / kNormThreads;
+#define PICO_LAUNCH(NV)                                                                            \
+  rmsnorm_fwd_push_kernel<NV><<<grid, kNormThreads, 0, stream>>>(                                  \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,            \
+      (__nv_bfloat16*)y_local, (__nv_bfloat16*)h_out, rstd, dst, flags, world, my_rank, rows, H,  \
+      eps, slot, epoch, counter + 1)
+  if (need <= 1) PICO_LAUNCH(1);
+  else if (need <= 2) PICO_LAUNCH(2);
+  else PICO_LAUNCH(4);
+#undef PICO_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) pico_host::set_error("rmsnorm_fwd_push: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+extern "C" int pico_slot_sum(const void* staging, int world, int rows, int cols, const void* addend,
+                             void* out, const uint32_t* local_flags, int slot, uint32_t epoch,
+                             uint32_t timeout_ms, cudaStream_t stream) {
+  if (int rc = check_world("slot_sum", world, slot)) return rc;
+  const int64_t n = (int64_t)rows * cols;
+  if (n % 8 != 0) {
+    pico_host::set_error("slot_sum: rows*cols must be a multiple of 8");
+    return -2;
+  }
+  const int64_t nvec = n / 8;
+  int grid = (int)((nvec + 255) / 256);
+  const int cap = pico_host::num_sms() * 8;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  slot_sum_kernel<<<grid, 256, 0, stream>>>((const uint4*)staging, world, nvec, (const uint4*)addend,
+                                            (uint4*)out, local_flags, slot, epoch,
+                                            (uint64_t)timeout_ms * 1000000ull, pico_status_buffer());
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) pico_host::set_error("slot_sum: %s", cudaGetErrorString(e));
+  return (int)e;
+}

@@ -17,6 +17,32 @@ int pico_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, i
                    int ldd, int a_mn_major, int b_mn_major, int out_mode, int max_ctas,
                    cudaStream_t stream);
 
+// Collective fusion (see csrc/runtime/symm.h for the symmetric-memory model).
+//   all-gather -> GEMM : A (K-major) is this GPU's gather buffer; row block b (a_rows_per_block
+//     rows) is written by rank b and announced by flag [a_slot][b] >= a_epoch in a_flags (local
+//     flag buffer). The kernel starts on block a_skip_block (this rank's own rows) and loads the
+//     other blocks as their flags arrive, so the transfer overlaps the math tile by tile.
+//   GEMM -> reduce-scatter : output row block b (d_rows_per_block rows) is stored through
+//     d_ptrs[b] — the slot reserved for this rank in rank b's staging buffer — instead of D;
+//     the owner sums the slots afterwards (pico_slot_sum / pico_slot_sum_add_rmsnorm).
+//   m_rotate_rows shifts the order in which row blocks are visited.
+typedef struct {
+  const unsigned int* a_flags;
+  int a_slot;
+  unsigned int a_epoch;
+  int a_rows_per_block;
+  int a_skip_block;
+  int d_num_dest;
+  int d_rows_per_block;
+  void* d_ptrs[8];
+  int m_rotate_rows;
+  unsigned int timeout_ms;
+} PicoGemmComm;
+
+int pico_gemm_bf16_ex(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb,
+                      int ldd, int a_mn_major, int b_mn_major, int out_mode, int max_ctas,
+                      const PicoGemmComm* comm, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -22,8 +22,11 @@
 // requirement is 16-byte aligned base pointers and leading dimensions.
 #include <cuda_bf16.h>
 
+#include <cstring>
+
 #include "../common/host.h"
 #include "../common/ptx.cuh"
+#include "../runtime/flags.cuh"
 #include "gemm.h"
 
 namespace pico {
@@ -50,13 +53,37 @@ struct GemmCfg {
 
 enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2 };
 
+// Output tensor maps: one per destination. A plain GEMM uses m[0]; a GEMM fused with a
+// reduce-scatter stores row block b of the output through m[b], which addresses rank b's
+// staging buffer (peer memory over NVLink).
+struct DMaps {
+  CUtensorMap m[PICO_MAX_PEERS];
+};
+
+// Collective fusion parameters (all zero = plain GEMM).
+struct GemmComm {
+  // all-gather -> GEMM: the rows of A arrive in equal blocks, block b written by rank b into
+  // this GPU's gather buffer; tiles of block b are loaded only after flag [a_slot][b] >= a_epoch
+  const uint32_t* a_flags;
+  int a_slot;
+  uint32_t a_epoch;
+  int a_rows_per_block;
+  int a_skip_block;       // this rank's own block: already in place, never waited for
+  // GEMM -> reduce-scatter: output row block b goes through DMaps::m[b]
+  int d_rows_per_block;
+  // both: logical m-tile t maps to physical m-tile (t + m_rotate) % num_m, so a rank starts
+  // with its own block (gather) or with its neighbour's (scatter)
+  int m_rotate;
+  unsigned long long timeout_ns;
+};
+
 struct TileCoord {
   int m, n;
 };
 
 // Grouped rasterisation: consecutive tile indices (= CTAs running at the same time) cover a
 // compact block of the output so A and B slices are shared through L2.
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) {
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int m_rotate = 0) {
   constexpr int kGroup = 16;
   int tiles_per_group = kGroup * num_n;
   int g = tile / tiles_per_group;
@@ -65,6 +92,10 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
   int r = tile - g * tiles_per_group;
   TileCoord c;
   c.m = first_m + r % gsize;
+  if (m_rotate) {
+    c.m += m_rotate;
+    if (c.m >= num_m) c.m -= num_m;
+  }
   c.n = r / gsize;
   return c;
 }
@@ -72,7 +103,8 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
 template <int BN, int A_MN, int B_MN, int OUT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_d, int M, int N, int K, int* status) {
+                 const __grid_constant__ DMaps dmaps, const GemmComm comm, int M, int N, int K,
+                 int* status) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
@@ -107,7 +139,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    tma_prefetch_desc(&tmap_d);
+    tma_prefetch_desc(&dmaps.m[0]);
   }
   if (warp == 1) {
     tmem_alloc(tmem_ptr_smem, Cfg::kTmemCols);
@@ -124,9 +156,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t ready_blocks = 0;  // row blocks of A known to have arrived
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        TileCoord tc = tile_coord(tile, num_m, num_n);
+        TileCoord tc = tile_coord(tile, num_m, num_n, comm.m_rotate);
         const int m0 = tc.m * BM, n0 = tc.n * BN;
+        if (comm.a_flags != nullptr) {
+          const int blk = m0 / comm.a_rows_per_block;
+          if (blk != comm.a_skip_block && !((ready_blocks >> blk) & 1u)) {
+            if (!wait_flag_ge(comm.a_flags + comm.a_slot * PICO_MAX_PEERS + blk, comm.a_epoch,
+                              comm.timeout_ns, status, 500 + blk)) {
+              *abort_word = 1;
+              break;
+            }
+            ready_blocks |= 1u << blk;
+            // the rows were written by another GPU; order the flag observation before the
+            // bulk-copy engine's reads of them
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_word, status, 100 + s)) {
             ok = false;
@@ -212,8 +259,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t acc_phase = 0;
     int buf = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      TileCoord tc = tile_coord(tile, num_m, num_n);
-      const int m0 = tc.m * BM, n0 = tc.n * BN;
+      TileCoord tc = tile_coord(tile, num_m, num_n, comm.m_rotate);
+      int m0 = tc.m * BM;
+      const int n0 = tc.n * BN;
+      const CUtensorMap* tmap_d = &dmaps.m[0];
+      if (comm.d_rows_per_block > 0) {
+        const int dest = m0 / comm.d_rows_per_block;
+        tmap_d = &dmaps.m[dest];
+        m0 -= dest * comm.d_rows_per_block;
+      }
       bool ok = mbar_wait(&tmem_full[acc], acc_phase, abort_word, status, 400 + acc);
       // uniform decision for the four epilogue warps (they share named barriers below)
       int all_ok;
@@ -275,9 +329,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         named_barrier_sync(1, kNumEpilogueThreads);
         if (et == 0) {
           if (OUT == OUT_F32_ACC)
-            tma_reduce_add_2d(&tmap_d, sbuf, n0 + c * kColsPerChunk, m0);
+            tma_reduce_add_2d(tmap_d, sbuf, n0 + c * kColsPerChunk, m0);
           else
-            tma_store_2d(&tmap_d, sbuf, n0 + c * kColsPerChunk, m0);
+            tma_store_2d(tmap_d, sbuf, n0 + c * kColsPerChunk, m0);
           tma_store_commit();
         }
         buf ^= 1;
@@ -310,10 +364,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
 template <int BN, int A_MN, int B_MN, int OUT>
 static int launch(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb,
-                  int ldd, int max_ctas, cudaStream_t stream) {
+                  int ldd, int max_ctas, const PicoGemmComm* pc, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   using pico_host::Swizzle;
-  CUtensorMap ta, tb, td;
+  CUtensorMap ta, tb;
+  DMaps dm;
+  GemmComm comm;
+  memset(&comm, 0, sizeof(comm));
   int rc;
   if (A_MN == 0)
     rc = pico_host::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, (uint64_t)lda * 2,
@@ -329,13 +386,46 @@ static int launch(const void* A, const void* B, void* D, int M, int N, int K, in
     rc = pico_host::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, (uint64_t)ldb * 2,
                                  64, 64, Swizzle::B128);
   if (rc) return rc;
-  if (OUT == OUT_BF16)
-    rc = pico_host::make_tmap_2d(&td, D, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, M, (uint64_t)ldd * 2,
-                                 64, BM, Swizzle::B128);
-  else
-    rc = pico_host::make_tmap_2d(&td, D, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, N, M, (uint64_t)ldd * 4,
-                                 32, BM, Swizzle::B128);
-  if (rc) return rc;
+  const int num_dest = (pc && pc->d_num_dest > 0) ? pc->d_num_dest : 1;
+  const int d_rows = (pc && pc->d_num_dest > 0) ? pc->d_rows_per_block : M;
+  if (num_dest > PICO_MAX_PEERS) {
+    pico_host::set_error("gemm: %d destinations exceed the maximum of %d", num_dest, PICO_MAX_PEERS);
+    return -2;
+  }
+  if (pc && pc->d_num_dest > 0) {
+    if (A_MN != 0 || d_rows % BM != 0 || d_rows * num_dest != M) {
+      pico_host::set_error("gemm->scatter: need K-major A and M (%d) = %d destinations x a multiple of %d rows",
+                           M, num_dest, BM);
+      return -2;
+    }
+    comm.d_rows_per_block = d_rows;
+  }
+  for (int b = 0; b < num_dest; ++b) {
+    void* dptr = (pc && pc->d_num_dest > 0) ? pc->d_ptrs[b] : D;
+    if (OUT == OUT_BF16)
+      rc = pico_host::make_tmap_2d(&dm.m[b], dptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, d_rows,
+                                   (uint64_t)ldd * 2, 64, BM, Swizzle::B128);
+    else
+      rc = pico_host::make_tmap_2d(&dm.m[b], dptr, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, N, d_rows,
+                                   (uint64_t)ldd * 4, 32, BM, Swizzle::B128);
+    if (rc) return rc;
+  }
+  for (int b = num_dest; b < PICO_MAX_PEERS; ++b) dm.m[b] = dm.m[0];
+  if (pc && pc->a_flags != nullptr) {
+    if (A_MN != 0 || pc->a_rows_per_block % BM != 0 || pc->a_rows_per_block <= 0) {
+      pico_host::set_error("gather->gemm: need K-major A and row blocks that are a multiple of %d", BM);
+      return -2;
+    }
+    comm.a_flags = pc->a_flags;
+    comm.a_slot = pc->a_slot;
+    comm.a_epoch = pc->a_epoch;
+    comm.a_rows_per_block = pc->a_rows_per_block;
+    comm.a_skip_block = pc->a_skip_block;
+  }
+  if (pc) {
+    comm.m_rotate = pc->m_rotate_rows / BM;
+    comm.timeout_ns = (unsigned long long)pc->timeout_ms * 1000000ull;
+  }
 
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT>;
   static bool attr_set = false;  // per template instantiation
@@ -357,7 +447,7 @@ static int launch(const void* A, const void* B, void* D, int M, int N, int K, in
   int ctas = pico_host::num_sms();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (num_tiles < ctas) ctas = num_tiles;
-  kern<<<ctas, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, td, M, N, K, pico_status_buffer());
+  kern<<<ctas, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, dm, comm, M, N, K, pico_status_buffer());
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     pico_host::set_error("gemm launch: %s", cudaGetErrorString(e));
@@ -368,10 +458,11 @@ static int launch(const void* A, const void* B, void* D, int M, int N, int K, in
 
 template <int BN>
 static int dispatch_bn(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb,
-                       int ldd, int a_mn, int b_mn, int out_mode, int max_ctas, cudaStream_t st) {
+                       int ldd, int a_mn, int b_mn, int out_mode, int max_ctas, const PicoGemmComm* pc,
+                       cudaStream_t st) {
 #define PICO_CASE(AM, BMJ, OM)                                                                   \
   if (a_mn == AM && b_mn == BMJ && out_mode == OM)                                               \
-    return launch<BN, AM, BMJ, OM>(A, B, D, M, N, K, lda, ldb, ldd, max_ctas, st);
+    return launch<BN, AM, BMJ, OM>(A, B, D, M, N, K, lda, ldb, ldd, max_ctas, pc, st);
   PICO_CASE(0, 0, OUT_BF16)
   PICO_CASE(0, 1, OUT_BF16)
   PICO_CASE(1, 1, OUT_BF16)
@@ -388,17 +479,24 @@ static int dispatch_bn(const void* A, const void* B, void* D, int M, int N, int 
 
 }  // namespace pico
 
-extern "C" int pico_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda,
-                              int ldb, int ldd, int a_mn_major, int b_mn_major, int out_mode,
-                              int max_ctas, cudaStream_t stream) {
+extern "C" int pico_gemm_bf16_ex(const void* A, const void* B, void* D, int M, int N, int K, int lda,
+                                 int ldb, int ldd, int a_mn_major, int b_mn_major, int out_mode,
+                                 int max_ctas, const PicoGemmComm* comm, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // Narrow outputs waste less of the tile with a smaller BN.
   if (N <= 64)
     return pico::dispatch_bn<64>(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_mode,
-                                 max_ctas, stream);
+                                 max_ctas, comm, stream);
   if (N <= 128 || ((N + 127) / 128) * ((M + 127) / 128) <= 148)
     return pico::dispatch_bn<128>(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major,
-                                  out_mode, max_ctas, stream);
+                                  out_mode, max_ctas, comm, stream);
   return pico::dispatch_bn<256>(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_mode,
-                                max_ctas, stream);
+                                max_ctas, comm, stream);
+}
+
+extern "C" int pico_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda,
+                              int ldb, int ldd, int a_mn_major, int b_mn_major, int out_mode,
+                              int max_ctas, cudaStream_t stream) {
+  return pico_gemm_bf16_ex(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_mode,
+                           max_ctas, nullptr, stream);
 }

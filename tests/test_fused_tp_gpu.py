@@ -1,0 +1,138 @@
+"""Fused tensor-parallel linears (push all-gather -> gated GEMM, GEMM -> peer-memory reduce-scatter)
+on 2+ GPUs against an fp32 single-device restatement. Each rank is its own process on its own GPU
+(spawned here); the test is skipped with fewer than two devices."""
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn, errors):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        fn(rank, world)
+        torch.cuda.synchronize()
+        dist.barrier()
+    except Exception:
+        errors.put((rank, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def run_gpu_ranks(fn, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    errors = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn, errors)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+    msgs = []
+    while not errors.empty():
+        r, tb = errors.get()
+        msgs.append(f"--- rank {r} ---\n{tb}")
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.terminate()
+    assert not msgs and not alive and all(p.exitcode == 0 for p in procs), "\n".join(msgs)
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+def _fused_ops_worker(rank, world):
+    from picotron_b200 import ops
+    from picotron_b200.ops import fused_tp
+    from picotron_b200.ops.gemm import WeightSet
+    from picotron_b200.runtime.symm import SymmGroup
+
+    dev = torch.device("cuda", rank)
+    b, s_loc, K, N = 2, 256, 512, 768
+    sg = SymmGroup(None)
+    tp = fused_tp.TPFused(sg, b * s_loc, max(K, N))
+    torch.manual_seed(0)                               # same full tensors on every rank
+    x_full = torch.randn(b, s_loc * world, K, device=dev).to(torch.bfloat16)
+    w_col = (torch.randn(N * world, K, device=dev) / K ** 0.5).to(torch.bfloat16)     # column-parallel weight
+    w_row = (torch.randn(K, N * world, device=dev) / N ** 0.5).to(torch.bfloat16)     # row-parallel weight
+    g_full = torch.randn(b, s_loc * world, N * world, device=dev).to(torch.bfloat16)
+    for it in range(3):                                # several rounds exercise buffer alternation
+        # ---- column parallel: y[:, :, my columns] = x_full @ w_col[my rows].T
+        x_sh = x_full[:, rank * s_loc:(rank + 1) * s_loc].clone().requires_grad_(True)
+        w_loc = torch.nn.Parameter(w_col[rank * N:(rank + 1) * N].clone())
+
+        class M:  # minimal module stand-in for WeightSet.of
+            weight = w_loc
+        y = fused_tp.ag_linear(x_sh, tp, [M], batch_major=True)
+        ref = x_full.float() @ w_loc.float().t()
+        assert _rel(y, ref) < 1e-2, ("ag_linear fwd", it)
+        gy = g_full[:, :, rank * N:(rank + 1) * N].contiguous()
+        y.backward(gy)
+        # dx shard = sum over ranks of (g[:, :, cols_r] @ w_col[rows_r]) restricted to my sequence chunk
+        dx_ref = (g_full.float() @ w_col.float())[:, rank * s_loc:(rank + 1) * s_loc]
+        assert _rel(x_sh.grad, dx_ref) < 1e-2, ("ag_linear dx", it)
+        dw_ref = gy.float().reshape(-1, N).t() @ x_full.float().reshape(-1, K)
+        assert _rel(w_loc.grad, dw_ref) < 1e-2, ("ag_linear dw", it)
+        # ---- row parallel: y_shard = (x2 @ w_row[:, my cols].T summed over ranks)[my sequence chunk]
+        xin_full = g_full                                  # [b, s, N*world] plays the role of the hidden activations
+        xin = xin_full[:, :, rank * N:(rank + 1) * N].clone().requires_grad_(True)
+        wr = torch.nn.Parameter(w_row[:, rank * N:(rank + 1) * N].clone())
+        res = x_full[:, rank * s_loc:(rank + 1) * s_loc].clone().requires_grad_(True)
+        out = fused_tp.linear_rs(xin, wr, tp, True, (b, s_loc), addend=res)
+        ref_full = xin_full.float() @ w_row.float().t() + x_full.float()
+        assert _rel(out, ref_full[:, rank * s_loc:(rank + 1) * s_loc]) < 1e-2, ("linear_rs fwd", it)
+        go = x_full[:, rank * s_loc:(rank + 1) * s_loc].contiguous()
+        out.backward(go)
+        dxin_ref = x_full.float() @ wr.float()
+        assert _rel(xin.grad, dxin_ref) < 1e-2, ("linear_rs dx", it)
+        dwr_ref = x_full.float().reshape(-1, K).t() @ xin_full.float().reshape(-1, N * world)[:, rank * N:(rank + 1) * N]
+        assert _rel(wr.grad, dwr_ref) < 1e-2, ("linear_rs dw", it)
+        assert _rel(res.grad, go) < 1e-3
+    ops.check_status("fused tp")
+
+
+def test_fused_tp_ops_2gpu():
+    run_gpu_ranks(_fused_ops_worker, 2)
+
+
+def _timeout_worker(rank, world):
+    """A flag that nobody raises: the bounded wait must give up, report, and leave the context usable."""
+    from picotron_b200 import ops
+    from picotron_b200.runtime.status import CommTimeoutError, raise_if_failed
+    from picotron_b200.runtime.symm import SymmGroup
+    sg = SymmGroup(None)
+    sg.wait(slot=200, epoch=7, timeout_ms=300)      # slot 200 is never signalled
+    try:
+        raise_if_failed("expected")
+        raise AssertionError("the wait did not report a timeout")
+    except CommTimeoutError as e:
+        assert e.code == 2
+    # the context still works: a normal barrier over the group succeeds afterwards
+    sg.barrier()
+    ops.check_status("after timeout")
+    t = torch.ones(4, device="cuda") * (rank + 1)
+    dist.all_reduce(t)
+    assert t[0].item() == sum(range(1, world + 1))
+
+
+def test_bounded_wait_reports_timeout_2gpu():
+    run_gpu_ranks(_timeout_worker, 2)
