@@ -1,0 +1,403 @@
+// Flash attention forward for sm_100a: S = Q K^T and O += P V run on tcgen05 tensor cores with
+// the accumulators in tensor memory; Q, K and V tiles arrive by TMA (128-byte swizzle); the
+// online softmax runs in registers, one thread per query row.
+//
+// One CTA handles 128 query rows of one (batch, head) and walks the key/value sequence in blocks
+// of 128:
+//   warp 4 (one thread)  : TMA loads of Q once and of K/V blocks into a 2-stage ring, and all
+//                          tcgen05.mma issue: S(j) = Q K_j^T, then O += P_j V_j once P_j is ready
+//   warps 0-3 (128 thr.) : tcgen05.ld the S row, scale, mask, online-softmax update, write P_j as
+//                          bf16 into swizzled shared memory (the A operand of the second GEMM),
+//                          rescale the O accumulator in TMEM when the running maximum moved,
+//                          final normalisation and store of O and the log-sum-exp
+// Two CTAs fit on an SM for head_dim 64 (each allocates 256 TMEM columns), so one CTA's softmax
+// overlaps the other's tensor-core work without intra-CTA software pipelining.
+//
+// Every wait is bounded (see common/ptx.cuh); a CTA that gives up frees its TMEM and returns.
+#include <cuda_bf16.h>
+#include <math_constants.h>
+
+#include <cstring>
+
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+#include "attention.h"
+
+namespace pico {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kFwdThreads = 160;
+constexpr float kLog2e = 1.4426950408889634f;
+// only rescale the accumulator when the running max grew by more than this (log2 units);
+// smaller drifts are absorbed by the fp32 range of the un-normalised probabilities
+constexpr float kRescaleThreshold = 8.0f;
+
+template <int D>
+struct FwdCfg {
+  static constexpr int kQBytes = kBlockM * D * 2;
+  static constexpr int kKVBytes = kBlockN * D * 2;       // one K or V tile
+  static constexpr int kPBytes = kBlockM * kBlockN * 2;  // P tile, bf16
+  static constexpr int kStages = 2;
+  static constexpr int kTiles = kQBytes + 2 * kStages * kKVBytes + kPBytes;
+  static constexpr int kNumBars = 1 + 3 * kStages + 3;   // q, k_full/v_full/kv_empty per stage, s_full, p_ready, pv_done
+  static constexpr int kSmemBytes = kTiles + kNumBars * 8 + 16 + 1024;
+  static constexpr int kTmemCols = 256;                  // S: 128 columns, O: D (<= 128) columns
+  static constexpr int kPanels = D / 64;                 // 64-element (128-byte) column panels of Q/K/V
+};
+
+struct FwdMaps {
+  CUtensorMap q, k, v;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kFwdThreads)
+flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict__ out,
+                 float* __restrict__ lse, const PicoAttnParams p, int* status) {
+  using Cfg = FwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Cfg::kQBytes;                       // [stage]
+  uint8_t* sV = sK + Cfg::kStages * Cfg::kKVBytes;       // [stage]
+  uint8_t* sP = sV + Cfg::kStages * Cfg::kKVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTiles);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* v_full = k_full + Cfg::kStages;
+  uint64_t* kv_empty = v_full + Cfg::kStages;
+  uint64_t* s_full = kv_empty + Cfg::kStages;
+  uint64_t* p_ready = s_full + 1;
+  uint64_t* pv_done = p_ready + 1;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(pv_done + 1);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // heavy (late) query tiles first so the causal triangle balances across the grid
+  const int num_q_tiles = (p.seq_q + kBlockM - 1) / kBlockM;
+  const int q_tile = num_q_tiles - 1 - (int)blockIdx.x;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / (p.heads / p.kv_heads);
+  const int q0 = q_tile * kBlockM;
+
+  // key blocks this tile needs: all of them, or (causal) those that start at or before the last
+  // query position of the tile
+  int num_kv = (p.seq_k + kBlockN - 1) / kBlockN;
+  if (p.causal) {
+    const int last_q_pos = p.q_pos0 + min(q0 + kBlockM, p.seq_q) - 1;
+    const int visible = last_q_pos - p.k_pos0 + 1;       // keys [0, visible) may be attended
+    num_kv = visible <= 0 ? 0 : min(num_kv, (visible + kBlockN - 1) / kBlockN);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, kBlockM);
+    mbar_init(pv_done, 1);
+    *abort_word = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&maps.q);
+    tma_prefetch_desc(&maps.k);
+    tma_prefetch_desc(&maps.v);
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_ptr_smem, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t tmem_s = tmem_base;          // columns [0, 128)
+  const uint32_t tmem_o = tmem_base + 128;    // columns [128, 128 + D)
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA + MMA issue (one thread)
+    if (lane == 0 && num_kv > 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
+      constexpr uint32_t idesc_o = umma_idesc_bf16(kBlockM, D, 0, 1);
+      auto load_kv = [&](int j) {
+        const int s = j & 1;
+        uint8_t* k_dst = sK + s * Cfg::kKVBytes;
+        uint8_t* v_dst = sV + s * Cfg::kKVBytes;
+        mbar_arrive_expect_tx(&k_full[s], Cfg::kKVBytes);
+#pragma unroll
+        for (int pn = 0; pn < Cfg::kPanels; ++pn)
+          tma_load_4d(k_dst + pn * 16384, &maps.k, &k_full[s], pn * 64, kv_head, j * kBlockN, batch);
+        mbar_arrive_expect_tx(&v_full[s], Cfg::kKVBytes);
+#pragma unroll
+        for (int pn = 0; pn < Cfg::kPanels; ++pn)
+          tma_load_4d(v_dst + pn * 16384, &maps.v, &v_full[s], pn * 64, kv_head, j * kBlockN, batch);
+      };
+      mbar_arrive_expect_tx(q_full, Cfg::kQBytes);
+#pragma unroll
+      for (int pn = 0; pn < Cfg::kPanels; ++pn)
+        tma_load_4d(sQ + pn * 16384, &maps.q, q_full, pn * 64, head, q0, batch);
+      load_kv(0);
+      bool ok = mbar_wait(q_full, 0, abort_word, status, 1000);
+      for (int j = 0; j < num_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < num_kv) {
+          if (j + 1 >= 2 &&
+              !mbar_wait(&kv_empty[(j + 1) & 1], (((j + 1) >> 1) - 1) & 1, abort_word, status, 1010)) {
+            ok = false;
+            break;
+          }
+          load_kv(j + 1);
+        }
+        if (!mbar_wait(&k_full[s], ph, abort_word, status, 1020)) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ);
+        const uint32_t k_addr = smem_u32(sK + s * Cfg::kKVBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          tc_mma_f16_ss(tmem_s, umma_smem_desc(q_addr + off, 16, 1024),
+                        umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+        }
+        tc_commit(s_full);
+        if (!mbar_wait(p_ready, j & 1, abort_word, status, 1030)) break;
+        if (!mbar_wait(&v_full[s], ph, abort_word, status, 1040)) break;
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(sP);
+        const uint32_t v_addr = smem_u32(sV + s * Cfg::kKVBytes);
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          const uint32_t a_off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          tc_mma_f16_ss(tmem_o, umma_smem_desc(p_addr + a_off, 16, 1024),
+                        umma_smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_o,
+                        (j | kk) != 0 ? 1u : 0u);
+        }
+        tc_commit(&kv_empty[s]);
+        tc_commit(pv_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax + epilogue (128 threads)
+    const int row = warp * 32 + lane;
+    const bool valid_row = (q0 + row) < p.seq_q;
+    const int q_pos = p.q_pos0 + q0 + row;
+    const float scale_log2 = p.sm_scale * kLog2e;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m_run = -CUDART_INF_F;   // running max of the scaled scores (log2 units)
+    float l_run = 0.f;
+    bool alive = true;
+    for (int j = 0; j < num_kv; ++j) {
+      const bool ok = mbar_wait(s_full, j & 1, abort_word, status, 1100);
+      int all_ok;
+      asm volatile(
+          "{\n\t"
+          ".reg .pred p, q;\n\t"
+          "setp.ne.b32 p, %1, 0;\n\t"
+          "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+          "selp.u32 %0, 1, 0, q;\n\t"
+          "}\n"
+          : "=r"(all_ok)
+          : "r"((int)ok)
+          : "memory");
+      if (!all_ok) {
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+      const int k_base = j * kBlockN;
+      const bool need_mask = (p.causal && (p.k_pos0 + k_base + kBlockN - 1 > p.q_pos0 + q0)) ||
+                             (k_base + kBlockN > p.seq_k);
+      // pass 1: row maximum of this block
+      float mx = -CUDART_INF_F;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float sc = __uint_as_float(v[i]) * scale_log2;
+          if (need_mask) {
+            const int kidx = k_base + c * 32 + i;
+            if (kidx >= p.seq_k || (p.causal && p.k_pos0 + kidx > q_pos)) sc = -CUDART_INF_F;
+          }
+          mx = fmaxf(mx, sc);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const bool grow = (m_new - m_run > kRescaleThreshold) || (m_run == -CUDART_INF_F);
+      const float m_use = grow ? m_new : m_run;
+      const float alpha = (m_run == -CUDART_INF_F) ? 0.f : exp2f(m_run - m_use);
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_o + lane_base + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32b_x32(tmem_o + lane_base + c * 32, v);
+        }
+        tmem_st_wait();
+      }
+      l_run *= alpha;
+      m_run = m_use;
+      // pass 2: probabilities -> bf16 P tile in shared memory, row sum
+      float sum = 0.f;
+      uint8_t* prow = sP + row * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float sc = __uint_as_float(v[i]) * scale_log2;
+          bool masked = (m_run == -CUDART_INF_F);
+          if (need_mask) {
+            const int kidx = k_base + c * 32 + i;
+            masked = masked || kidx >= p.seq_k || (p.causal && p.k_pos0 + kidx > q_pos);
+          }
+          pr[i] = masked ? 0.f : exp2f(sc - m_run);
+          sum += pr[i];
+        }
+        uint8_t* panel = prow + (c >> 1) * 16384;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 o;
+          o.x = pack_bf16x2(pr[8 * q4 + 0], pr[8 * q4 + 1]);
+          o.y = pack_bf16x2(pr[8 * q4 + 2], pr[8 * q4 + 3]);
+          o.z = pack_bf16x2(pr[8 * q4 + 4], pr[8 * q4 + 5]);
+          o.w = pack_bf16x2(pr[8 * q4 + 6], pr[8 * q4 + 7]);
+          const int chunk = (c & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(panel + ((chunk ^ (row & 7)) << 4)) = o;
+        }
+      }
+      l_run += sum;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    // ---- epilogue
+    if (alive) {
+      bool ok = true;
+      if (num_kv > 0) ok = mbar_wait(pv_done, (num_kv - 1) & 1, abort_word, status, 1200);
+      int all_ok;
+      asm volatile(
+          "{\n\t"
+          ".reg .pred p, q;\n\t"
+          "setp.ne.b32 p, %1, 0;\n\t"
+          "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+          "selp.u32 %0, 1, 0, q;\n\t"
+          "}\n"
+          : "=r"(all_ok)
+          : "r"((int)ok)
+          : "memory");
+      if (all_ok) {
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* orow =
+            out + (int64_t)batch * p.o_batch_stride + (int64_t)(q0 + row) * p.o_row_stride + head * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          if (num_kv > 0) {
+            tmem_ld_32x32b_x32(tmem_o + lane_base + c * 32, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (valid_row) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
+              o.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
+              o.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
+              o.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = o;
+            }
+          }
+        }
+        if (valid_row && lse != nullptr) {
+          const float val = l_run > 0.f ? (m_run + log2f(l_run)) / kLog2e : -CUDART_INF_F;
+          lse[((int64_t)batch * p.heads + head) * p.seq_q + q0 + row] = val;
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  if (*abort_word) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int D>
+static int launch_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                      const PicoAttnParams* p, cudaStream_t stream) {
+  using Cfg = FwdCfg<D>;
+  FwdMaps maps;
+  int rc = pico_host::make_tmap_bshd(&maps.q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, p->heads, p->seq_q,
+                                     p->batch, p->q_row_stride * 2, p->q_batch_stride * 2, 64, kBlockM);
+  if (rc) return rc;
+  rc = pico_host::make_tmap_bshd(&maps.k, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, p->kv_heads, p->seq_k,
+                                 p->batch, p->k_row_stride * 2, p->k_batch_stride * 2, 64, kBlockN);
+  if (rc) return rc;
+  rc = pico_host::make_tmap_bshd(&maps.v, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, p->kv_heads, p->seq_k,
+                                 p->batch, p->v_row_stride * 2, p->v_batch_stride * 2, 64, kBlockN);
+  if (rc) return rc;
+  auto kern = flash_fwd_kernel<D>;
+  static int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (attr_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) {
+      pico_host::set_error("attention fwd: cudaFuncSetAttribute(%d): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
+      return (int)e;
+    }
+    attr_dev = dev;
+  }
+  dim3 grid((p->seq_q + kBlockM - 1) / kBlockM, p->heads, p->batch);
+  kern<<<grid, kFwdThreads, Cfg::kSmemBytes, stream>>>(maps, (__nv_bfloat16*)out, lse, *p, pico_status_buffer());
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    pico_host::set_error("attention fwd launch: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
+}  // namespace pico
+
+extern "C" int pico_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                                  const PicoAttnParams* p, cudaStream_t stream) {
+  if (p->batch <= 0 || p->seq_q <= 0 || p->heads <= 0) return 0;
+  if (p->heads % p->kv_heads != 0) {
+    pico_host::set_error("attention: heads (%d) must be a multiple of kv_heads (%d)", p->heads, p->kv_heads);
+    return -2;
+  }
+  if ((p->o_row_stride % 8) != 0 || (p->o_batch_stride % 8) != 0 || (reinterpret_cast<uintptr_t>(out) & 15)) {
+    pico_host::set_error("attention: output must be 16-byte aligned with strides that are multiples of 8");
+    return -2;
+  }
+  if (p->head_dim == 64) return pico::launch_fwd<64>(q, k, v, out, lse, p, stream);
+  if (p->head_dim == 128) return pico::launch_fwd<128>(q, k, v, out, lse, p, stream);
+  pico_host::set_error("attention: head_dim %d not supported (64 or 128)", p->head_dim);
+  return -2;
+}

@@ -88,6 +88,43 @@ int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, 
   return 0;
 }
 
+int make_tmap_bshd(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                   uint64_t d, uint64_t heads, uint64_t seq, uint64_t batch, uint64_t row_stride_bytes,
+                   uint64_t batch_stride_bytes, uint32_t box_d, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  {
+    thread_local int bound_dev = -1;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev != bound_dev) {
+      cudaSetDevice(dev);
+      bound_dev = dev;
+    }
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_stride_bytes & 15) != 0 ||
+      (batch_stride_bytes & 15) != 0 || ((d * elem_bytes) & 15) != 0 || box_d * (uint32_t)elem_bytes != 128) {
+    set_error("attention operand: base/strides must be 16-byte aligned and the box 128 bytes wide "
+              "(ptr=%p row=%llu batch=%llu d=%llu)", base, (unsigned long long)row_stride_bytes,
+              (unsigned long long)batch_stride_bytes, (unsigned long long)d);
+    return -2;
+  }
+  cuuint64_t dims[4] = {d, heads, seq, batch};
+  cuuint64_t strides[3] = {d * (uint64_t)elem_bytes, row_stride_bytes, batch_stride_bytes};
+  cuuint32_t box[4] = {box_d, 1, box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled(4d) failed with CUresult %d (d=%llu heads=%llu seq=%llu batch=%llu "
+              "row=%llu batchstride=%llu)", (int)r, (unsigned long long)d, (unsigned long long)heads,
+              (unsigned long long)seq, (unsigned long long)batch, (unsigned long long)row_stride_bytes,
+              (unsigned long long)batch_stride_bytes);
+    return -3;
+  }
+  return 0;
+}
+
 int num_sms() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;

@@ -35,6 +35,12 @@ int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, 
                  uint64_t inner, uint64_t outer, uint64_t ld_bytes, uint32_t box_inner,
                  uint32_t box_outer, Swizzle sw);
 
+// 4-D map for [batch, seq, heads, head_dim] tensors: dims (d, heads, seq, batch), box
+// (box_d, 1, box_rows, 1), 128-byte swizzle. Strides in bytes.
+int make_tmap_bshd(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                   uint64_t d, uint64_t heads, uint64_t seq, uint64_t batch, uint64_t row_stride_bytes,
+                   uint64_t batch_stride_bytes, uint32_t box_d, uint32_t box_rows);
+
 int num_sms();
 
 }  // namespace pico_host

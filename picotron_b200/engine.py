@@ -44,6 +44,11 @@ def _dtype_of(cfg, device) -> torch.dtype:
 def loss_fn(model, logits, targets) -> torch.Tensor:
     """Mean token loss from the model output: dense logits, or vocabulary-sharded logits when
     the lm head keeps them sharded (``vocab_parallel_ce``)."""
+    if logits.dim() == 2 and targets.dim() == 2:
+        # fused sequence-parallel lm head: rows are rank-major, bring the targets into that order
+        world = group_size(getattr(model, "tp_group", None))
+        b, s = targets.shape
+        targets = targets.view(b, world, s // world).transpose(0, 1).reshape(-1)
     if getattr(model, "vocab_parallel_ce", False) and group_size(getattr(model, "tp_group", None)) > 1:
         g = model.tp_group
         start = group_rank(g) * logits.shape[-1]
@@ -169,6 +174,29 @@ class TrainEngine:
         self.model = model
         self.flat = self.device.type == "cuda" and self.dtype == torch.bfloat16
         self.store = ParamStore(model, pad_to_multiple=max(1, self._grad_group_size())) if self.flat else None
+        self.fused_tp = None
+        self._maybe_install_fused_tp()
+
+    def _maybe_install_fused_tp(self):
+        """Switch the sequence-parallel linears to the kernels that carry their collectives through
+        NVLink peer memory (``ops.fused_tp``). Needs the flat bf16 path, TP > 1 with sequence
+        parallelism, and a micro-batch whose per-rank token count is a multiple of the GEMM tile;
+        ``PICO_FUSED_TP=0`` keeps the NCCL collectives."""
+        import os
+        d, t, m = self.cfg["distributed"], self.cfg["training"], self.pgm
+        if not (self.flat and m.tp_world_size > 1 and d["sequence_parallel"] and not d["overlap_comm"]):
+            return
+        if os.environ.get("PICO_FUSED_TP", "1") == "0":
+            return
+        from .ops.fused_tp import TPFused
+        from .parallel.tensor_parallel import install_fused_tp
+        from .runtime.symm import SymmGroup
+        m_local = t["micro_batch_size"] * (t["seq_length"] // m.cp_world_size // m.tp_world_size)
+        if not TPFused.usable(m_local):
+            return
+        sg = SymmGroup(m.tp_group, device=self.device)
+        self.fused_tp = TPFused(sg, m_local, self.model_config.hidden_size)
+        install_fused_tp(self.model, self.fused_tp)
 
     def _grad_group(self):
         m = self.pgm

@@ -114,13 +114,17 @@ class Attention(nn.Module):
         k = rope.apply(k)
         return q, k, v
 
-    def forward(self, x, rope, out_addend=None):
+    def forward(self, x, rope, out_addend=None, residual=None):
+        """``residual`` (optional) is added to the projected output inside the row-parallel
+        reduction, so the caller gets ``x_res + attention(x)`` without a separate add."""
         q, k, v = self.qkv(x, rope)
         b, s = q.shape[0], q.shape[1]
         out = self.core(q, k, v, True)
         out = out.reshape(b, s, self.num_local_heads * self.head_dim)
         if out_addend is not None:
             return self.out_proj(out, out_addend)
+        if residual is not None:
+            return self.out_proj(out, residual=residual)
         return self.out_proj(out)
 
 
@@ -144,8 +148,17 @@ class MLP(nn.Module):
     def hidden(self, x):
         return swiglu_ops.swiglu(multi_linear([self.gate_proj, self.up_proj], x, cat=True))
 
-    def forward(self, x):
-        return self.down_proj(self.hidden(x))
+    def forward(self, x, residual=None):
+        fused = getattr(self.gate_proj, "fused", None)
+        if fused is not None and x.is_cuda and x.dim() == 3 and x.shape[0] * x.shape[1] == fused.m_local \
+                and not getattr(self.gate_proj, "raw", False):
+            # fused sequence parallelism: gate/up output, SwiGLU and the down projection all work on
+            # rank-major rows; the reduce-scatter epilogue adds the residual
+            gu = multi_linear([self.gate_proj, self.up_proj], x, cat=True, rank_major=True)
+            return self.down_proj(swiglu_ops.swiglu(gu), residual=residual, rank_major_in=True,
+                                  shard_bs=(x.shape[0], x.shape[1]))
+        y = self.down_proj(self.hidden(x))
+        return y if residual is None else y + residual
 
 
 class RotaryTables:
@@ -227,6 +240,10 @@ class DecoderLayer(nn.Module):
     def forward(self, x, rope):
         if self.parallel_block:
             return self._forward_parallel(x, rope)
+        if getattr(self.attention.out_proj, "fused", None) is not None and not getattr(self.mlp, "is_moe", False):
+            # the residual adds ride in the reduce-scatter epilogues of out_proj and down_proj
+            h = self.attention(self.input_layernorm(x), rope, residual=x)
+            return self.mlp(self.post_attention_layernorm(h), residual=h)
         a = self.attention(self.input_layernorm(x), rope)
         y, h = self.post_attention_layernorm(a, residual=x)
         return h + self.mlp(y)
@@ -242,6 +259,19 @@ class DecoderLayer(nn.Module):
             partial = self.attention(ng, rope) + self.mlp(ng)
             return x + sp.ReduceScatterToSequenceParallelRegion.apply(partial, self.tp_group)
         return x + self.attention(n, rope) + self.mlp(n)
+
+
+def lm_head(model, x):
+    """final norm + vocabulary projection. On the fused sequence-parallel path the logits stay in
+    rank-major row order (2-D ``[tokens, V/tp]``); ``engine.loss_fn`` reorders the targets to match
+    instead of copying the much larger logits."""
+    x = model.final_norm(x)
+    proj = model.final_proj
+    fused = getattr(proj, "fused", None)
+    if fused is not None and x.is_cuda and x.dim() == 3 and x.shape[0] * x.shape[1] == fused.m_local \
+            and not proj.gather_output:
+        return multi_linear([proj], x, cat=True, rank_major=True)
+    return proj(x)
 
 
 class Llama(nn.Module):
@@ -279,5 +309,4 @@ class Llama(nn.Module):
         x = self.embedding(input_ids)
         for layer in self.decoder_layers_iter():
             x = layer(x, self.rope)
-        x = self.final_norm(x)
-        return self.final_proj(x)
+        return lm_head(self, x)

@@ -93,7 +93,8 @@ class PipelineParallel(nn.Module):
         for i in self.chunk_layers[chunk]:
             x = self.decoder_layers[str(i)](x, self.rope)
         if stage == self.stage_map.num_stages - 1:
-            x = self.final_proj(self.final_norm(x))
+            from ..models.llama import lm_head
+            x = lm_head(self, x)
         return x
 
     def forward(self, input_ids=None, position_ids=None, hidden_states=None):

@@ -101,17 +101,35 @@ class ColumnParallelLinear(nn.Module):
                 f"sp={self.sequence_parallel}, async={self.async_all_reduce}, overlap={self.overlap_comm}")
 
 
-def multi_linear(mods: Sequence[nn.Module], x: torch.Tensor, cat: bool = False):
+def _fused_ctx(mod, x):
+    """The fused tensor-parallel context of a layer if it applies to ``x`` (bf16 CUDA activations of
+    the micro-batch shape the symmetric buffers were sized for), else None."""
+    tp = getattr(mod, "fused", None)
+    if tp is None or not x.is_cuda or x.dtype != torch.bfloat16 or not mod.sequence_parallel:
+        return None
+    rows = x.numel() // x.shape[-1]
+    if rows not in (tp.m_local, tp.m_full):
+        return None
+    return tp
+
+
+def multi_linear(mods: Sequence[nn.Module], x: torch.Tensor, cat: bool = False, rank_major: bool = False):
     """Apply several bias-free projections to the same input, sharing the input collective and,
     when the weights are stored back to back, the GEMM. Returns the list of outputs (column
-    slices of one buffer), or that buffer itself ``[..., sum(out_i)]`` with ``cat=True``."""
+    slices of one buffer), or that buffer itself ``[..., sum(out_i)]`` with ``cat=True``.
+    ``rank_major`` (fused sequence-parallel path only) keeps the gathered rows in rank-major
+    order as a 2-D ``[tokens, sum(out_i)]`` tensor instead of restoring ``[b, s, ...]``."""
     first = mods[0]
     splits = [m.weight.shape[0] for m in mods]
     if not isinstance(first, ColumnParallelLinear):
         y = gemm_ops.multi_linear_cat(x, mods)
         return y if cat else list(y.split(splits, dim=-1))
     group = first.group
-    if first.raw or first.tp_world_size == 1:
+    tp = None if (first.raw or first.tp_world_size == 1) else _fused_ctx(first, x)
+    if tp is not None and x.dim() == 3 and x.shape[0] * x.shape[1] == tp.m_local:
+        from ..ops import fused_tp
+        y = fused_tp.ag_linear(x, tp, mods, batch_major=not rank_major)
+    elif first.raw or first.tp_world_size == 1:
         y = gemm_ops.multi_linear_cat(x, mods)
     elif first.sequence_parallel:
         if first.overlap_comm:
@@ -129,6 +147,18 @@ def multi_linear(mods: Sequence[nn.Module], x: torch.Tensor, cat: bool = False):
     outs = y.split(splits, dim=-1)
     return [tpc.GatherFromModelParallelRegion.apply(o, group) if m.gather_output else o
             for o, m in zip(outs, mods)]
+
+
+def install_fused_tp(model, tp_ctx) -> int:
+    """Attach a fused tensor-parallel context (``ops.fused_tp.TPFused``) to every sequence-parallel
+    column / row linear of ``model``. Returns the number of layers switched."""
+    n = 0
+    for mod in model.modules():
+        if isinstance(mod, (ColumnParallelLinear, RowParallelLinear)) and mod.sequence_parallel \
+                and not mod.overlap_comm and mod.tp_world_size > 1:
+            mod.fused = tp_ctx
+            n += 1
+    return n
 
 
 class RowParallelLinear(nn.Module):
@@ -161,21 +191,34 @@ class RowParallelLinear(nn.Module):
         with torch.no_grad():
             self.weight.copy_(master[:, lo:lo + self.input_size_per_partition])
 
-    def forward(self, x, addend=None):
+    def forward(self, x, addend=None, residual=None, rank_major_in=False, shard_bs=None):
         """``addend`` (parallel block, overlap mode) is a second partial sum folded into the
-        same reduction."""
+        same reduction; ``residual`` is added once to the reduced result. ``rank_major_in`` /
+        ``shard_bs`` describe an input that is still in the rank-major row order of the fused
+        sequence-parallel path (see ``ops.fused_tp``)."""
+        tp = _fused_ctx(self, x)
+        if tp is not None and addend is None and not self.raw:
+            from ..ops import fused_tp
+            if shard_bs is None:
+                shard_bs = (x.shape[0], x.shape[1] // self.tp_world_size)
+            return fused_tp.linear_rs(x, self.weight, tp, not rank_major_in, shard_bs, addend=residual)
+        assert not rank_major_in, "rank-major inputs exist only on the fused path"
         if self.raw or self.tp_world_size == 1:
             y = gemm_ops.linear(x, self.weight)
-            return y if addend is None else y + addend
+            y = y if addend is None else y + addend
+            return y if residual is None else y + residual
         if self.sequence_parallel and self.overlap_comm:
             from .sp_overlap import linear_pipelined_reduce_scatter
-            return linear_pipelined_reduce_scatter(x, self.weight, self.group, addend)
+            y = linear_pipelined_reduce_scatter(x, self.weight, self.group, addend)
+            return y if residual is None else y + residual
         y = gemm_ops.linear(x, self.weight)
         if addend is not None:
             y = y + addend
         if self.sequence_parallel:
-            return sp.ReduceScatterToSequenceParallelRegion.apply(y, self.group)
-        return tpc.ReduceFromModelParallelRegion.apply(y, self.group)
+            y = sp.ReduceScatterToSequenceParallelRegion.apply(y, self.group)
+        else:
+            y = tpc.ReduceFromModelParallelRegion.apply(y, self.group)
+        return y if residual is None else y + residual
 
     def extra_repr(self):
         return (f"in={self.in_features}/{self.tp_world_size}, out={self.out_features}, "

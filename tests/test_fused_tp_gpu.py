@@ -136,3 +136,30 @@ def _timeout_worker(rank, world):
 
 def test_bounded_wait_reports_timeout_2gpu():
     run_gpu_ranks(_timeout_worker, 2)
+
+
+def _engine_worker(rank, world):
+    """Two optimizer steps of a small Llama with TP=2 + sequence parallelism + vocabulary-parallel
+    loss: the fused-kernel path and the NCCL-collective path must agree to bf16 accuracy."""
+    from picotron_b200 import ops
+    from picotron_b200.engine import TrainEngine
+    losses = {}
+    for fused in ("1", "0"):
+        os.environ["PICO_FUSED_TP"] = fused
+        cfg = {"distributed": dict(tp_size=world, dp_size=1, sequence_parallel=True, vocab_parallel_ce=True),
+               "model": dict(name="tiny-llama-test", init_std=0.02, dtype="bfloat16", num_hidden_layers=2,
+                             hidden_size=512, intermediate_size=1024, num_attention_heads=8, num_key_value_heads=4),
+               "training": dict(seed=0, learning_rate=1e-3, seq_length=256, micro_batch_size=2,
+                                gradient_accumulation_steps=2, num_samples=512),
+               "dataset": dict(name="synthetic")}
+        eng = TrainEngine(cfg, device=torch.device("cuda", rank))
+        assert (eng.fused_tp is not None) == (fused == "1")
+        losses[fused] = [eng.train_step().item() for _ in range(3)]
+        ops.check_status("engine fused=" + fused)
+    for a, b in zip(losses["1"], losses["0"]):
+        assert abs(a - b) < 3e-2, losses
+    assert losses["1"][-1] < losses["1"][0]
+
+
+def test_engine_fused_tp_matches_nccl_path_2gpu():
+    run_gpu_ranks(_engine_worker, 2)
