@@ -7,6 +7,7 @@
 
 #include <cstring>
 
+#include "attention/attention.h"
 #include "common/host.h"
 #include "elementwise/elementwise.h"
 #include "fused/tp_comm.h"
@@ -261,6 +262,66 @@ void gemm_ex(const at::Tensor& A, const at::Tensor& B, const c10::optional<at::T
         "gemm_ex");
 }
 
+// ---------------------------------------------------------------------------------------------
+// attention
+// ---------------------------------------------------------------------------------------------
+PicoAttnParams attn_params(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o,
+                           double sm_scale, bool causal, int64_t q_pos0, int64_t k_pos0) {
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && o.dim() == 4, "attention: [b, s, h, d] tensors");
+  for (const at::Tensor* t : std::initializer_list<const at::Tensor*>{&q, &k, &v, &o}) {
+    TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->is_cuda(), "attention: bf16 CUDA tensors");
+    TORCH_CHECK(t->stride(3) == 1 && t->stride(2) == t->size(3), "attention: heads must be head_dim apart");
+  }
+  PicoAttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.batch = (int)q.size(0);
+  p.seq_q = (int)q.size(1);
+  p.seq_k = (int)k.size(1);
+  p.heads = (int)q.size(2);
+  p.kv_heads = (int)k.size(2);
+  p.head_dim = (int)q.size(3);
+  p.q_batch_stride = q.stride(0); p.q_row_stride = q.stride(1);
+  p.k_batch_stride = k.stride(0); p.k_row_stride = k.stride(1);
+  p.v_batch_stride = v.stride(0); p.v_row_stride = v.stride(1);
+  p.o_batch_stride = o.stride(0); p.o_row_stride = o.stride(1);
+  p.sm_scale = (float)sm_scale;
+  p.causal = causal;
+  p.q_pos0 = (int)q_pos0;
+  p.k_pos0 = (int)k_pos0;
+  return p;
+}
+
+void attention_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& out,
+                   at::Tensor& lse, double sm_scale, bool causal, int64_t q_pos0, int64_t k_pos0) {
+  c10::cuda::CUDAGuard guard(q.device());
+  PicoAttnParams p = attn_params(q, k, v, out, sm_scale, causal, q_pos0, k_pos0);
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous(), "attention: fp32 contiguous lse");
+  check(pico_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), (float*)lse.data_ptr(),
+                           &p, stream_of(q)),
+        "attention_fwd");
+}
+
+void attention_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
+                   const at::Tensor& dout, const at::Tensor& lse, at::Tensor& dq, at::Tensor& dk, at::Tensor& dv,
+                   at::Tensor& delta, at::Tensor& dq_accum, double sm_scale, bool causal, int64_t q_pos0,
+                   int64_t k_pos0) {
+  c10::cuda::CUDAGuard guard(q.device());
+  PicoAttnParams p = attn_params(q, k, v, out, sm_scale, causal, q_pos0, k_pos0);
+  for (const at::Tensor* t : std::initializer_list<const at::Tensor*>{&dout, &dq, &dk, &dv}) {
+    TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->dim() == 4 && t->stride(3) == 1 &&
+                    t->stride(2) == t->size(3), "attention_bwd: [b, s, h, d] bf16 tensors with packed heads");
+  }
+  TORCH_CHECK(delta.scalar_type() == at::kFloat && dq_accum.scalar_type() == at::kFloat &&
+                  dq_accum.is_contiguous() && delta.numel() >= lse.numel() && dq_accum.numel() >= q.numel(),
+              "attention_bwd: fp32 scratch too small");
+  check(pico_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                           (const float*)lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                           (float*)delta.data_ptr(), (float*)dq_accum.data_ptr(), &p, dout.stride(0),
+                           dout.stride(1), dq.stride(0), dq.stride(1), dk.stride(0), dk.stride(1), dv.stride(0),
+                           dv.stride(1), stream_of(q)),
+        "attention_bwd");
+}
+
 // Returns the 8 status words after synchronising (word 0 != 0 means a kernel gave up a wait).
 std::vector<int64_t> status_fetch() {
   int out[8] = {0};
@@ -286,6 +347,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("accumulate_bf16_into_f32", &accumulate_bf16_into_f32);
   m.def("fill_u32", &fill_u32);
   m.def("status_fetch", &status_fetch);
+  m.def("attention_fwd", &attention_fwd);
+  m.def("attention_bwd", &attention_bwd);
   m.def("symm_alloc", &symm_alloc);
   m.def("symm_open", &symm_open);
   m.def("symm_close", &symm_close);

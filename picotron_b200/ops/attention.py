@@ -75,10 +75,75 @@ def merge_attention_blocks(out, lse, blk_out, blk_lse):
     return out.float() * w_old + blk_out.float() * w_new, new_lse
 
 
+def _packed_heads(t: torch.Tensor) -> bool:
+    return t.stride(3) == 1 and t.stride(2) == t.shape[3] and (t.stride(1) * 2) % 16 == 0 \
+        and (t.stride(0) * 2) % 16 == 0 and t.data_ptr() % 16 == 0
+
+
+def flash_attention_forward(q, k, v, causal, sm_scale=None, q_pos0: int = 0, k_pos0: int = 0):
+    """tcgen05 kernel: returns (out [b, sq, H, d] bf16, lse [b, H, sq] fp32)."""
+    from . import count_launch, ext
+    b, sq, H, d = q.shape
+    scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(d)
+    q, k, v = (t if _packed_heads(t) else t.contiguous() for t in (q, k, v))
+    out = torch.empty((b, sq, H, d), device=q.device, dtype=q.dtype)
+    lse = torch.empty((b, H, sq), device=q.device, dtype=torch.float32)
+    ext().attention_fwd(q, k, v, out, lse, scale, causal, q_pos0, k_pos0)
+    count_launch()
+    return out, lse
+
+
+def flash_attention_backward(dout, q, k, v, out, lse, causal, sm_scale=None, q_pos0: int = 0, k_pos0: int = 0):
+    """tcgen05 kernel: returns (dq, dk, dv) as column slices of one ``[b, s, (H + 2*Hkv)*d]`` buffer when
+    the sequence lengths match (so a fused QKV projection can consume them without a copy)."""
+    from . import count_launch, ext
+    b, sq, H, d = q.shape
+    sk, kvh = k.shape[1], k.shape[2]
+    scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(d)
+    q, k, v, dout, out = (t if _packed_heads(t) else t.contiguous() for t in (q, k, v, dout, out))
+    if sq == sk:
+        fused = torch.empty((b, sq, (H + 2 * kvh) * d), device=q.device, dtype=q.dtype)
+        dq = fused[..., :H * d].view(b, sq, H, d)
+        dk = fused[..., H * d:(H + kvh) * d].view(b, sk, kvh, d)
+        dv = fused[..., (H + kvh) * d:].view(b, sk, kvh, d)
+    else:
+        dq = torch.empty((b, sq, H, d), device=q.device, dtype=q.dtype)
+        dk = torch.empty((b, sk, kvh, d), device=q.device, dtype=q.dtype)
+        dv = torch.empty((b, sk, kvh, d), device=q.device, dtype=q.dtype)
+    delta = torch.empty((b, H, sq), device=q.device, dtype=torch.float32)
+    dq_accum = torch.empty((b, sq, H, d), device=q.device, dtype=torch.float32)
+    ext().attention_bwd(q, k, v, out, dout, lse, dq, dk, dv, delta, dq_accum, scale, causal, q_pos0, k_pos0)
+    count_launch(4)
+    return dq, dk, dv
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale):
+        out, lse = flash_attention_forward(q, k, v, causal, sm_scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.sm_scale = causal, sm_scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, ctx.causal, ctx.sm_scale)
+        return dq, dk, dv, None, None
+
+
+def kernel_supports(q, k) -> bool:
+    return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and q.shape[2] % k.shape[2] == 0
+
+
 def attention(q, k, v, causal: bool = True, sm_scale: float | None = None) -> torch.Tensor:
-    """Whole-sequence attention. q: [b, s, H, d]; k, v: [b, s, Hkv, d] -> [b, s, H, d]."""
+    """Whole-sequence attention. q: [b, s, H, d]; k, v: [b, s, Hkv, d] -> [b, s, H, d]. bf16 CUDA
+    tensors with head_dim 64 or 128 run on the tcgen05 flash-attention kernels of this library;
+    everything else uses the torch restatement."""
+    from . import reference_ops_forced
+    if kernel_supports(q, k) and not reference_ops_forced():
+        return _FlashAttnFn.apply(q, k, v, causal, sm_scale)
     if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
-        # library flash kernel (cuDNN / FlashAttention through SDPA), GQA handled natively
         H, kvh = q.shape[2], k.shape[2]
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                            is_causal=causal, scale=sm_scale, enable_gqa=(H != kvh))
