@@ -26,6 +26,9 @@ typedef struct {
   float sm_scale;
   int causal;
   int q_pos0, k_pos0;
+  // optional: device buffer of 1024 uint64; CTA (0,0,0) of the forward kernel records globaltimer
+  // stamps of its pipeline phases there (performance debugging). NULL = off.
+  unsigned long long* trace;
 } PicoAttnParams;
 
 // out[b, sq, H, d] (bf16) and lse[b, H, sq] (fp32, natural log; -inf for rows without keys).

@@ -291,6 +291,11 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
         lse_log2 = (l == -CUDART_INF_F) ? CUDART_INF_F : l * kBwdLog2e;
         delta_r = delta[off];
       }
+      // keys with index >= k_limit are invisible to this row (0 for rows that are out of range or
+      // saw no key at all in the forward pass)
+      int k_limit = p.seq_k;
+      if (p.causal) k_limit = min(k_limit, q_pos - p.k_pos0 + 1);
+      if (!valid || lse_log2 == CUDART_INF_F) k_limit = 0;
       if (!all_agree_128(mbar_wait(sdp_full, it & 1, abort_word, status, 2100))) {
         alive = false;
         break;
@@ -305,11 +310,13 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
         tmem_ld_32x32b_x32(tmem_dp + lane_base + c * 32, dpv);
         tmem_ld_wait();
         float pr[32], ds[32];
+        // columns [0, lim) of this chunk are visible to this query row (branch-free masking)
+        const int lim = k_limit - (k0 + c * 32);
+        const float neg_lse = (lse_log2 == CUDART_INF_F) ? 0.f : -lse_log2;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int kidx = k0 + c * 32 + i;
-          const bool masked = !valid || kidx >= p.seq_k || (p.causal && p.k_pos0 + kidx > q_pos);
-          const float pv = masked ? 0.f : exp2f(__uint_as_float(sv[i]) * scale_log2 - lse_log2);
+          const float e = exp2f(fmaf(__uint_as_float(sv[i]), scale_log2, neg_lse));
+          const float pv = i < lim ? e : 0.f;
           pr[i] = pv;
           ds[i] = pv * (__uint_as_float(dpv[i]) - delta_r) * p.sm_scale;
         }

@@ -41,7 +41,9 @@ struct FwdCfg {
   static constexpr int kStages = 2;
   static constexpr int kTiles = kQBytes + 2 * kStages * kKVBytes + kPBytes;
   static constexpr int kNumBars = 1 + 3 * kStages + 3;   // q, k_full/v_full/kv_empty per stage, s_full, p_ready, pv_done
-  static constexpr int kSmemBytes = kTiles + kNumBars * 8 + 16 + 1024;
+  // no alignment slack: the kernel has no static shared memory, so the dynamic window starts on a
+  // 1024-byte boundary (checked at run time); this keeps two CTAs per SM for head_dim 64
+  static constexpr int kSmemBytes = kTiles + 256;
   static constexpr int kTmemCols = 256;                  // S: 128 columns, O: D (<= 128) columns
   static constexpr int kPanels = D / 64;                 // 64-element (128-byte) column panels of Q/K/V
 };
@@ -56,8 +58,11 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
                  float* __restrict__ lse, const PicoAttnParams p, int* status) {
   using Cfg = FwdCfg<D>;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {   // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) report_error(status, PICO_ERR_BOUNDS, 1999, (int)(smem_u32(smem) & 1023u));
+    return;
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::kQBytes;                       // [stage]
   uint8_t* sV = sK + Cfg::kStages * Cfg::kKVBytes;       // [stage]
@@ -118,6 +123,12 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
   const uint32_t tmem_base = *tmem_ptr_smem;
   const uint32_t tmem_s = tmem_base;          // columns [0, 128)
   const uint32_t tmem_o = tmem_base + 128;    // columns [128, 128 + D)
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  int trace_n = 0;
+#define PICO_STAMP(base)                                                             \
+  do {                                                                               \
+    if (tracing && trace_n < 250) p.trace[(base) + trace_n++] = global_timer_ns();   \
+  } while (0)
 
   if (warp == 4) {
     // ------------------------------------------------------------ TMA + MMA issue (one thread)
@@ -154,7 +165,9 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
           }
           load_kv(j + 1);
         }
+        PICO_STAMP(0);
         if (!mbar_wait(&k_full[s], ph, abort_word, status, 1020)) break;
+        PICO_STAMP(0);
         tc_fence_after();
         const uint32_t q_addr = smem_u32(sQ);
         const uint32_t k_addr = smem_u32(sK + s * Cfg::kKVBytes);
@@ -165,7 +178,9 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
                         umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
         }
         tc_commit(s_full);
+        PICO_STAMP(0);
         if (!mbar_wait(p_ready, j & 1, abort_word, status, 1030)) break;
+        PICO_STAMP(0);
         if (!mbar_wait(&v_full[s], ph, abort_word, status, 1040)) break;
         tc_fence_after();
         const uint32_t p_addr = smem_u32(sP);
@@ -192,7 +207,9 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
     float l_run = 0.f;
     bool alive = true;
     for (int j = 0; j < num_kv; ++j) {
+      if (threadIdx.x == 0) PICO_STAMP(512);
       const bool ok = mbar_wait(s_full, j & 1, abort_word, status, 1100);
+      if (threadIdx.x == 0) PICO_STAMP(512);
       int all_ok;
       asm volatile(
           "{\n\t"
@@ -212,23 +229,40 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
       const int k_base = j * kBlockN;
       const bool need_mask = (p.causal && (p.k_pos0 + k_base + kBlockN - 1 > p.q_pos0 + q0)) ||
                              (k_base + kBlockN > p.seq_k);
-      // pass 1: row maximum of this block
+      // pass 1: row maximum of this block (branch-free inner loops: the mask is applied with
+      // selects and only on blocks that need it; four independent running maxima)
       float mx = -CUDART_INF_F;
+      // keys with index >= k_limit are invisible to this row
+      int k_limit = p.seq_k;
+      if (p.causal) k_limit = min(k_limit, q_pos - p.k_pos0 + 1);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, v);
         tmem_ld_wait();
+        float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, m2 = -CUDART_INF_F, m3 = -CUDART_INF_F;
+        if (need_mask) {
+          const int lim = k_limit - (k_base + c * 32);   // columns [0, lim) of this chunk are visible
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float sc = __uint_as_float(v[i]) * scale_log2;
-          if (need_mask) {
-            const int kidx = k_base + c * 32 + i;
-            if (kidx >= p.seq_k || (p.causal && p.k_pos0 + kidx > q_pos)) sc = -CUDART_INF_F;
+          for (int i = 0; i < 32; i += 4) {
+            m0 = fmaxf(m0, i + 0 < lim ? __uint_as_float(v[i + 0]) : -CUDART_INF_F);
+            m1 = fmaxf(m1, i + 1 < lim ? __uint_as_float(v[i + 1]) : -CUDART_INF_F);
+            m2 = fmaxf(m2, i + 2 < lim ? __uint_as_float(v[i + 2]) : -CUDART_INF_F);
+            m3 = fmaxf(m3, i + 3 < lim ? __uint_as_float(v[i + 3]) : -CUDART_INF_F);
           }
-          mx = fmaxf(mx, sc);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(v[i + 0]));
+            m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+          }
         }
+        mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
       }
+      mx *= scale_log2;   // scale > 0, so the maximum commutes with the scaling
+      if (threadIdx.x == 0) PICO_STAMP(512);
       const float m_new = fmaxf(m_run, mx);
       const bool grow = (m_new - m_run > kRescaleThreshold) || (m_run == -CUDART_INF_F);
       const float m_use = grow ? m_new : m_run;
@@ -256,17 +290,29 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
         tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, v);
         tmem_ld_wait();
         float pr[32];
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        // exp2(s*scale - m) as one fused multiply-add per element; a row that has seen no key yet
+        // (m = -inf) gets offset 0 and is masked entirely through lim = 0
+        const float neg_m = (m_run == -CUDART_INF_F) ? 0.f : -m_run;
+        if (need_mask || m_run == -CUDART_INF_F) {
+          const int lim = (m_run == -CUDART_INF_F) ? 0 : k_limit - (k_base + c * 32);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float sc = __uint_as_float(v[i]) * scale_log2;
-          bool masked = (m_run == -CUDART_INF_F);
-          if (need_mask) {
-            const int kidx = k_base + c * 32 + i;
-            masked = masked || kidx >= p.seq_k || (p.causal && p.k_pos0 + kidx > q_pos);
+          for (int i = 0; i < 32; ++i) {
+            const float e = exp2f(fmaf(__uint_as_float(v[i]), scale_log2, neg_m));
+            pr[i] = i < lim ? e : 0.f;
           }
-          pr[i] = masked ? 0.f : exp2f(sc - m_run);
-          sum += pr[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pr[i] = exp2f(fmaf(__uint_as_float(v[i]), scale_log2, neg_m));
         }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          s0 += pr[i + 0];
+          s1 += pr[i + 1];
+          s2 += pr[i + 2];
+          s3 += pr[i + 3];
+        }
+        sum += (s0 + s1) + (s2 + s3);
         uint8_t* panel = prow + (c >> 1) * 16384;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
@@ -283,6 +329,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
+      if (threadIdx.x == 0) PICO_STAMP(512);
     }
     // ---- epilogue
     if (alive) {

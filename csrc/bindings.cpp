@@ -292,9 +292,14 @@ PicoAttnParams attn_params(const at::Tensor& q, const at::Tensor& k, const at::T
 }
 
 void attention_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& out,
-                   at::Tensor& lse, double sm_scale, bool causal, int64_t q_pos0, int64_t k_pos0) {
+                   at::Tensor& lse, double sm_scale, bool causal, int64_t q_pos0, int64_t k_pos0,
+                   const c10::optional<at::Tensor>& trace) {
   c10::cuda::CUDAGuard guard(q.device());
   PicoAttnParams p = attn_params(q, k, v, out, sm_scale, causal, q_pos0, k_pos0);
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->scalar_type() == at::kLong && trace->numel() >= 1024, "trace: int64[1024]");
+    p.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
+  }
   TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous(), "attention: fp32 contiguous lse");
   check(pico_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), (float*)lse.data_ptr(),
                            &p, stream_of(q)),

@@ -84,13 +84,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. `abort_word` lives in shared memory; once any role sets it, every wait
 // in the CTA gives up immediately. Returns false when the wait was abandoned.
 constexpr uint64_t PICO_MBAR_TIMEOUT_NS = 2000ull * 1000ull * 1000ull;  // 2 s
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word,
                                           int* status, int site) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // poll without suspending first: hand-offs between the roles of a CTA are on the critical path
+  // and a suspended try_wait wakes up late
+#pragma unroll 1
+  for (int i = 0; i < 2048; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
   uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {

@@ -88,7 +88,7 @@ def flash_attention_forward(q, k, v, causal, sm_scale=None, q_pos0: int = 0, k_p
     q, k, v = (t if _packed_heads(t) else t.contiguous() for t in (q, k, v))
     out = torch.empty((b, sq, H, d), device=q.device, dtype=q.dtype)
     lse = torch.empty((b, H, sq), device=q.device, dtype=torch.float32)
-    ext().attention_fwd(q, k, v, out, lse, scale, causal, q_pos0, k_pos0)
+    ext().attention_fwd(q, k, v, out, lse, scale, causal, q_pos0, k_pos0, None)
     count_launch()
     return out, lse
 

@@ -16,7 +16,7 @@ def _run_fwd(q, k, v, causal, q_pos0=0, k_pos0=0):
     b, sq, H, d = q.shape
     out = torch.empty((b, sq, H, d), device=q.device, dtype=q.dtype)
     lse = torch.empty((b, H, sq), device=q.device, dtype=torch.float32)
-    ops.ext().attention_fwd(q, k, v, out, lse, d ** -0.5, causal, q_pos0, k_pos0)
+    ops.ext().attention_fwd(q, k, v, out, lse, d ** -0.5, causal, q_pos0, k_pos0, None)
     ops.check_status("attention fwd")
     return out, lse
 
