@@ -15,7 +15,7 @@
 // copying. delta = rowsum(dO * O) comes from a small pre-pass; the dQ accumulator is converted to
 // bf16 by a post-pass.
 //
-// Roles: warp 4 (one thread) issues all TMA loads and tcgen05.mma; warps 0-3 do the softmax
+// Roles: warp 8 (one thread) issues all TMA loads and tcgen05.mma; warps 0-7 do the softmax
 // arithmetic and all epilogues. Every wait is bounded.
 #include <cuda_bf16.h>
 #include <math_constants.h>
@@ -30,7 +30,8 @@ namespace pico {
 
 constexpr int kBM = 128;   // query rows per step
 constexpr int kBN = 128;   // keys per CTA
-constexpr int kBwdThreads = 160;
+constexpr int kBwdSoftmaxThreads = 256;   // two threads per query row, 64 key columns each
+constexpr int kBwdThreads = kBwdSoftmaxThreads + 32;
 constexpr float kBwdLog2e = 1.4426950408889634f;
 
 template <int D>
@@ -98,14 +99,14 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
   }
 }
 
-// uniform yes/no across the 128 softmax threads (they share named barriers afterwards)
+// uniform yes/no across the 256 softmax threads (they share named barriers afterwards)
 __device__ __forceinline__ int all_agree_128(bool ok) {
   int all_ok;
   asm volatile(
       "{\n\t"
       ".reg .pred p, q;\n\t"
       "setp.ne.b32 p, %1, 0;\n\t"
-      "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+      "barrier.cta.red.and.pred q, 1, 256, p;\n\t"
       "selp.u32 %0, 1, 0, q;\n\t"
       "}\n"
       : "=r"(all_ok)
@@ -167,9 +168,9 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
       mbar_init(&qdo_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 128);
+    mbar_init(pds_ready, kBwdSoftmaxThreads);
     mbar_init(dq_full, 1);
-    mbar_init(s_free, 128);
+    mbar_init(s_free, kBwdSoftmaxThreads);
     *abort_word = 0;
     mbar_fence_init();
     tma_prefetch_desc(&maps.q);
@@ -178,7 +179,7 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
     tma_prefetch_desc(&maps.dout);
     tma_prefetch_desc(&maps.dq_accum);
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_ptr_smem, Cfg::kTmemCols);
     tmem_relinquish();
   }
@@ -190,8 +191,11 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
   const uint32_t tmem_dp = tmem_base + 128;
   const uint32_t tmem_dv = tmem_base + 256;
   const uint32_t tmem_dk = tmem_base + 256 + D;
+  // head_dim 64 leaves room for a separate dQ accumulator, so S/dP of the next step can be issued
+  // while the dQ tile of this step is still being drained; head_dim 128 reuses the S columns
+  const uint32_t tmem_dq = (D == 64) ? tmem_base + 384 : tmem_s;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0 && total > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);   // S, dP: both operands K-major
       constexpr uint32_t idesc_t = umma_idesc_bf16(128, D, 1, 1);     // dV, dK: both operands MN-major
@@ -215,20 +219,15 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
         tma_load_4d(sV + pn * 16384, &maps.v, kv_full, pn * 64, kv_head, k0, batch);
       }
       load_qdo(0);
+      if (Cfg::kStages > 1 && total > 1) load_qdo(1);
       bool ok = mbar_wait(kv_full, 0, abort_word, status, 2000);
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sdS);
-      for (int it = 0; it < total && ok; ++it) {
+      // S = Q K^T and dP = dO V^T of step `it`
+      auto issue_sdp = [&](int it) -> bool {
         const int st = it % Cfg::kStages;
-        const uint32_t ph = (it / Cfg::kStages) & 1;
-        if (Cfg::kStages > 1 && it + 1 < total) {
-          const int st2 = (it + 1) % Cfg::kStages;
-          if (it + 1 >= Cfg::kStages &&
-              !mbar_wait(&qdo_empty[st2], (((it + 1) / Cfg::kStages) - 1) & 1, abort_word, status, 2010)) break;
-          load_qdo(it + 1);
-        }
-        if (!mbar_wait(&qdo_full[st], ph, abort_word, status, 2020)) break;
-        if (it >= 1 && !mbar_wait(s_free, (it - 1) & 1, abort_word, status, 2030)) break;
+        if (!mbar_wait(&qdo_full[st], (it / Cfg::kStages) & 1, abort_word, status, 2020)) return false;
+        if (D != 64 && it >= 1 && !mbar_wait(s_free, (it - 1) & 1, abort_word, status, 2030)) return false;
         tc_fence_after();
         const uint32_t q_addr = smem_u32(sQ + st * Cfg::kTile);
         const uint32_t do_addr = smem_u32(sdO + st * Cfg::kTile);
@@ -245,8 +244,15 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
                         idesc_s, kk != 0 ? 1u : 0u);
         }
         tc_commit(sdp_full);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int it = 0; it < total && ok; ++it) {
+        const int st = it % Cfg::kStages;
         if (!mbar_wait(pds_ready, it & 1, abort_word, status, 2040)) break;
         tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + st * Cfg::kTile);
+        const uint32_t do_addr = smem_u32(sdO + st * Cfg::kTile);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {   // contraction over the 128 query rows, 16 per step
           tc_mma_f16_ss(tmem_dv, umma_smem_desc(p_addr + kk * 2048, 16384, 1024),
@@ -260,21 +266,31 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {   // contraction over the 128 keys
           const uint32_t a_off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          tc_mma_f16_ss(tmem_s, umma_smem_desc(ds_addr + a_off, 16, 1024),
+          tc_mma_f16_ss(tmem_dq, umma_smem_desc(ds_addr + a_off, 16, 1024),
                         umma_smem_desc(k_addr + kk * 2048, 16384, 1024), idesc_q, kk != 0 ? 1u : 0u);
         }
         tc_commit(&qdo_empty[st]);
         tc_commit(dq_full);
-        if (Cfg::kStages == 1 && it + 1 < total) {
+        if (Cfg::kStages > 1) {
+          // next step's S/dP first (its operands are already resident), then refill this stage
+          if (it + 1 < total && !issue_sdp(it + 1)) break;
+          if (it + 2 < total) {
+            if (!mbar_wait(&qdo_empty[st], (it / Cfg::kStages) & 1, abort_word, status, 2050)) break;
+            load_qdo(it + 2);
+          }
+        } else if (it + 1 < total) {
           if (!mbar_wait(&qdo_empty[0], it & 1, abort_word, status, 2050)) break;
           load_qdo(it + 1);
+          if (!issue_sdp(it + 1)) break;
         }
       }
     }
   } else {
-    const int row = warp * 32 + lane;
+    // warps w and w+4 share TMEM lane quarter w%4 (rows) and split the columns in halves
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
     const int et = threadIdx.x;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const float scale_log2 = p.sm_scale * kBwdLog2e;
     bool alive = true;
     for (int it = 0; it < total; ++it) {
@@ -304,7 +320,7 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
       uint8_t* prow = sP + row * 128;
       uint8_t* dsrow = sdS + row * 128;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t sv[32], dpv[32];
         tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, sv);
         tmem_ld_32x32b_x32(tmem_dp + lane_base + c * 32, dpv);
@@ -348,9 +364,9 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
       }
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, v);
+        tmem_ld_32x32b_x32(tmem_dq + lane_base + c * 32, v);
         tmem_ld_wait();
         uint8_t* srow = staging + c * 16384 + row * 128;
 #pragma unroll
@@ -361,7 +377,7 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
       tc_fence_before();
       mbar_arrive(s_free);
       fence_proxy_async_smem();
-      named_barrier_sync(2, 128);
+      named_barrier_sync(2, kBwdSoftmaxThreads);
       if (et == 0) {
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c)
@@ -369,7 +385,7 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
         tma_store_commit();
         tma_store_wait_read<0>();
       }
-      named_barrier_sync(2, 128);
+      named_barrier_sync(2, kBwdSoftmaxThreads);
     }
     // ---- dK / dV of this key block
     if (alive) {
@@ -382,7 +398,7 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
         const uint32_t src = which == 0 ? tmem_dv : tmem_dk;
         __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t v[32];
           if (total > 0) {
             tmem_ld_32x32b_x32(src + lane_base + c * 32, v);
@@ -414,7 +430,7 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }

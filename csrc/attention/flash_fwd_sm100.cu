@@ -4,9 +4,9 @@
 //
 // One CTA handles 128 query rows of one (batch, head) and walks the key/value sequence in blocks
 // of 128:
-//   warp 4 (one thread)  : TMA loads of Q once and of K/V blocks into a 2-stage ring, and all
+//   warp 8 (one thread)  : TMA loads of Q once and of K/V blocks into a 2-stage ring, and all
 //                          tcgen05.mma issue: S(j) = Q K_j^T, then O += P_j V_j once P_j is ready
-//   warps 0-3 (128 thr.) : tcgen05.ld the S row, scale, mask, online-softmax update, write P_j as
+//   warps 0-7 (256 thr.) : tcgen05.ld the S row, scale, mask, online-softmax update, write P_j as
 //                          bf16 into swizzled shared memory (the A operand of the second GEMM),
 //                          rescale the O accumulator in TMEM when the running maximum moved,
 //                          final normalisation and store of O and the log-sum-exp
@@ -27,7 +27,8 @@ namespace pico {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kFwdThreads = 160;
+constexpr int kSoftmaxThreads = 256;   // two threads per query row, 64 key columns each
+constexpr int kFwdThreads = kSoftmaxThreads + 32;
 constexpr float kLog2e = 1.4426950408889634f;
 // only rescale the accumulator when the running max grew by more than this (log2 units);
 // smaller drifts are absorbed by the fp32 range of the un-normalised probabilities
@@ -53,7 +54,7 @@ struct FwdMaps {
 };
 
 template <int D>
-__global__ void __launch_bounds__(kFwdThreads)
+__global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict__ out,
                  float* __restrict__ lse, const PicoAttnParams p, int* status) {
   using Cfg = FwdCfg<D>;
@@ -105,7 +106,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_ready, kBlockM);
+    mbar_init(p_ready, kSoftmaxThreads);
     mbar_init(pv_done, 1);
     *abort_word = 0;
     mbar_fence_init();
@@ -113,7 +114,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
     tma_prefetch_desc(&maps.k);
     tma_prefetch_desc(&maps.v);
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_ptr_smem, Cfg::kTmemCols);
     tmem_relinquish();
   }
@@ -130,7 +131,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
     if (tracing && trace_n < 250) p.trace[(base) + trace_n++] = global_timer_ns();   \
   } while (0)
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------ TMA + MMA issue (one thread)
     if (lane == 0 && num_kv > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
@@ -157,14 +158,6 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
       for (int j = 0; j < num_kv && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (j + 1 < num_kv) {
-          if (j + 1 >= 2 &&
-              !mbar_wait(&kv_empty[(j + 1) & 1], (((j + 1) >> 1) - 1) & 1, abort_word, status, 1010)) {
-            ok = false;
-            break;
-          }
-          load_kv(j + 1);
-        }
         PICO_STAMP(0);
         if (!mbar_wait(&k_full[s], ph, abort_word, status, 1020)) break;
         PICO_STAMP(0);
@@ -178,6 +171,16 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
                         umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
         }
         tc_commit(s_full);
+        // prefetch the next K/V block while the softmax of this one runs; its stage was last read by
+        // the P V product of block j-1, which has had the whole S(j) issue to finish
+        if (j + 1 < num_kv) {
+          if (j + 1 >= 2 &&
+              !mbar_wait(&kv_empty[(j + 1) & 1], (((j + 1) >> 1) - 1) & 1, abort_word, status, 1010)) {
+            ok = false;
+            break;
+          }
+          load_kv(j + 1);
+        }
         PICO_STAMP(0);
         if (!mbar_wait(p_ready, j & 1, abort_word, status, 1030)) break;
         PICO_STAMP(0);
@@ -197,12 +200,15 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax + epilogue (128 threads)
-    const int row = warp * 32 + lane;
+    // ------------------------------------------------------------ softmax + epilogue (256 threads)
+    // warps w and w+4 share TMEM lane quarter w%4 (rows) and split the 128 key columns in halves
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    float* xchg = reinterpret_cast<float*>(sP);   // [2][128] floats, valid while no P tile is live
     const bool valid_row = (q0 + row) < p.seq_q;
     const int q_pos = p.q_pos0 + q0 + row;
     const float scale_log2 = p.sm_scale * kLog2e;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     float m_run = -CUDART_INF_F;   // running max of the scaled scores (log2 units)
     float l_run = 0.f;
     bool alive = true;
@@ -215,7 +221,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
           "{\n\t"
           ".reg .pred p, q;\n\t"
           "setp.ne.b32 p, %1, 0;\n\t"
-          "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+          "barrier.cta.red.and.pred q, 1, 256, p;\n\t"
           "selp.u32 %0, 1, 0, q;\n\t"
           "}\n"
           : "=r"(all_ok)
@@ -229,39 +235,47 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
       const int k_base = j * kBlockN;
       const bool need_mask = (p.causal && (p.k_pos0 + k_base + kBlockN - 1 > p.q_pos0 + q0)) ||
                              (k_base + kBlockN > p.seq_k);
-      // pass 1: row maximum of this block (branch-free inner loops: the mask is applied with
-      // selects and only on blocks that need it; four independent running maxima)
+      // S values of this thread's 64 columns are read from TMEM once and stay in registers for
+      // both the maximum and the exponentials (branch-free inner loops: the mask is applied with
+      // selects, and only on blocks that need it)
       float mx = -CUDART_INF_F;
       // keys with index >= k_limit are invisible to this row
       int k_limit = p.seq_k;
       if (p.causal) k_limit = min(k_limit, q_pos - p.k_pos0 + 1);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, v);
-        tmem_ld_wait();
+      uint32_t sv[2][32];
+      tmem_ld_32x32b_x32(tmem_s + lane_base + (2 * half) * 32, sv[0]);
+      tmem_ld_32x32b_x32(tmem_s + lane_base + (2 * half + 1) * 32, sv[1]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
         float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, m2 = -CUDART_INF_F, m3 = -CUDART_INF_F;
         if (need_mask) {
-          const int lim = k_limit - (k_base + c * 32);   // columns [0, lim) of this chunk are visible
+          const int lim = k_limit - (k_base + (2 * half + cc) * 32);   // columns [0, lim) are visible
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            m0 = fmaxf(m0, i + 0 < lim ? __uint_as_float(v[i + 0]) : -CUDART_INF_F);
-            m1 = fmaxf(m1, i + 1 < lim ? __uint_as_float(v[i + 1]) : -CUDART_INF_F);
-            m2 = fmaxf(m2, i + 2 < lim ? __uint_as_float(v[i + 2]) : -CUDART_INF_F);
-            m3 = fmaxf(m3, i + 3 < lim ? __uint_as_float(v[i + 3]) : -CUDART_INF_F);
+            m0 = fmaxf(m0, i + 0 < lim ? __uint_as_float(sv[cc][i + 0]) : -CUDART_INF_F);
+            m1 = fmaxf(m1, i + 1 < lim ? __uint_as_float(sv[cc][i + 1]) : -CUDART_INF_F);
+            m2 = fmaxf(m2, i + 2 < lim ? __uint_as_float(sv[cc][i + 2]) : -CUDART_INF_F);
+            m3 = fmaxf(m3, i + 3 < lim ? __uint_as_float(sv[cc][i + 3]) : -CUDART_INF_F);
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(v[i + 0]));
-            m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
-            m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+            m0 = fmaxf(m0, __uint_as_float(sv[cc][i + 0]));
+            m1 = fmaxf(m1, __uint_as_float(sv[cc][i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(sv[cc][i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(sv[cc][i + 3]));
           }
         }
         mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
       }
       mx *= scale_log2;   // scale > 0, so the maximum commutes with the scaling
+      // combine with the other half of the row (the P buffer is idle here: the previous P V
+      // product completed before this S tile was signalled)
+      xchg[half * 128 + row] = mx;
+      named_barrier_sync(3, kSoftmaxThreads);
+      mx = fmaxf(mx, xchg[(half ^ 1) * 128 + row]);
+      named_barrier_sync(3, kSoftmaxThreads);   // both halves have read before P overwrites the area
       if (threadIdx.x == 0) PICO_STAMP(512);
       const float m_new = fmaxf(m_run, mx);
       const bool grow = (m_new - m_run > kRescaleThreshold) || (m_run == -CUDART_INF_F);
@@ -269,7 +283,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
       const float alpha = (m_run == -CUDART_INF_F) ? 0.f : exp2f(m_run - m_use);
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(tmem_o + lane_base + c * 32, v);
           tmem_ld_wait();
@@ -284,11 +298,10 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
       // pass 2: probabilities -> bf16 P tile in shared memory, row sum
       float sum = 0.f;
       uint8_t* prow = sP + row * 128;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, v);
-        tmem_ld_wait();
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * half + cc;
+        const uint32_t (&v)[32] = sv[cc];
         float pr[32];
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
         // exp2(s*scale - m) as one fused multiply-add per element; a row that has seen no key yet
@@ -340,7 +353,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
           "{\n\t"
           ".reg .pred p, q;\n\t"
           "setp.ne.b32 p, %1, 0;\n\t"
-          "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+          "barrier.cta.red.and.pred q, 1, 256, p;\n\t"
           "selp.u32 %0, 1, 0, q;\n\t"
           "}\n"
           : "=r"(all_ok)
@@ -348,11 +361,14 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
           : "memory");
       if (all_ok) {
         tc_fence_after();
+        xchg[half * 128 + row] = l_run;
+        named_barrier_sync(3, kSoftmaxThreads);
+        l_run += xchg[(half ^ 1) * 128 + row];
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         __nv_bfloat16* orow =
             out + (int64_t)batch * p.o_batch_stride + (int64_t)(q0 + row) * p.o_row_stride + head * D;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t v[32];
           if (num_kv > 0) {
             tmem_ld_32x32b_x32(tmem_o + lane_base + c * 32, v);
@@ -373,7 +389,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
             }
           }
         }
-        if (valid_row && lse != nullptr) {
+        if (valid_row && lse != nullptr && half == 0) {
           const float val = l_run > 0.f ? (m_run + log2f(l_run)) / kLog2e : -CUDART_INF_F;
           lse[((int64_t)batch * p.heads + head) * p.seq_q + q0 + row] = val;
         }
@@ -388,7 +404,7 @@ flash_fwd_kernel(const __grid_constant__ FwdMaps maps, __nv_bfloat16* __restrict
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }

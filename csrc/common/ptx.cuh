@@ -104,10 +104,10 @@ constexpr uint64_t PICO_MBAR_TIMEOUT_NS = 2000ull * 1000ull * 1000ull;  // 2 s
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word,
                                           int* status, int site) {
-  // poll without suspending first: hand-offs between the roles of a CTA are on the critical path
-  // and a suspended try_wait wakes up late
+  // a few non-suspending polls catch hand-offs that are about to complete; after that the
+  // suspending form is used so that waiting warps do not take issue slots from working ones
 #pragma unroll 1
-  for (int i = 0; i < 2048; ++i)
+  for (int i = 0; i < 16; ++i)
     if (mbar_test_wait(bar, parity)) return true;
   uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
