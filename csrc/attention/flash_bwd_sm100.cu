@@ -38,8 +38,11 @@ template <int D>
 struct BwdCfg {
   static constexpr int kTile = 128 * D * 2;                 // one bf16 [128, D] tile
   static constexpr int kStages = (D == 64) ? 2 : 1;         // Q_i / dO_i ring depth
-  static constexpr int kPds = 2 * 128 * 128 * 2;            // P and dS tiles (also the dQ staging)
-  static constexpr int kTiles = 2 * kTile + kStages * 2 * kTile + kPds;
+  static constexpr int kPds = 2 * 128 * 128 * 2;            // P and dS tiles
+  // fp32 dQ staging tile: its own buffer for head_dim 64 (so the reduce-add of one step can still
+  // be reading it while the next step writes P/dS); aliases P/dS for head_dim 128 (no room)
+  static constexpr int kStagingOwn = (D == 64) ? 128 * D * 4 : 0;
+  static constexpr int kTiles = 2 * kTile + kStages * 2 * kTile + kPds + kStagingOwn;
   static constexpr int kNumBars = 1 + 2 * kStages + 4;      // kv, qdo_full/qdo_empty per stage, sdp_full, pds_ready, dq_full, s_free
   static constexpr int kSmemBytes = kTiles + kNumBars * 8 + 16 + 1024;
   static constexpr int kPanels = D / 64;
@@ -131,7 +134,7 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
   uint8_t* sdO = sQ + Cfg::kStages * Cfg::kTile;          // [stage]
   uint8_t* sP = sdO + Cfg::kStages * Cfg::kTile;
   uint8_t* sdS = sP + 128 * 128 * 2;
-  uint8_t* staging = sP;                                  // fp32 dQ tile; aliases P and dS
+  uint8_t* staging = (D == 64) ? sdS + 128 * 128 * 2 : sP;  // fp32 dQ tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTiles);
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;
@@ -363,6 +366,10 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
         break;
       }
       tc_fence_after();
+      if (D == 64 && it > 0) {
+        if (et == 0) tma_store_wait_read<0>();
+        named_barrier_sync(2, kBwdSoftmaxThreads);
+      }
 #pragma unroll 1
       for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t v[32];
@@ -383,9 +390,11 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
         for (int c = 0; c < D / 32; ++c)
           tma_reduce_add_4d(&maps.dq_accum, staging + c * 16384, c * 32, head, q0, batch);
         tma_store_commit();
-        tma_store_wait_read<0>();
+        // with a private staging buffer the read-out may overlap the next step's P/dS phase;
+        // it only has to finish before the staging tile is written again
+        if (D != 64) tma_store_wait_read<0>();
       }
-      named_barrier_sync(2, kBwdSoftmaxThreads);
+      if (D != 64) named_barrier_sync(2, kBwdSoftmaxThreads);
     }
     // ---- dK / dV of this key block
     if (alive) {
