@@ -114,13 +114,29 @@ class Attention(nn.Module):
         k = rope.apply(k)
         return q, k, v
 
+    def _fused_local(self, x, rope):
+        """Local attention on bf16 CUDA tensors: fused QKV GEMM -> in-place RoPE -> flash attention,
+        with a backward that produces one dQKV buffer. None when the path does not apply (context
+        parallelism, CPU, unsupported head size)."""
+        if self.core is not _local_attention or not x.is_cuda or x.dtype != torch.bfloat16 \
+                or self.head_dim not in (64, 128) or attn_ops.reference_ops_forced_():
+            return None
+        qkv = multi_linear([self.q_proj, self.k_proj, self.v_proj], x, cat=True)
+        if qkv.dim() != 3 or not qkv.is_contiguous():
+            return None
+        _, _, half = rope.tables(x.device, x.dtype)
+        return attn_ops.rope_attention_fused(qkv, self.num_local_heads, self.num_local_kv_heads, self.head_dim,
+                                             half[0], half[1], rope.pos_offset)
+
     def forward(self, x, rope, out_addend=None, residual=None):
         """``residual`` (optional) is added to the projected output inside the row-parallel
         reduction, so the caller gets ``x_res + attention(x)`` without a separate add."""
-        q, k, v = self.qkv(x, rope)
-        b, s = q.shape[0], q.shape[1]
-        out = self.core(q, k, v, True)
-        out = out.reshape(b, s, self.num_local_heads * self.head_dim)
+        out = self._fused_local(x, rope)
+        if out is None:
+            q, k, v = self.qkv(x, rope)
+            b, s = q.shape[0], q.shape[1]
+            out = self.core(q, k, v, True)
+            out = out.reshape(b, s, self.num_local_heads * self.head_dim)
         if out_addend is not None:
             return self.out_proj(out, out_addend)
         if residual is not None:

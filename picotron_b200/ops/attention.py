@@ -132,6 +132,56 @@ class _FlashAttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+class _RopeAttentionFn(torch.autograd.Function):
+    """Rotary embedding + causal attention on the fused QKV projection output.
+
+    ``qkv``: [b, s, (H + 2*Hkv)*d] as the fused GEMM wrote it. q and k are rotated in place (the
+    projection output is not needed by any other backward), attention runs on strided views, and
+    the backward writes dq/dk/dv straight into one ``[b, s, (H + 2*Hkv)*d]`` buffer, un-rotates
+    dq/dk in place and hands that buffer to the projection's backward: no split / cat / clone copies.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, H, Hkv, d, cos_half, sin_half, pos_offset, causal, sm_scale):
+        from .rope import rope_inplace_
+        b, s, _ = qkv.shape
+        raw = qkv.detach()
+        q = raw[..., :H * d].view(b, s, H, d)
+        k = raw[..., H * d:(H + Hkv) * d].view(b, s, Hkv, d)
+        v = raw[..., (H + Hkv) * d:].view(b, s, Hkv, d)
+        rope_inplace_(q, cos_half, sin_half, pos_offset, 1)
+        rope_inplace_(k, cos_half, sin_half, pos_offset, 1)
+        out, lse = flash_attention_forward(q, k, v, causal, sm_scale)
+        ctx.save_for_backward(raw, out, lse, cos_half, sin_half)
+        ctx.dims = (H, Hkv, d, pos_offset, causal, sm_scale)
+        return out.view(b, s, H * d)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from .rope import rope_inplace_
+        raw, out, lse, cos_half, sin_half = ctx.saved_tensors
+        H, Hkv, d, pos_offset, causal, sm_scale = ctx.dims
+        b, s, _ = raw.shape
+        q = raw[..., :H * d].view(b, s, H, d)
+        k = raw[..., H * d:(H + Hkv) * d].view(b, s, Hkv, d)
+        v = raw[..., (H + Hkv) * d:].view(b, s, Hkv, d)
+        dq, dk, dv = flash_attention_backward(dout.reshape(b, s, H, d), q, k, v, out, lse, causal, sm_scale)
+        rope_inplace_(dq, cos_half, sin_half, pos_offset, -1)
+        rope_inplace_(dk, cos_half, sin_half, pos_offset, -1)
+        dqkv = dq._base if dq._base is not None else torch.cat(
+            [dq.reshape(b, s, -1), dk.reshape(b, s, -1), dv.reshape(b, s, -1)], dim=-1)
+        return dqkv.view(b, s, -1), None, None, None, None, None, None, None, None
+
+
+def rope_attention_fused(qkv, H, Hkv, d, cos_half, sin_half, pos_offset, causal=True, sm_scale=None):
+    return _RopeAttentionFn.apply(qkv, H, Hkv, d, cos_half, sin_half, pos_offset, causal, sm_scale)
+
+
+def reference_ops_forced_() -> bool:
+    from . import reference_ops_forced
+    return reference_ops_forced()
+
+
 def kernel_supports(q, k) -> bool:
     return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and q.shape[2] % k.shape[2] == 0
 
