@@ -10,6 +10,7 @@
 #include "attention/attention.h"
 #include "common/host.h"
 #include "elementwise/elementwise.h"
+#include "fused/dp_zero.h"
 #include "fused/tp_comm.h"
 #include "gemm/gemm.h"
 #include "runtime/symm.h"
@@ -235,6 +236,22 @@ void slot_sum(const at::Tensor& staging, int64_t world, int64_t rows, int64_t co
         "slot_sum");
 }
 
+void zero1_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, at::Tensor& m,
+                 at::Tensor& v, const c10::optional<at::Tensor>& master, int64_t shard_start, int64_t shard_len,
+                 int64_t world, int64_t my_rank, double lr, double beta1, double beta2, double eps, double wd,
+                 double bc1, double bc2, double grad_scale, int64_t local_flags, int64_t ready_slot,
+                 int64_t epoch, int64_t timeout_ms) {
+  c10::cuda::CUDAGuard guard(m.device());
+  TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && m.numel() >= shard_len &&
+                  v.numel() >= shard_len, "zero1_adamw: fp32 state of the shard's length");
+  check(pico_zero1_adamw(table_of(grad_ptrs), table_of(param_ptrs), (float*)m.data_ptr(), (float*)v.data_ptr(),
+                         (float*)mptr(master), shard_start, shard_len, (int)world, (int)my_rank, (float)lr,
+                         (float)beta1, (float)beta2, (float)eps, (float)wd, (float)bc1, (float)bc2,
+                         (float)grad_scale, reinterpret_cast<const uint32_t*>(local_flags), (int)ready_slot,
+                         (uint32_t)epoch, (uint32_t)timeout_ms, stream_of(m)),
+        "zero1_adamw");
+}
+
 // GEMM with collective fusion; see PicoGemmComm in gemm/gemm.h.
 void gemm_ex(const at::Tensor& A, const at::Tensor& B, const c10::optional<at::Tensor>& D, int64_t M,
              int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldd, bool a_mn_major, bool b_mn_major,
@@ -365,4 +382,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd_push", &rmsnorm_fwd_push);
   m.def("slot_sum", &slot_sum);
   m.def("gemm_ex", &gemm_ex);
+  m.def("zero1_adamw", &zero1_adamw);
 }

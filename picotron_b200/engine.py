@@ -61,8 +61,12 @@ class FlatOptimizer:
     (ZeRO-1: reduce-scatter gradients, update the local shard, all-gather parameters)."""
 
     def __init__(self, store: ParamStore, lr, weight_decay=0.01, betas=(0.9, 0.999), eps=1e-8, dp_group=None,
-                 zero_stage: int = 0, sp_grad_params=None, tp_group=None, expert_store=None):
+                 zero_stage: int = 0, sp_grad_params=None, tp_group=None, fused=None):
+        """``fused``: (SymmGroup, params SymmBuffer, grads SymmBuffer) selects the kernel that does the
+        gradient reduce-scatter, the sharded AdamW update and the parameter all-gather in one launch
+        over NVLink peer memory; otherwise the two collectives are NCCL calls around the AdamW kernel."""
         self.store, self.dp_group, self.zero_stage = store, dp_group, zero_stage
+        self.fused = fused
         self.dp_size = group_size(dp_group)
         self.dp_rank = group_rank(dp_group)
         self.sp_grad_params = list(sp_grad_params or [])
@@ -92,9 +96,33 @@ class FlatOptimizer:
             p.main_grad.copy_(flat[off:off + p.numel()].view_as(p.main_grad))
             off += p.numel()
 
+    READY_SLOT, DONE_SLOT = 10, 11
+
+    def _fused_step(self, grad_scale: float):
+        from .ops import count_launch, ext
+        sg, pbuf, gbuf = self.fused
+        a = self.adam
+        a.step_count += 1
+        b1, b2 = a.betas
+        shard = self.store.numel // self.dp_size
+        ready = sg.next_epoch(self.READY_SLOT)
+        sg.signal(self.READY_SLOT, ready)                      # my gradients are final
+        ext().zero1_adamw(gbuf.ptrs, pbuf.ptrs, a.exp_avg, a.exp_avg_sq, a.master, self.dp_rank * shard, shard,
+                          self.dp_size, self.dp_rank, a.lr, b1, b2, a.eps, a.weight_decay,
+                          1.0 - b1 ** a.step_count, 1.0 - b2 ** a.step_count, grad_scale / self.dp_size,
+                          sg.flags.local_ptr, self.READY_SLOT, ready, 60000)
+        count_launch()
+        done = sg.next_epoch(self.DONE_SLOT)
+        sg.signal(self.DONE_SLOT, done)                        # my shard is written everywhere
+        sg.wait(self.DONE_SLOT, done, 60000)                   # ... and so is everyone else's
+        self.store.flat_grads.zero_()
+
     def step(self, grad_scale: float = 1.0):
         self.reduce_sequence_parallel_grads()
         st = self.store
+        if self.fused is not None and self.dp_size > 1 and self.zero_stage >= 1:
+            self._fused_step(grad_scale)
+            return
         if self.dp_size > 1:
             if self.zero_stage >= 1:
                 dist.reduce_scatter_tensor(self.shard_grads, st.flat_grads, group=self.dp_group)
@@ -173,7 +201,21 @@ class TrainEngine:
         model.to(self.dtype).to(self.device)
         self.model = model
         self.flat = self.device.type == "cuda" and self.dtype == torch.bfloat16
-        self.store = ParamStore(model, pad_to_multiple=max(1, self._grad_group_size())) if self.flat else None
+        self.dp_symm = None
+        allocator = None
+        if self.flat and self._use_fused_dp():
+            # flat parameters and gradients live in symmetric memory so the optimizer kernel can
+            # read every replica's gradients and write every replica's parameters directly
+            from .runtime.symm import SymmGroup
+            self.dp_symm = SymmGroup(self._grad_group(), device=self.device)
+            self._symm_flat = []
+
+            def allocator(numel, dtype):
+                buf = self.dp_symm.alloc(numel * torch.tensor([], dtype=dtype).element_size())
+                self._symm_flat.append(buf)
+                return buf.view(dtype, (numel,))
+        self.store = ParamStore(model, pad_to_multiple=max(1, self._grad_group_size()),
+                                allocator=allocator) if self.flat else None
         self.fused_tp = None
         self._maybe_install_fused_tp()
 
@@ -198,6 +240,15 @@ class TrainEngine:
         self.fused_tp = TPFused(sg, m_local, self.model_config.hidden_size)
         install_fused_tp(self.model, self.fused_tp)
 
+    def _use_fused_dp(self) -> bool:
+        """ZeRO-1 through the peer-memory optimizer kernel (``csrc/fused/dp_zero.cu``): needs the
+        flat bf16 path, a gradient-reduction group of 2..8 GPUs and zero_stage >= 1;
+        ``PICO_FUSED_DP=0`` keeps the NCCL reduce-scatter / all-gather."""
+        import os
+        n = self._grad_group_size()
+        return (self.cfg["distributed"]["zero_stage"] >= 1 and 1 < n <= 8
+                and os.environ.get("PICO_FUSED_DP", "1") != "0")
+
     def _grad_group(self):
         m = self.pgm
         if self.cfg["distributed"]["ep_as_dp"] and m.ep_world_size > 1:
@@ -219,7 +270,9 @@ class TrainEngine:
             self.optimizer = FlatOptimizer(self.store, lr=t["learning_rate"], weight_decay=t["weight_decay"],
                                            dp_group=self._grad_group() if self._grad_group_size() > 1 else None,
                                            zero_stage=d["zero_stage"], sp_grad_params=sp_params,
-                                           tp_group=m.tp_group)
+                                           tp_group=m.tp_group,
+                                           fused=(self.dp_symm, self._symm_flat[0], self._symm_flat[1])
+                                           if self.dp_symm is not None else None)
             self.dp_model = self.model
             return
         from .parallel.data_parallel import DataParallelBucket, DataParallelNaive

@@ -48,7 +48,9 @@ def _fusion_groups(model: nn.Module):
 
 class ParamStore:
     def __init__(self, model: nn.Module, with_grads: bool = True, grad_dtype: torch.dtype = torch.float32,
-                 pad_to_multiple: int = 1):
+                 pad_to_multiple: int = 1, allocator=None):
+        """``allocator(numel, dtype) -> 1-D tensor`` lets the caller place the flat buffers in special
+        memory (symmetric memory for the fused data-parallel optimizer); default: ordinary tensors."""
         params = [p for p in model.parameters() if p.requires_grad]
         assert params, "model has no trainable parameters"
         dtype, device = params[0].dtype, params[0].device
@@ -95,8 +97,13 @@ class ParamStore:
         self.numel = total
         self.params = order
         self.offsets = offsets
-        self.flat_params = torch.zeros(total, dtype=dtype, device=device)
-        self.flat_grads = torch.zeros(total, dtype=grad_dtype, device=device) if with_grads else None
+        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
+        self.flat_params = alloc(total, dtype)
+        self.flat_grads = alloc(total, grad_dtype) if with_grads else None
+        if allocator is not None:
+            self.flat_params.zero_()
+            if self.flat_grads is not None:
+                self.flat_grads.zero_()
         with torch.no_grad():
             for p in order:
                 o = offsets[id(p)]

@@ -163,3 +163,37 @@ def _engine_worker(rank, world):
 
 def test_engine_fused_tp_matches_nccl_path_2gpu():
     run_gpu_ranks(_engine_worker, 2)
+
+
+def _dp_engine_worker(rank, world):
+    """DP=2 + ZeRO-1: the peer-memory optimizer kernel (reduce-scatter + AdamW + all-gather in one
+    launch) against the NCCL reduce-scatter / all-gather path."""
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.engine import TrainEngine
+    results = {}
+    for fused in ("1", "0"):
+        os.environ["PICO_FUSED_DP"] = fused
+        pgm.process_group_manager = None
+        cfg = {"distributed": dict(tp_size=1, dp_size=world, zero_stage=1),
+               "model": dict(name="tiny-llama-test", init_std=0.02, dtype="bfloat16", num_hidden_layers=2,
+                             hidden_size=512, intermediate_size=1024, num_attention_heads=8, num_key_value_heads=4),
+               "training": dict(seed=0, learning_rate=1e-3, seq_length=256, micro_batch_size=2,
+                                gradient_accumulation_steps=2, num_samples=512),
+               "dataset": dict(name="synthetic")}
+        eng = TrainEngine(cfg, device=torch.device("cuda", rank))
+        assert (eng.dp_symm is not None) == (fused == "1")
+        losses = [eng.train_step().item() for _ in range(3)]
+        ops.check_status("dp engine fused=" + fused)
+        results[fused] = (losses, eng.store.flat_params.float().clone())
+        # every replica must hold identical parameters after the step
+        ref = results[fused][1].clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(ref, results[fused][1]), "replicas diverged"
+    for a, b in zip(results["1"][0], results["0"][0]):
+        assert abs(a - b) < 2e-2, (results["1"][0], results["0"][0])
+    rel = (results["1"][1] - results["0"][1]).norm() / results["0"][1].norm()
+    assert rel < 1e-2, rel
+
+
+def test_engine_fused_zero1_matches_nccl_path_2gpu():
+    run_gpu_ranks(_dp_engine_worker, 2)
