@@ -65,6 +65,23 @@ extern "C" int pico_rmsnorm_bwd(const void* dy, const void* h, const void* w, co
     return -2;
   }
   const int grid = pico_rmsnorm_bwd_num_partials();
+  if (H % 256 == 0 && H <= 2048) {
+    const __nv_bfloat16* a = (const __nv_bfloat16*)dy;
+    const __nv_bfloat16* b = (const __nv_bfloat16*)h;
+    const __nv_bfloat16* c = (const __nv_bfloat16*)w;
+    const __nv_bfloat16* d = (const __nv_bfloat16*)dres;
+    __nv_bfloat16* o = (__nv_bfloat16*)dh;
+    switch (H / 256) {
+#define PICO_W(N) case N: pico::rmsnorm_bwd_warp_kernel<N><<<grid, pico::kNormThreads, 0, stream>>>(a, b, c, rstd, d, o, dw_partial, rows, H); break;
+      PICO_W(1) PICO_W(2) PICO_W(3) PICO_W(4) PICO_W(5) PICO_W(6) PICO_W(7) PICO_W(8)
+#undef PICO_W
+    }
+    pico::colsum_kernel<<<(H + 31) / 32, 256, 0, stream>>>(dw_partial, grid, H, dw_f32,
+                                                             (__nv_bfloat16*)dw_bf16, accumulate);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) pico_host::set_error("rmsnorm_bwd: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
   int rc = pico::pick_nv(H, [&](auto nv) {
     pico::rmsnorm_bwd_kernel<decltype(nv)::value><<<grid, pico::kNormThreads, 0, stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd,
@@ -72,7 +89,7 @@ extern "C" int pico_rmsnorm_bwd(const void* dy, const void* h, const void* w, co
     return 0;
   });
   if (rc) return rc;
-  pico::colsum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, grid, H, dw_f32,
+  pico::colsum_kernel<<<(H + 31) / 32, 256, 0, stream>>>(dw_partial, grid, H, dw_f32,
                                                            (__nv_bfloat16*)dw_bf16, accumulate);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) pico_host::set_error("rmsnorm_bwd: %s", cudaGetErrorString(e));

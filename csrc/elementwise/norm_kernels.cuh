@@ -158,16 +158,103 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// Warp-per-row variant for H = 256 * NVW (NVW <= 8, i.e. H <= 2048): no block-level barrier per
+// row, each lane owns NVW vectors of 8 columns and keeps its weight-gradient partials in
+// registers; the warps of a CTA combine theirs through shared memory at the end.
+template <int NVW>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dh,
+                        float* __restrict__ dw_partial, int rows, int H) {
+  constexpr int kWarps = kNormThreads / 32;
+  __shared__ float red[kWarps][32 * 8 + 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float dw_acc[NVW][8];
+  float wv[NVW][8];
+#pragma unroll
+  for (int i = 0; i < NVW; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[i][j] = 0.f;
+    unpack8(reinterpret_cast<const uint4*>(w)[lane + i * 32], wv[i]);
+  }
+  const float inv_h = 1.f / (float)H;
+  for (int row = blockIdx.x * kWarps + warp; row < rows; row += gridDim.x * kWarps) {
+    const float rstd = rstd_in[row];
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
+    const uint4* hr = reinterpret_cast<const uint4*>(h + (size_t)row * H);
+    uint4 draw[NVW], hraw[NVW];
+#pragma unroll
+    for (int i = 0; i < NVW; ++i) {
+      draw[i] = dyr[lane + i * 32];
+      hraw[i] = hr[lane + i * 32];
+    }
+    float g[NVW][8], hv[NVW][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVW; ++i) {
+      float d[8];
+      unpack8(draw[i], d);
+      unpack8(hraw[i], hv[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        g[i][j] = d[j] * wv[i][j];
+        dot += g[i][j] * hv[i][j];
+        dw_acc[i][j] += d[j] * hv[i][j] * rstd;
+      }
+    }
+    dot = warp_sum(dot);
+    const float c = dot * inv_h * rstd * rstd * rstd;
+#pragma unroll
+    for (int i = 0; i < NVW; ++i) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rstd * g[i][j] - hv[i][j] * c;
+      if (dres) {
+        float r[8];
+        unpack8(reinterpret_cast<const uint4*>(dres + (size_t)row * H)[lane + i * 32], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      reinterpret_cast<uint4*>(dh + (size_t)row * H)[lane + i * 32] = pack8(o);
+    }
+  }
+  // combine the warps' partials (fixed order) and write this CTA's row of dw_partial
+#pragma unroll 1
+  for (int i = 0; i < NVW; ++i) {
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = dw_acc[i][j];
+    __syncthreads();
+    // 256 columns of this slice, one per thread
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kWarps; ++k) s += red[k][threadIdx.x];
+    dw_partial[(size_t)blockIdx.x * H + i * 256 + threadIdx.x] = s;
+  }
+}
+
 // dw[H] (=|+=) sum_p partial[p][H]; fixed summation order (deterministic)
 static __global__ void colsum_kernel(const float* __restrict__ partial, int nparts, int H,
-                              float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16,
-                              int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+                                     float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16,
+                                     int accumulate) {
+  // block = 32 columns x 8 row groups; each thread sums every 8th partial row of its column, the
+  // eight sub-sums are then added in a fixed order
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * H + c];
-  if (out_f32) out_f32[c] = accumulate ? out_f32[c] + s : s;
-  if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + s : s);
+  if (c < H)
+    for (int p = ry; p < nparts; p += 8) s += partial[(size_t)p * H + c];
+  red[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][cx];
+    if (out_f32) out_f32[c] = accumulate ? out_f32[c] + t : t;
+    if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + t : t);
+  }
 }
 
 }  // namespace pico

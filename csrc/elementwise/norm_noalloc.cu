@@ -77,7 +77,7 @@ extern "C" int pico_rmsnorm_bwd_noalloc(const void* dy, const void* h, const voi
     pico::rmsnorm_bwd_kernel<2><<<grid, pico::kNormThreads, 0, stream>>>(dyp, hp, wp, rstd, rp, dhp, scratch, rows, H);
   else
     pico::rmsnorm_bwd_kernel<4><<<grid, pico::kNormThreads, 0, stream>>>(dyp, hp, wp, rstd, rp, dhp, scratch, rows, H);
-  pico::colsum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, grid, H, dw_f32,
+  pico::colsum_kernel<<<(H + 31) / 32, 256, 0, stream>>>(scratch, grid, H, dw_f32,
                                                            static_cast<__nv_bfloat16*>(dw_bf16), accumulate);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
