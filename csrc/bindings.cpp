@@ -11,6 +11,7 @@
 #include "common/host.h"
 #include "elementwise/elementwise.h"
 #include "fused/dp_zero.h"
+#include "fused/ep_comm.h"
 #include "fused/tp_comm.h"
 #include "gemm/gemm.h"
 #include "runtime/symm.h"
@@ -252,6 +253,40 @@ void zero1_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_
         "zero1_adamw");
 }
 
+void ep_dispatch(const at::Tensor& tokens, const at::Tensor& row_of_slot, int64_t top_k,
+                 const std::vector<int64_t>& payload_ptrs, const std::vector<int64_t>& scale_ptrs,
+                 const std::vector<int64_t>& flag_ptrs, int64_t ep, int64_t my_rank, int64_t L, int64_t C, int64_t d,
+                 bool quant, int64_t slot, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(tokens.device());
+  TORCH_CHECK(tokens.scalar_type() == at::kBFloat16 && tokens.is_contiguous() && tokens.size(-1) == d,
+              "ep_dispatch: contiguous bf16 tokens [T, d]");
+  TORCH_CHECK(row_of_slot.scalar_type() == at::kInt && row_of_slot.numel() == ep * L * C, "ep_dispatch: int32 row_of_slot[E*C]");
+  check(pico_ep_dispatch(tokens.data_ptr(), (const int32_t*)row_of_slot.data_ptr(), (int)top_k, table_of(payload_ptrs),
+                         table_of(scale_ptrs), table_of(flag_ptrs), (int)ep, (int)my_rank, (int)L, (int)C, (int)d,
+                         quant, (int)slot, (uint32_t)epoch, stream_of(tokens)),
+        "ep_dispatch");
+}
+
+void ep_dequant(const at::Tensor& payload, const at::Tensor& scales, at::Tensor& out, int64_t rows, int64_t d,
+                int64_t local_flags, int64_t ep, int64_t slot, int64_t epoch, int64_t timeout_ms) {
+  c10::cuda::CUDAGuard guard(out.device());
+  check(pico_ep_dequant(payload.data_ptr(), (const float*)scales.data_ptr(), out.data_ptr(), rows, (int)d,
+                        reinterpret_cast<const uint32_t*>(local_flags), (int)ep, (int)slot, (uint32_t)epoch,
+                        (uint32_t)timeout_ms, stream_of(out)),
+        "ep_dequant");
+}
+
+void ep_block_exchange(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs,
+                       const std::vector<int64_t>& flag_ptrs, int64_t ep, int64_t my_rank, int64_t L, int64_t C,
+                       int64_t d, bool to_expert_major, int64_t slot, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.scalar_type() == at::kBFloat16 && src.is_contiguous() && src.numel() == ep * L * C * d,
+              "ep_block_exchange: contiguous bf16 [E*C, d]");
+  check(pico_ep_block_exchange(src.data_ptr(), table_of(dst_ptrs), table_of(flag_ptrs), (int)ep, (int)my_rank, (int)L,
+                               (int)C, (int)d, to_expert_major, (int)slot, (uint32_t)epoch, stream_of(src)),
+        "ep_block_exchange");
+}
+
 // GEMM with collective fusion; see PicoGemmComm in gemm/gemm.h.
 void gemm_ex(const at::Tensor& A, const at::Tensor& B, const c10::optional<at::Tensor>& D, int64_t M,
              int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldd, bool a_mn_major, bool b_mn_major,
@@ -383,4 +418,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("slot_sum", &slot_sum);
   m.def("gemm_ex", &gemm_ex);
   m.def("zero1_adamw", &zero1_adamw);
+  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_dequant", &ep_dequant);
+  m.def("ep_block_exchange", &ep_block_exchange);
 }

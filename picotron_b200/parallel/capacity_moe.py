@@ -35,8 +35,31 @@ def slot_assignment(expert_idx: torch.Tensor, num_experts: int) -> torch.Tensor:
     return slot
 
 
+def _capacity_moe_fused(layer, epf, tokens, expert_idx, weights, token_idx, num_tokens, slot, rounds):
+    """Same computation with the exchanges done by the peer-memory kernels of ``ops.fused_ep``: rows
+    are gathered from the tokens and (optionally) quantised while they are being sent, and arrive
+    grouped by local expert; the outputs come back indexed by (expert, slot)."""
+    from ..ops import fused_ep
+    E, L, ep, C, d = layer.num_experts, layer.num_local_experts, layer.ep_world_size, epf.C, epf.d
+    R = expert_idx.numel()
+    y = torch.zeros((num_tokens, d), device=tokens.device, dtype=torch.float32)
+    rows = torch.arange(R, device=tokens.device, dtype=torch.int32)
+    for r in range(rounds):
+        in_round = (slot >= r * C) & (slot < (r + 1) * C)
+        idx = expert_idx * C + (slot - r * C)
+        row_of_slot = torch.full((E * C,), -1, device=tokens.device, dtype=torch.int32)
+        row_of_slot[idx[in_round]] = rows[in_round]
+        x = fused_ep.dispatch(tokens, row_of_slot, layer.top_k, epf, bool(layer.ep_fp8_dispatch))   # [L, ep*C, d]
+        out = torch.stack([layer.local_experts[l](x[l]) for l in range(L)])
+        back = fused_ep.combine(out, epf)                                                           # [E*C, d]
+        sel = torch.nonzero(in_round).squeeze(1)
+        y = y.index_add(0, token_idx[sel], back[idx[sel]].float() * weights[sel].float().unsqueeze(-1))
+    dropped = (slot >= rounds * C).float().mean()
+    return y.to(tokens.dtype), dropped
+
+
 def capacity_moe(layer, routed, expert_idx, weights, token_idx, num_tokens: int, capacity: int, dropless: bool,
-                 max_rounds: int):
+                 max_rounds: int, tokens=None):
     """Returns (y [T, d] gate-weighted and summed per token, fraction of routed rows dropped)."""
     E, L, ep, d = layer.num_experts, layer.num_local_experts, layer.ep_world_size, routed.shape[1]
     C = capacity
@@ -50,6 +73,10 @@ def capacity_moe(layer, routed, expert_idx, weights, token_idx, num_tokens: int,
         rounds = int(need.item())
     y = torch.zeros((num_tokens, d), device=routed.device, dtype=routed.dtype)
     equal = [L * C] * ep
+    epf = getattr(layer, "fused_ep", None)
+    if epf is not None and routed.is_cuda and routed.dtype == torch.bfloat16 and ep > 1 and tokens is not None \
+            and epf.C == C:
+        return _capacity_moe_fused(layer, epf, tokens, expert_idx, weights, token_idx, num_tokens, slot, rounds)
     for r in range(rounds):
         sel = torch.nonzero((slot >= r * C) & (slot < (r + 1) * C)).squeeze(1)
         idx = expert_idx[sel] * C + (slot[sel] - r * C)

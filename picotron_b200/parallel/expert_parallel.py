@@ -108,6 +108,8 @@ class MoELayer(nn.Module):
         self.aux_loss = None
         self.last_dropped_fraction = None
         self._shared_stream = None
+        #: optional ``ops.fused_ep.EPFused``: capacity-mode exchanges through NVLink peer memory
+        self.fused_ep = None
 
     def reset_parameters(self):
         # experts use the same RNG stream on every EP rank so replicated parameters stay in sync
@@ -243,7 +245,7 @@ class MoELayer(nn.Module):
             from .capacity_moe import capacity_moe, compute_capacity
             cap = compute_capacity(T, self.top_k, self.num_experts, self.ep_capacity_factor)
             y, dropped = capacity_moe(self, routed, expert_idx, weights, token_idx, T, cap,
-                                      self.ep_capacity_dropless, self.ep_max_rounds)
+                                      self.ep_capacity_dropless, self.ep_max_rounds, tokens=latent)
             self.last_dropped_fraction = dropped
         else:
             if self.ep_world_size > 1 and self.ep_num_tiles > 1:

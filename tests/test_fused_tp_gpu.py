@@ -197,3 +197,48 @@ def _dp_engine_worker(rank, world):
 
 def test_engine_fused_zero1_matches_nccl_path_2gpu():
     run_gpu_ranks(_dp_engine_worker, 2)
+
+
+def _ep_worker(rank, world):
+    """Capacity-mode MoE layer on EP=2: exchanges through the peer-memory kernels (bf16 and FP8 block
+    scaled dispatch) against the NCCL all-to-all path of the same layer; outputs and gradients."""
+    import types
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.ops.fused_ep import EPFused
+    from picotron_b200.parallel.capacity_moe import compute_capacity
+    from picotron_b200.parallel.expert_parallel import MoELayer
+    from picotron_b200.runtime.symm import SymmGroup
+    pgm.setup_process_group_manager(tp_size=1, cp_size=1, pp_size=1, dp_size=1, ep_size=world)
+    dev = torch.device("cuda", rank)
+    sg = SymmGroup(pgm.get_pgm().ep_group, device=dev)
+    for fp8 in (False, True):
+        for dropless in (False, True):
+            cfg = types.SimpleNamespace(hidden_size=512, intermediate_size=256, num_experts=8, num_experts_per_tok=2,
+                                        num_shared_experts=1, norm_topk_prob=True, ep_fp8_dispatch=fp8,
+                                        ep_capacity_factor=0.75, ep_capacity_dropless=dropless, ep_max_rounds=8,
+                                        init_std=0.05, ep_overlap=False)
+            torch.manual_seed(3)
+            layer = MoELayer(cfg).to(dev).to(torch.bfloat16)
+            torch.manual_seed(10 + rank)
+            x = torch.randn(2, 256, 512, device=dev, dtype=torch.bfloat16)
+            T = 512
+            C = compute_capacity(T, 2, 8, 0.75)
+            outs = []
+            for fused in (False, True):
+                layer.fused_ep = EPFused(sg, layer.num_local_experts, C, 512) if fused else None
+                xi = x.clone().requires_grad_(True)
+                layer.zero_grad()
+                y = layer(xi)
+                y.float().square().mean().backward()
+                outs.append((y.detach().float(), xi.grad.float(),
+                             layer.local_experts[0].down_proj.weight.grad.float().clone(),
+                             layer.gate.weight.grad.float().clone()))
+            ops.check_status(f"fused ep fp8={fp8} dropless={dropless}")
+            names = ("output", "input grad", "expert weight grad", "router grad")
+            for n, a, b in zip(names, outs[1], outs[0]):
+                rel = ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+                assert rel < 3e-2, (n, fp8, dropless, rel)
+
+
+def test_fused_ep_capacity_moe_2gpu():
+    run_gpu_ranks(_ep_worker, 2)
