@@ -61,12 +61,13 @@ class FlatOptimizer:
     (ZeRO-1: reduce-scatter gradients, update the local shard, all-gather parameters)."""
 
     def __init__(self, store: ParamStore, lr, weight_decay=0.01, betas=(0.9, 0.999), eps=1e-8, dp_group=None,
-                 zero_stage: int = 0, sp_grad_params=None, tp_group=None, fused=None):
+                 zero_stage: int = 0, sp_grad_params=None, tp_group=None, fused=None, extra_grad_scale: float = 1.0):
         """``fused``: (SymmGroup, params SymmBuffer, grads SymmBuffer) selects the kernel that does the
         gradient reduce-scatter, the sharded AdamW update and the parameter all-gather in one launch
         over NVLink peer memory; otherwise the two collectives are NCCL calls around the AdamW kernel."""
         self.store, self.dp_group, self.zero_stage = store, dp_group, zero_stage
         self.fused = fused
+        self.extra_grad_scale = extra_grad_scale
         self.dp_size = group_size(dp_group)
         self.dp_rank = group_rank(dp_group)
         self.sp_grad_params = list(sp_grad_params or [])
@@ -118,6 +119,7 @@ class FlatOptimizer:
         self.store.flat_grads.zero_()
 
     def step(self, grad_scale: float = 1.0):
+        grad_scale = grad_scale * self.extra_grad_scale
         self.reduce_sequence_parallel_grads()
         st = self.store
         if self.fused is not None and self.dp_size > 1 and self.zero_stage >= 1:
@@ -141,6 +143,31 @@ class FlatOptimizer:
 
     def load_state_dict(self, sd):
         self.adam.load_state_dict(sd)
+
+
+class MultiFlatOptimizer:
+    """Several flat optimizers stepped together (dense and expert parameters reduce over different
+    groups when expert parallelism doubles as data parallelism)."""
+
+    def __init__(self, parts):
+        self.parts = list(parts)
+        self.zero_stage = self.parts[0].zero_stage
+        self.dp_size = self.parts[0].dp_size
+
+    def step(self, grad_scale: float = 1.0):
+        for p in self.parts:
+            p.step(grad_scale)
+
+    def zero_grad(self):
+        for p in self.parts:
+            p.zero_grad()
+
+    def state_dict(self):
+        return {"parts": [p.state_dict() for p in self.parts]}
+
+    def load_state_dict(self, sd):
+        for p, s in zip(self.parts, sd["parts"]):
+            p.load_state_dict(s)
 
 
 class TrainEngine:
@@ -214,8 +241,47 @@ class TrainEngine:
                 buf = self.dp_symm.alloc(numel * torch.tensor([], dtype=dtype).element_size())
                 self._symm_flat.append(buf)
                 return buf.view(dtype, (numel,))
-        self.store = ParamStore(model, pad_to_multiple=max(1, self._grad_group_size()),
-                                allocator=allocator) if self.flat else None
+        self.expert_store = None
+        if self.flat and self._split_expert_params():
+            is_expert = lambda n, p: ".local_experts." in n      # noqa: E731
+            self.store = ParamStore(model, pad_to_multiple=max(1, self._grad_group_size()), allocator=allocator,
+                                    param_filter=lambda n, p: not is_expert(n, p))
+            self.expert_store = ParamStore(model, pad_to_multiple=max(1, self.pgm.cp_dp_world_size),
+                                           param_filter=is_expert)
+        else:
+            self.store = ParamStore(model, pad_to_multiple=max(1, self._grad_group_size()),
+                                    allocator=allocator) if self.flat else None
+        self._maybe_install_fused_ep()
+
+    def _split_expert_params(self) -> bool:
+        return (self.cfg["distributed"]["ep_as_dp"] and self.pgm.ep_world_size > 1
+                and getattr(self.model_config, "num_experts", 1) > 1)
+
+    def _maybe_install_fused_ep(self):
+        """Capacity-mode MoE layers exchange rows through NVLink peer memory (``ops.fused_ep``) on the
+        flat bf16 path; ``PICO_FUSED_EP=0`` keeps the NCCL all-to-alls."""
+        import os
+        mc, m, t = self.model_config, self.pgm, self.cfg["training"]
+        self.fused_ep = None
+        if not (self.flat and m.ep_world_size > 1 and getattr(mc, "num_experts", 1) > 1
+                and (getattr(mc, "ep_capacity_factor", 0.0) or 0.0) > 0
+                and os.environ.get("PICO_FUSED_EP", "1") != "0"):
+            return
+        from .ops.fused_ep import EPFused
+        from .parallel.capacity_moe import compute_capacity
+        from .parallel.expert_parallel import MoELayer
+        from .runtime.symm import SymmGroup
+        tokens = t["micro_batch_size"] * (t["seq_length"] // m.cp_world_size)
+        if self.cfg["distributed"]["sequence_parallel"] and m.tp_world_size > 1:
+            tokens //= m.tp_world_size
+        cap = compute_capacity(tokens, mc.num_experts_per_tok, mc.num_experts, mc.ep_capacity_factor)
+        layers = [mod for mod in self.model.modules() if isinstance(mod, MoELayer)]
+        if not layers or layers[0].expert_dim % 8 != 0:
+            return
+        sg = SymmGroup(m.ep_group, device=self.device)
+        self.fused_ep = EPFused(sg, layers[0].num_local_experts, cap, layers[0].expert_dim)
+        for mod in layers:
+            mod.fused_ep = self.fused_ep
         self.fused_tp = None
         self._maybe_install_fused_tp()
 
@@ -273,12 +339,19 @@ class TrainEngine:
                                            tp_group=m.tp_group,
                                            fused=(self.dp_symm, self._symm_flat[0], self._symm_flat[1])
                                            if self.dp_symm is not None else None)
+            if self.expert_store is not None:
+                experts = FlatOptimizer(self.expert_store, lr=t["learning_rate"], weight_decay=t["weight_decay"],
+                                        dp_group=m.cp_dp_group if m.cp_dp_world_size > 1 else None,
+                                        zero_stage=d["zero_stage"], extra_grad_scale=1.0 / m.ep_world_size)
+                self.optimizer = MultiFlatOptimizer([self.optimizer, experts])
             self.dp_model = self.model
             return
-        from .parallel.data_parallel import DataParallelBucket, DataParallelNaive
+        from .parallel.data_parallel import DataParallelBucket, DataParallelExpertAware, DataParallelNaive
         from .parallel.zero import DataParallelZero, ShardedOptimizer
         self.dp_model = self.model
-        if self._grad_group_size() > 1:
+        if self._split_expert_params():
+            self.dp_model = DataParallelExpertAware(self.model, m.dense_dp_group, m.cp_dp_group)
+        elif self._grad_group_size() > 1:
             if d["zero_stage"] >= 1 or d["dp_engine"] == "zero":
                 self.dp_model = DataParallelZero(self.model, stage=max(1, d["zero_stage"]), group=self._grad_group())
                 self.optimizer = ShardedOptimizer(self.dp_model, torch.optim.AdamW, lr=t["learning_rate"],

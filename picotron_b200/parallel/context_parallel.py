@@ -38,7 +38,8 @@ class _RingAttention(torch.autograd.Function):
         comm = ContextCommunicate("fwd", group=group, send_rank=_ring_peer(group, +1),
                                   recv_rank=_ring_peer(group, -1))
         out, lse = None, None
-        cur_k, cur_v = k, v
+        cur_k, cur_v = k.contiguous(), v.contiguous()
+        use_kernel = attn_ops.kernel_supports(q, k) and not attn_ops.reference_ops_forced_()
         for step in range(n):
             if step + 1 < n:
                 next_k = comm.send_recv(cur_k)
@@ -46,15 +47,20 @@ class _RingAttention(torch.autograd.Function):
                 comm.commit()
             src = (rank - step) % n          # owner of the block in hand
             if not causal or src <= rank:
-                blk_out, blk_lse = attn_ops.attention_block(q, cur_k, cur_v, causal and src == rank, sm_scale,
-                                                            q_offset=0, k_offset=0)
+                if use_kernel:
+                    # tcgen05 flash attention on this key block; global positions give the mask
+                    blk_out, blk_lse = attn_ops.flash_attention_forward(q, cur_k, cur_v, causal, sm_scale,
+                                                                        q_pos0=rank * s_loc, k_pos0=src * s_loc)
+                else:
+                    blk_out, blk_lse = attn_ops.attention_block(q, cur_k, cur_v, causal and src == rank, sm_scale,
+                                                                q_offset=0, k_offset=0)
                 out, lse = attn_ops.merge_attention_blocks(out, lse, blk_out, blk_lse)
             if step + 1 < n:
                 comm.wait()
                 cur_k, cur_v = next_k, next_v
         out = out.to(q.dtype)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.sm_scale, ctx.causal, ctx.group = sm_scale, causal, group
+        ctx.sm_scale, ctx.causal, ctx.group, ctx.use_kernel = sm_scale, causal, group, use_kernel
         return out
 
     @staticmethod
@@ -68,7 +74,9 @@ class _RingAttention(torch.autograd.Function):
                                        recv_rank=_ring_peer(group, -1))
         dq = torch.zeros(q.shape, device=q.device, dtype=torch.float32)
         dk_acc = dv_acc = None   # fp32 accumulators travelling with the K/V block they belong to
-        cur_k, cur_v = k, v
+        cur_k, cur_v = k.contiguous(), v.contiguous()
+        s_loc = q.shape[1]
+        dout = dout.contiguous()
         for step in range(n):
             if step + 1 < n:
                 next_k = kv_comm.send_recv(cur_k)
@@ -76,8 +84,14 @@ class _RingAttention(torch.autograd.Function):
                 kv_comm.commit()
             src = (rank - step) % n
             if not causal or src <= rank:
-                bdq, bdk, bdv = attn_ops.attention_block_backward(dout, q, cur_k, cur_v, out, lse,
-                                                                  causal and src == rank, ctx.sm_scale)
+                if ctx.use_kernel:
+                    bdq, bdk, bdv = attn_ops.flash_attention_backward(dout, q, cur_k, cur_v, out, lse, causal,
+                                                                      ctx.sm_scale, q_pos0=rank * s_loc,
+                                                                      k_pos0=src * s_loc)
+                    bdk, bdv = bdk.float(), bdv.float()
+                else:
+                    bdq, bdk, bdv = attn_ops.attention_block_backward(dout, q, cur_k, cur_v, out, lse,
+                                                                      causal and src == rank, ctx.sm_scale)
                 dq += bdq
             else:
                 bdk = torch.zeros(cur_k.shape, device=q.device, dtype=torch.float32)

@@ -132,3 +132,35 @@ class DataParallelBucket(_DataParallelBase):
             bm.grad_data /= self.world_size
         for p in bm.params:
             p.grad = p.main_grad.to(p.dtype)
+
+
+class DataParallelExpertAware(_DataParallelBase):
+    """Gradient averaging when expert parallelism doubles as data parallelism (every EP rank holds
+    different tokens): dense parameters are replicated over CP x EP x DP and averaged over that
+    whole group; an expert lives on one EP rank only, so its gradient — which already contains the
+    contributions of every EP rank's tokens through the backward of the dispatch — is summed over
+    CP x DP and divided by the size of the whole group."""
+
+    def __init__(self, module: nn.Module, dense_group, expert_group, is_expert=None):
+        super().__init__(module, dense_group)
+        self.expert_group = expert_group
+        self.expert_world = group_size(expert_group)
+        is_expert = is_expert or (lambda name: ".local_experts." in name)
+        self._expert_ids = {id(p) for n, p in module.named_parameters() if is_expert(n)}
+        for p in self.module.parameters():
+            if p.requires_grad:
+                p.register_post_accumulate_grad_hook(self._hook)
+
+    def _hook(self, p):
+        if not self.require_backward_grad_sync:
+            return
+        if id(p) in self._expert_ids:
+            if self.expert_world > 1:
+                dist.all_reduce(p.grad, group=self.expert_group)
+            p.grad /= self.world_size
+        elif self.world_size > 1:
+            dist.all_reduce(p.grad, group=self.group)
+            p.grad /= self.world_size
+
+    def reset(self):
+        pass

@@ -48,11 +48,13 @@ def _fusion_groups(model: nn.Module):
 
 class ParamStore:
     def __init__(self, model: nn.Module, with_grads: bool = True, grad_dtype: torch.dtype = torch.float32,
-                 pad_to_multiple: int = 1, allocator=None):
+                 pad_to_multiple: int = 1, allocator=None, param_filter=None):
         """``allocator(numel, dtype) -> 1-D tensor`` lets the caller place the flat buffers in special
         memory (symmetric memory for the fused data-parallel optimizer); default: ordinary tensors."""
-        params = [p for p in model.parameters() if p.requires_grad]
-        assert params, "model has no trainable parameters"
+        params = [p for n, p in model.named_parameters()
+                  if p.requires_grad and (param_filter is None or param_filter(n, p))]
+        assert params, "no trainable parameters selected"
+        selected = {id(p) for p in params}
         dtype, device = params[0].dtype, params[0].device
         assert all(p.dtype == dtype and p.device == device for p in params), \
             "ParamStore needs a single parameter dtype/device (cast the model first)"
@@ -60,7 +62,7 @@ class ParamStore:
         in_group = {}
         for g in groups:
             ws = [m.weight for m in g]
-            if any(w.dim() != 2 or w.shape[1] != ws[0].shape[1] for w in ws):
+            if any(w.dim() != 2 or w.shape[1] != ws[0].shape[1] or id(w) not in selected for w in ws):
                 continue
             for w in ws:
                 in_group[id(w)] = g

@@ -242,3 +242,36 @@ def _ep_worker(rank, world):
 
 def test_fused_ep_capacity_moe_2gpu():
     run_gpu_ranks(_ep_worker, 2)
+
+
+def _cp_worker(rank, world):
+    """Ring (flash kernels per block, position offsets) and Ulysses attention on 2 GPUs in bf16 against
+    single-device attention over the full sequence."""
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.ops import attention as A
+    from picotron_b200.parallel.context_parallel import ring_attention_bshd
+    from picotron_b200.parallel.ulysses import ulysses_attention_bshd
+    pgm.setup_process_group_manager(tp_size=1, cp_size=world, pp_size=1, dp_size=1)
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    b, s, H, Hkv, d = 1, 512 * world, 8, 4, 64
+    q = torch.randn(b, s, H, d, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(b, s, Hkv, d, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(b, s, Hkv, d, device=dev, dtype=torch.bfloat16)
+    go = torch.randn(b, s, H, d, device=dev, dtype=torch.bfloat16)
+    qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref = A.attention_ref(qr, kr, vr, True)
+    ref.backward(go.float())
+    sl = slice(rank * s // world, (rank + 1) * s // world)
+    for fn in (ring_attention_bshd, ulysses_attention_bshd):
+        ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+        out = fn(ql, kl, vl, True)
+        out.backward(go[:, sl].contiguous())
+        ops.check_status(fn.__name__)
+        assert _rel(out, ref[:, sl]) < 2e-2, fn.__name__
+        for got, want in ((ql.grad, qr.grad), (kl.grad, kr.grad), (vl.grad, vr.grad)):
+            assert _rel(got, want[:, sl]) < 3e-2, fn.__name__
+
+
+def test_context_parallel_attention_2gpu():
+    run_gpu_ranks(_cp_worker, 2)

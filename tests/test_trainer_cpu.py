@@ -197,3 +197,30 @@ def test_create_config_and_train_cli(tmp_path):
     assert os.path.exists(tmp_path / "global_metrics.csv")
     rows = open(tmp_path / "global_metrics.csv").read().strip().splitlines()
     assert rows[0].startswith("run_name,status,dp,tp,pp") and len(rows) == 2
+
+
+def _ep_as_dp_worker(rank, world):
+    """EP=2 used as data parallelism for the dense weights: every EP rank trains on different tokens;
+    dense replicas must stay identical, experts (one owner each) must not be averaged away."""
+    from picotron_b200.engine import TrainEngine
+    cfg = tiny_cfg(ep_size=world, ep_as_dp=True)
+    cfg["model"].update(num_experts=4, num_experts_per_tok=2, num_shared_experts=1, intermediate_size=128,
+                        router_aux_loss_coef=0.01, num_hidden_layers=2)
+    cfg["training"].update(seq_length=64)
+    engine = TrainEngine(cfg, device=torch.device("cpu"))
+    assert engine.data_loader.dp_world_size == world and engine.data_loader.dp_rank == rank
+    losses = [engine.average_loss(engine.train_step()) for _ in range(3)]
+    assert all(l == l for l in losses)
+    for name, p in engine.model.named_parameters():
+        mine = p.detach().clone()
+        other = mine.clone()
+        dist.broadcast(other, src=0)
+        if ".local_experts." in name:
+            continue
+        assert torch.equal(mine, other), f"dense replica diverged: {name}"
+    g = engine.model.decoder_layers[0].mlp.local_experts[0].down_proj.weight
+    assert g.grad is None or torch.isfinite(g.grad).all()
+
+
+def test_ep_as_dp_keeps_dense_replicas_in_sync():
+    run_distributed(_ep_as_dp_worker, 2)
