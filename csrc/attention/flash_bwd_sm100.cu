@@ -57,26 +57,38 @@ struct BwdMaps {
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
                                   float* __restrict__ delta, PicoAttnParams p, int64_t do_batch_stride,
                                   int64_t do_row_stride) {
-  // one warp per (batch, row, head)
+  // head_dim / 8 adjacent lanes per (batch, row, head), 16 bytes of each operand per lane; the
+  // heads of a row are contiguous, so a warp reads one 512-byte run of each tensor
+  const int gsz = p.head_dim >> 3;            // 8 or 16 lanes per item
+  const int per_warp = 32 / gsz;
   const int64_t total = (int64_t)p.batch * p.seq_q * p.heads;
   const int lane = threadIdx.x & 31;
-  for (int64_t w = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5; w < total;
-       w += ((int64_t)gridDim.x * blockDim.x) >> 5) {
-    const int h = (int)(w % p.heads);
-    const int64_t t = w / p.heads;
-    const int row = (int)(t % p.seq_q);
-    const int b = (int)(t / p.seq_q);
-    const __nv_bfloat16* o = out + b * p.o_batch_stride + row * p.o_row_stride + h * p.head_dim;
-    const __nv_bfloat16* d = dout + b * do_batch_stride + row * do_row_stride + h * p.head_dim;
+  const int sub = lane / gsz, li = lane % gsz;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t w = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5; w * per_warp < total; w += warps) {
+    const int64_t item = w * per_warp + sub;
     float acc = 0.f;
-    for (int i = lane * 2; i < p.head_dim; i += 64) {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
-      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
-      acc += a.x * g.x + a.y * g.y;
-    }
+    int h = 0, row = 0, b = 0;
+    if (item < total) {
+      h = (int)(item % p.heads);
+      const int64_t t = item / p.heads;
+      row = (int)(t % p.seq_q);
+      b = (int)(t / p.seq_q);
+      const uint4 ov = *reinterpret_cast<const uint4*>(out + b * p.o_batch_stride + row * p.o_row_stride +
+                                                      h * p.head_dim + li * 8);
+      const uint4 dv = *reinterpret_cast<const uint4*>(dout + b * do_batch_stride + row * do_row_stride +
+                                                      h * p.head_dim + li * 8);
+      const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+      const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) delta[((int64_t)b * p.heads + h) * p.seq_q + row] = acc;
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(o2[i]);
+        const float2 g = __bfloat1622float2(d2[i]);
+        acc += a.x * g.x + a.y * g.y;
+      }
+    }
+    for (int off = gsz >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (item < total && li == 0) delta[((int64_t)b * p.heads + h) * p.seq_q + row] = acc;
   }
 }
 
@@ -515,7 +527,7 @@ extern "C" int pico_attention_bwd(const void* q, const void* k, const void* v, c
   const int64_t rows = (int64_t)p->batch * p->seq_q * p->heads;
   const int sms = pico_host::num_sms();
   {
-    int64_t blocks = (rows * 32 + 255) / 256;
+    int64_t blocks = (rows * (p->head_dim / 8) + 255) / 256;
     if (blocks > sms * 16) blocks = sms * 16;
     attn_delta_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, delta,
                                                       *p, do_batch_stride, do_row_stride);

@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 #include <math_constants.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "../common/host.h"
@@ -446,6 +447,11 @@ static int launch_fwd(const void* q, const void* k, const void* v, void* out, fl
   return 0;
 }
 
+// two query tiles per CTA, softmax of one overlapping the tensor-core work of the other
+// (flash_fwd_pingpong_sm100.cu)
+int launch_fwd_pingpong(const void* q, const void* k, const void* v, void* out, float* lse,
+                        const PicoAttnParams* p, cudaStream_t stream);
+
 }  // namespace pico
 
 extern "C" int pico_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
@@ -459,6 +465,13 @@ extern "C" int pico_attention_fwd(const void* q, const void* k, const void* v, v
     pico_host::set_error("attention: output must be 16-byte aligned with strides that are multiples of 8");
     return -2;
   }
+  // PICO_ATTN_FWD=single selects the one-tile-per-CTA kernel of this file (A/B comparisons)
+  static const bool single = [] {
+    const char* e = getenv("PICO_ATTN_FWD");
+    return e != nullptr && strcmp(e, "single") == 0;
+  }();
+  if (!single && (p->head_dim == 64 || p->head_dim == 128))
+    return pico::launch_fwd_pingpong(q, k, v, out, lse, p, stream);
   if (p->head_dim == 64) return pico::launch_fwd<64>(q, k, v, out, lse, p, stream);
   if (p->head_dim == 128) return pico::launch_fwd<128>(q, k, v, out, lse, p, stream);
   pico_host::set_error("attention: head_dim %d not supported (64 or 128)", p->head_dim);

@@ -314,6 +314,33 @@ void gemm_ex(const at::Tensor& A, const at::Tensor& B, const c10::optional<at::T
         "gemm_ex");
 }
 
+// Grouped GEMM over the local experts; see PicoGemmComm (tile_group / seg_start) in gemm/gemm.h.
+// mode 0: row-grouped, `groups` = tile_group [ceil(M/128)] int32; mode 1: reduction-grouped,
+// `groups` = seg_start [num_groups + 1] int32.
+void gemm_grouped(const at::Tensor& A, const at::Tensor& B, at::Tensor& D, int64_t M, int64_t N, int64_t K,
+                  int64_t lda, int64_t ldb, int64_t ldd, bool a_mn_major, bool b_mn_major, int64_t out_mode,
+                  int64_t mode, const at::Tensor& groups, int64_t num_groups, int64_t b_group_rows) {
+  c10::cuda::CUDAGuard guard(A.device());
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && D.is_cuda() && groups.is_cuda(), "gemm_grouped: CUDA tensors required");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm_grouped: bf16 operands");
+  TORCH_CHECK((out_mode == 0) == (D.scalar_type() == at::kBFloat16), "gemm_grouped: output dtype/mode mismatch");
+  TORCH_CHECK(groups.scalar_type() == at::kInt && groups.is_contiguous(), "gemm_grouped: int32 group array");
+  PicoGemmComm c;
+  memset(&c, 0, sizeof(c));
+  c.num_groups = (int)num_groups;
+  if (mode == 0) {
+    TORCH_CHECK(groups.numel() >= (M + 127) / 128, "gemm_grouped: tile_group too short");
+    c.tile_group = groups.data_ptr<int>();
+    c.b_group_rows = (int)b_group_rows;
+  } else {
+    TORCH_CHECK(groups.numel() == num_groups + 1, "gemm_grouped: seg_start needs num_groups + 1 entries");
+    c.seg_start = groups.data_ptr<int>();
+  }
+  check(pico_gemm_bf16_ex(A.data_ptr(), B.data_ptr(), D.data_ptr(), (int)M, (int)N, (int)K, (int)lda, (int)ldb,
+                          (int)ldd, a_mn_major, b_mn_major, (int)out_mode, 0, &c, stream_of(A)),
+        "gemm_grouped");
+}
+
 // ---------------------------------------------------------------------------------------------
 // attention
 // ---------------------------------------------------------------------------------------------
@@ -417,6 +444,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd_push", &rmsnorm_fwd_push);
   m.def("slot_sum", &slot_sum);
   m.def("gemm_ex", &gemm_ex);
+  m.def("gemm_grouped", &gemm_grouped);
   m.def("zero1_adamw", &zero1_adamw);
   m.def("ep_dispatch", &ep_dispatch);
   m.def("ep_dequant", &ep_dequant);

@@ -37,6 +37,20 @@ typedef struct {
   void* d_ptrs[8];
   int m_rotate_rows;
   unsigned int timeout_ms;
+  // Grouped GEMM for the experts of a mixture-of-experts layer: one launch covers every local
+  // expert. Rows of the activation matrices are expert-contiguous and every expert's segment
+  // starts on a multiple of 128 rows (padding rows are zero), so a 128-row tile never mixes experts.
+  //   row-grouped (forward / input gradient): tile_group[t] is the expert of row tile t (a device
+  //     array of ceil(M/128) ints, -1 = tile not computed); B holds num_groups matrices of
+  //     b_group_rows rows stacked along its rows ([G*N, K] for b_mn_major 0, [G*K, N] for 1).
+  //   reduction-grouped (weight gradient): D holds num_groups [M, N] blocks stacked along its rows;
+  //     block g = A[:, rows_g]^T-style product reduced over rows seg_start[g] .. seg_start[g+1]
+  //     (device array of num_groups + 1 ints, multiples of 64) of the MN-major operands. K is the
+  //     total number of rows. Blocks of empty groups are left untouched.
+  const int* tile_group;
+  int b_group_rows;
+  const int* seg_start;
+  int num_groups;
 } PicoGemmComm;
 
 int pico_gemm_bf16_ex(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb,

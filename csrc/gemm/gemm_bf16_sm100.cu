@@ -75,10 +75,23 @@ struct GemmComm {
   // with its own block (gather) or with its neighbour's (scatter)
   int m_rotate;
   unsigned long long timeout_ns;
+  // grouped GEMM (experts of a mixture-of-experts layer), see PicoGemmGroups in gemm.h
+  const int* tile_group;  // row-grouped mode: group of every 128-row tile of A / D (-1 = skip)
+  int b_group_rows;       //   rows of one group's matrix inside the stacked B
+  const int* seg_start;   // reduction-grouped mode: group g reduces over rows [seg_start[g], seg_start[g+1])
+  int num_groups;
 };
 
 struct TileCoord {
   int m, n;
+};
+
+// What one persistent-loop iteration works on. Plain GEMM: the whole K range of output tile
+// (m, n). Row-grouped: the same, with B taken from group `grp`. Reduction-grouped: output tile
+// (m, n) of group `grp` (stacked along the rows of D), reduced over that group's K blocks.
+struct TileWork {
+  int m, n, grp, kb0, kb1;
+  bool skip;
 };
 
 // Grouped rasterisation: consecutive tile indices (= CTAs running at the same time) cover a
@@ -98,6 +111,34 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
   }
   c.n = r / gsize;
   return c;
+}
+
+__device__ __forceinline__ TileWork tile_work(int tile, int num_m, int num_n, int num_kb,
+                                              const GemmComm& comm) {
+  TileWork w;
+  w.grp = 0;
+  w.kb0 = 0;
+  w.kb1 = num_kb;
+  w.skip = false;
+  if (comm.seg_start != nullptr) {
+    const int per_group = num_m * num_n;
+    w.grp = tile / per_group;
+    TileCoord c = tile_coord(tile - w.grp * per_group, num_m, num_n);
+    w.m = c.m;
+    w.n = c.n;
+    w.kb0 = __ldg(comm.seg_start + w.grp) / BK;
+    w.kb1 = __ldg(comm.seg_start + w.grp + 1) / BK;
+    w.skip = w.kb1 <= w.kb0;
+    return w;
+  }
+  TileCoord c = tile_coord(tile, num_m, num_n, comm.m_rotate);
+  w.m = c.m;
+  w.n = c.n;
+  if (comm.tile_group != nullptr) {
+    w.grp = __ldg(comm.tile_group + c.m);
+    w.skip = w.grp < 0;
+  }
+  return w;
 }
 
 template <int BN, int A_MN, int B_MN, int OUT>
@@ -123,7 +164,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const int num_m = (M + BM - 1) / BM;
   const int num_n = (N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
+  const int num_tiles = num_m * num_n * (comm.seg_start != nullptr ? comm.num_groups : 1);
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -158,8 +199,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       uint32_t ready_blocks = 0;  // row blocks of A known to have arrived
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        TileCoord tc = tile_coord(tile, num_m, num_n, comm.m_rotate);
-        const int m0 = tc.m * BM, n0 = tc.n * BN;
+        const TileWork tw = tile_work(tile, num_m, num_n, num_kb, comm);
+        if (tw.skip) continue;
+        const int m0 = tw.m * BM, n0 = tw.n * BN;
+        // row-grouped mode: this tile's B is group grp's block of the stacked matrix
+        const int b_off = comm.tile_group != nullptr ? tw.grp * comm.b_group_rows : 0;
         if (comm.a_flags != nullptr) {
           const int blk = m0 / comm.a_rows_per_block;
           if (blk != comm.a_skip_block && !((ready_blocks >> blk) & 1u)) {
@@ -174,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             asm volatile("fence.proxy.async;" ::: "memory");
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = tw.kb0; kb < tw.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_word, status, 100 + s)) {
             ok = false;
             break;
@@ -191,11 +235,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               tma_load_2d(sa + j * (64 * BK * 2), &tmap_a, &full_bar[s], m0 + j * 64, k0);
           }
           if (B_MN == 0) {
-            tma_load_2d(sb, &tmap_b, &full_bar[s], k0, n0);  // box 64(K) x BN
+            tma_load_2d(sb, &tmap_b, &full_bar[s], k0, n0 + b_off);  // box 64(K) x BN
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)  // boxes 64(N) x 64(K)
-              tma_load_2d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[s], n0 + j * 64, k0);
+              tma_load_2d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[s], n0 + j * 64, k0 + b_off);
           }
           if (++s == Cfg::kStages) {
             s = 0;
@@ -214,10 +258,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TileWork tw = tile_work(tile, num_m, num_n, num_kb, comm);
+        if (tw.skip) continue;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word, status, 200 + acc)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = tw.kb0; kb < tw.kb1; ++kb) {
           if (!mbar_wait(&full_bar[s], phase, abort_word, status, 300 + s)) {
             ok = false;
             break;
@@ -232,7 +278,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                     : umma_smem_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024);
             uint64_t db = B_MN == 0 ? umma_smem_desc(sb + k * (UMMA_K * 2), 16, 1024)
                                     : umma_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024);
-            tc_mma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_f16_ss(d_tmem, da, db, idesc, ((kb - tw.kb0) | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
           if (++s == Cfg::kStages) {
@@ -259,9 +305,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t acc_phase = 0;
     int buf = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      TileCoord tc = tile_coord(tile, num_m, num_n, comm.m_rotate);
-      int m0 = tc.m * BM;
-      const int n0 = tc.n * BN;
+      const TileWork tw = tile_work(tile, num_m, num_n, num_kb, comm);
+      if (tw.skip) continue;
+      int m0 = tw.m * BM;
+      if (comm.seg_start != nullptr) m0 += tw.grp * M;   // groups are stacked along the rows of D
+      const int n0 = tw.n * BN;
       const CUtensorMap* tmap_d = &dmaps.m[0];
       if (comm.d_rows_per_block > 0) {
         const int dest = m0 / comm.d_rows_per_block;
@@ -379,15 +427,32 @@ static int launch(const void* A, const void* B, void* D, int M, int N, int K, in
     rc = pico_host::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, (uint64_t)lda * 2,
                                  64, 64, Swizzle::B128);
   if (rc) return rc;
+  const bool row_grouped = pc && pc->tile_group != nullptr;
+  const bool red_grouped = pc && pc->seg_start != nullptr;
+  if (row_grouped || red_grouped) {
+    if (pc->num_groups <= 0 || (row_grouped && red_grouped) || pc->d_num_dest > 0 || pc->a_flags != nullptr) {
+      pico_host::set_error("grouped gemm: one grouping mode, at least one group, no collective fusion");
+      return -2;
+    }
+    if (row_grouped && (A_MN != 0 || pc->b_group_rows != (B_MN == 0 ? N : K) || (B_MN == 1 && K % BK != 0))) {
+      pico_host::set_error("row-grouped gemm: need K-major A, one [N,K] or [K,N] matrix per group and K %% %d == 0", BK);
+      return -2;
+    }
+    if (red_grouped && (A_MN != 1 || B_MN != 1 || M % BM != 0)) {
+      pico_host::set_error("reduction-grouped gemm: need MN-major A and B and M %% %d == 0", BM);
+      return -2;
+    }
+  }
+  const int b_rows_total = row_grouped ? pc->num_groups * pc->b_group_rows : (B_MN == 0 ? N : K);
   if (B_MN == 0)
-    rc = pico_host::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldb * 2,
+    rc = pico_host::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, b_rows_total, (uint64_t)ldb * 2,
                                  64, BN, Swizzle::B128);
   else
-    rc = pico_host::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, (uint64_t)ldb * 2,
+    rc = pico_host::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, b_rows_total, (uint64_t)ldb * 2,
                                  64, 64, Swizzle::B128);
   if (rc) return rc;
   const int num_dest = (pc && pc->d_num_dest > 0) ? pc->d_num_dest : 1;
-  const int d_rows = (pc && pc->d_num_dest > 0) ? pc->d_rows_per_block : M;
+  const int d_rows = (pc && pc->d_num_dest > 0) ? pc->d_rows_per_block : (red_grouped ? pc->num_groups * M : M);
   if (num_dest > PICO_MAX_PEERS) {
     pico_host::set_error("gemm: %d destinations exceed the maximum of %d", num_dest, PICO_MAX_PEERS);
     return -2;
@@ -425,6 +490,10 @@ static int launch(const void* A, const void* B, void* D, int M, int N, int K, in
   if (pc) {
     comm.m_rotate = pc->m_rotate_rows / BM;
     comm.timeout_ns = (unsigned long long)pc->timeout_ms * 1000000ull;
+    comm.tile_group = pc->tile_group;
+    comm.b_group_rows = pc->b_group_rows;
+    comm.seg_start = pc->seg_start;
+    comm.num_groups = pc->num_groups;
   }
 
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT>;
@@ -443,7 +512,7 @@ static int launch(const void* A, const void* B, void* D, int M, int N, int K, in
     attr_set = true;
     attr_dev = dev;
   }
-  const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * (red_grouped ? pc->num_groups : 1);
   int ctas = pico_host::num_sms();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (num_tiles < ctas) ctas = num_tiles;

@@ -41,9 +41,10 @@ def _dtype_of(cfg, device) -> torch.dtype:
     return {"bfloat16": torch.bfloat16, "float32": torch.float32}[cfg["model"].get("dtype", "bfloat16")]
 
 
-def loss_fn(model, logits, targets) -> torch.Tensor:
-    """Mean token loss from the model output: dense logits, or vocabulary-sharded logits when
-    the lm head keeps them sharded (``vocab_parallel_ce``)."""
+def loss_fn(model, logits, targets, divisor: float = 1.0) -> torch.Tensor:
+    """Mean token loss (divided by ``divisor``, the number of micro-batches) from the model output:
+    dense logits, or vocabulary-sharded logits when the lm head keeps them sharded
+    (``vocab_parallel_ce``). ``backward()`` must be called on the result (or a sum containing it)."""
     if logits.dim() == 2 and targets.dim() == 2:
         # fused sequence-parallel lm head: rows are rank-major, bring the targets into that order
         world = group_size(getattr(model, "tp_group", None))
@@ -52,8 +53,8 @@ def loss_fn(model, logits, targets) -> torch.Tensor:
     if getattr(model, "vocab_parallel_ce", False) and group_size(getattr(model, "tp_group", None)) > 1:
         g = model.tp_group
         start = group_rank(g) * logits.shape[-1]
-        return ce_ops.cross_entropy(logits, targets, vocab_start=start, group=g).mean()
-    return ce_ops.cross_entropy(logits, targets).mean()
+        return ce_ops.mean_cross_entropy(logits, targets, vocab_start=start, group=g, divisor=divisor)
+    return ce_ops.mean_cross_entropy(logits, targets, divisor=divisor)
 
 
 class FlatOptimizer:
@@ -392,7 +393,7 @@ class TrainEngine:
                     target_ids = batch["target_ids"].to(self.device, non_blocking=True)
                 self._sync_context(i == ga - 1)
                 logits = self.dp_model(input_ids=input_ids)
-                mb_loss = loss_fn(self.model, logits, target_ids) / ga
+                mb_loss = loss_fn(self.model, logits, target_ids, divisor=ga)
                 aux = self._aux_loss()
                 total = mb_loss + aux / ga if aux is not None else mb_loss
                 total.backward()

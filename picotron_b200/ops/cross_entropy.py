@@ -13,6 +13,8 @@ the loss. The reference keeps a full ``[N, V/tp]`` softmax for the backward
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
@@ -108,6 +110,52 @@ class _FusedCEFn(torch.autograd.Function):
         scale = dloss.reshape(-1)[:1].to(dlogits.dtype)
         dlogits.mul_(scale)
         return dlogits.view(ctx.shape), None, None, None, None
+
+
+class _FusedMeanCEFn(torch.autograd.Function):
+    """Scalar ``mean(loss) / divisor``. The gradient of that scalar w.r.t. the logits,
+    ``(softmax - onehot) / (rows * divisor)``, is written over the logits during the forward pass
+    and handed out unchanged in backward: the result must be the quantity ``backward()`` is called
+    on (possibly added to other losses), i.e. its incoming gradient must be exactly 1. This saves
+    the extra pass over the ``[rows, V]`` gradient that a late scaling costs.
+    ``PICO_CE_CHECK_UNIT_GRAD=1`` verifies the contract (with a device synchronisation)."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, vocab_start, group, divisor):
+        V = logits.shape[-1]
+        l2 = logits.view(-1, V)
+        assert l2.stride(1) == 1
+        rows = l2.shape[0]
+        t = targets.reshape(-1)
+        if not t.is_contiguous():
+            t = t.contiguous()
+        stats = torch.empty((rows, 3), device=logits.device, dtype=torch.float32)
+        ext().ce_stats(l2, l2.stride(0), t, stats, rows, V, vocab_start)
+        stats = combine_stats(stats, group)
+        loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
+        scale = 1.0 / (rows * divisor)
+        ext().ce_loss_grad(l2, l2.stride(0), t, stats, loss, l2, l2.stride(0), scale, rows, V, vocab_start)
+        count_launch(2)
+        ctx.save_for_backward(l2)
+        ctx.shape = logits.shape
+        return loss.sum() * scale
+
+    @staticmethod
+    def backward(ctx, dloss):
+        (dlogits,) = ctx.saved_tensors
+        if os.environ.get("PICO_CE_CHECK_UNIT_GRAD", "0") == "1":
+            assert float(dloss) == 1.0, "mean_cross_entropy must be the root of backward (incoming gradient 1)"
+        return dlogits.view(ctx.shape), None, None, None, None
+
+
+def mean_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, vocab_start: int = 0, group=None,
+                       divisor: float = 1.0) -> torch.Tensor:
+    """``cross_entropy(...).mean() / divisor`` as a scalar; on the kernel path the logits are consumed
+    and the result must be what ``backward()`` is called on (see ``_FusedMeanCEFn``)."""
+    if use_kernels(logits) and logits.shape[-1] % 8 == 0 and logits.is_contiguous() and torch.is_grad_enabled() \
+            and logits.requires_grad:
+        return _FusedMeanCEFn.apply(logits, targets, vocab_start, group, float(divisor))
+    return cross_entropy(logits, targets, vocab_start, group).mean() / divisor
 
 
 def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, vocab_start: int = 0, group=None,

@@ -50,7 +50,7 @@ def _capacity_moe_fused(layer, epf, tokens, expert_idx, weights, token_idx, num_
         row_of_slot = torch.full((E * C,), -1, device=tokens.device, dtype=torch.int32)
         row_of_slot[idx[in_round]] = rows[in_round]
         x = fused_ep.dispatch(tokens, row_of_slot, layer.top_k, epf, bool(layer.ep_fp8_dispatch))   # [L, ep*C, d]
-        out = torch.stack([layer.local_experts[l](x[l]) for l in range(L)])
+        out = layer.experts_uniform(x)
         back = fused_ep.combine(out, epf)                                                           # [E*C, d]
         sel = torch.nonzero(in_round).squeeze(1)
         y = y.index_add(0, token_idx[sel], back[idx[sel]].float() * weights[sel].float().unsqueeze(-1))
@@ -89,7 +89,7 @@ def capacity_moe(layer, routed, expert_idx, weights, token_idx, num_tokens: int,
         else:
             recv = buf
         x = recv.view(ep, L, C, d).transpose(0, 1).reshape(L, ep * C, d)
-        out = torch.stack([layer.local_experts[l](x[l]) for l in range(L)])
+        out = layer.experts_uniform(x)
         back = out.view(L, ep, C, d).transpose(0, 1).reshape(ep * L * C, d)
         if ep > 1:
             back = epc.all_to_all(back, equal, equal, layer.ep_group)

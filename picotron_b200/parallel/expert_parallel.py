@@ -31,6 +31,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import process_group_manager as pgm
+from ..ops import grouped_gemm
+from ..ops import swiglu as swiglu_ops
 from . import ep_communications as epc
 from .dist_utils import group_rank, group_size
 from .tensor_parallel import Linear
@@ -83,6 +85,7 @@ class MoELayer(nn.Module):
         expert_cfg = types.SimpleNamespace(hidden_size=self.expert_dim, intermediate_size=config.intermediate_size,
                                            init_std=std)
         self.local_experts = nn.ModuleList([MLP(expert_cfg) for _ in range(self.num_local_experts)])
+        self._uniform_layouts = {}
         self.num_shared_experts = getattr(config, "num_shared_experts", 0) or 0
         shared_width = getattr(config, "shared_expert_intermediate_size", None)
         if shared_width is None and self.num_shared_experts > 0:
@@ -206,11 +209,43 @@ class MoELayer(nn.Module):
         if x.shape[0] == 0:
             # keep the experts in the autograd graph so their (zero) gradients exist on every rank
             return x + 0.0 * sum(p.sum() for e in self.local_experts for p in e.parameters())
+        if self._grouped_ok(x):
+            layout = grouped_gemm.GroupLayout.from_counts([int(c) for c in counts], x.device)
+            return layout.unpad(self._experts_on_layout(layout.pad(x), layout))
         outs, off = [], 0
         for e, n in enumerate(counts):
             outs.append(self.local_experts[e](x[off:off + n]))
             off += n
         return torch.cat(outs, dim=0)
+
+    def experts_uniform(self, x: torch.Tensor) -> torch.Tensor:
+        """Local experts on ``x[l]`` (``[L, rows, d]``, the same number of rows for every expert)."""
+        L, R, d = x.shape
+        if self._grouped_ok(x) and R > 0:
+            key = (L, R, x.device)
+            layout = self._uniform_layouts.get(key)
+            if layout is None:
+                layout = self._uniform_layouts[key] = grouped_gemm.GroupLayout.uniform(L, R, x.device)
+            if layout.pad_index is None:
+                return self._experts_on_layout(x.reshape(L * R, d), layout).view(L, R, -1)
+            return layout.unpad(self._experts_on_layout(layout.pad(x.reshape(L * R, d)), layout)).view(L, R, -1)
+        return torch.stack([self.local_experts[l](x[l]) for l in range(L)])
+
+    def _grouped_ok(self, x: torch.Tensor) -> bool:
+        e0 = self.local_experts[0]
+        # the stacked weight-gradient blocks need output widths that are whole 128-row tiles
+        return grouped_gemm.kernel_ok(x, self.expert_dim, e0.gate_proj.weight.shape[0]) and \
+            self.expert_dim % 128 == 0 and e0.gate_proj.weight.dtype == torch.bfloat16
+
+    def _experts_on_layout(self, xp: torch.Tensor, layout) -> torch.Tensor:
+        """SwiGLU feed-forward of every local expert over the padded expert-major rows ``xp``: two
+        grouped GEMM launches around one SwiGLU kernel (the reference's fused-MoE composition,
+        picotron/expert_parallel/megakernel.py:294-357)."""
+        experts = list(self.local_experts)
+        inter = experts[0].gate_proj.weight.shape[0]
+        gu = grouped_gemm.grouped_linear(xp, [m for e in experts for m in (e.gate_proj, e.up_proj)], layout, 2 * inter)
+        return grouped_gemm.grouped_linear(swiglu_ops.swiglu(gu), [e.down_proj for e in experts], layout,
+                                           experts[0].down_proj.weight.shape[0])
 
     def _dispatch(self, rows_sorted, plan: RoutePlan):
         if self.ep_fp8_dispatch:

@@ -205,7 +205,10 @@ def run_schedule(engine: str, model, data_loader, tensor_shapes, device, dtype, 
                         out = stage_mod.forward_chunk(c, hidden_states=inp)
                     aux = _collect_aux(stage_mod, c)
                     if s == S - 1:
-                        out = loss_function(stage_mod, out, batch(i)["target_ids"]) / m
+                        if loss_function is default_loss:
+                            out = loss_function(stage_mod, out, batch(i)["target_ids"], divisor=m)
+                        else:
+                            out = loss_function(stage_mod, out, batch(i)["target_ids"]) / m
                         total_loss += out.detach().float()
                     elif smap.rank_of(s + 1) == rank:
                         local_act[(s + 1, i)] = out

@@ -38,10 +38,21 @@ class FusedGroup:
 def _fusion_groups(model: nn.Module):
     """Lists of modules whose weights should be adjacent: q/k/v and gate/up of each block."""
     groups = []
+    expert_mlps = set()
+    for m in model.modules():
+        # routed experts: gate/up of all local experts form one stacked block, the down projections
+        # another, so one grouped GEMM covers every local expert
+        if getattr(m, "is_moe", False) and hasattr(m, "local_experts"):
+            experts = list(m.local_experts)
+            if experts and all(hasattr(e, n) for e in experts for n in ("gate_proj", "up_proj", "down_proj")):
+                groups.append([p for e in experts for p in (e.gate_proj, e.up_proj)])
+                groups.append([e.down_proj for e in experts])
+                expert_mlps.update(id(e) for e in experts)
     for m in model.modules():
         if all(hasattr(m, n) for n in ("q_proj", "k_proj", "v_proj")):
             groups.append([m.q_proj, m.k_proj, m.v_proj])
-        if all(hasattr(m, n) for n in ("gate_proj", "up_proj")) and not getattr(m, "is_moe", False):
+        if all(hasattr(m, n) for n in ("gate_proj", "up_proj")) and not getattr(m, "is_moe", False) \
+                and id(m) not in expert_mlps:
             groups.append([m.gate_proj, m.up_proj])
     return groups
 

@@ -108,3 +108,90 @@ def test_linear_main_grad_accumulation():
     assert w.grad is None
     ref = 3 * torch.ones(256, 64, device="cuda").t() @ x.detach().float()
     assert _rel_err(w.main_grad, ref) < 1e-5
+
+
+# ---------------------------------------------------------------------------------------------
+# grouped GEMM over the local experts of a mixture-of-experts layer
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("counts,d_in,d_out", [([128, 256, 128], 128, 256), ([5, 0, 300, 129], 256, 384),
+                                                ([1000, 17, 64, 512, 3, 250, 0, 77], 512, 1024)])
+def test_grouped_gemm_forward_dgrad_wgrad(counts, d_in, d_out):
+    ops, _ = _ops()
+    from picotron_b200.ops import grouped_gemm as gg
+    torch.manual_seed(3)
+    G = len(counts)
+    n = sum(counts)
+    layout = gg.GroupLayout.from_counts(counts, "cuda")
+    assert layout.rows % 128 == 0 and layout.tile_group.numel() == max(layout.rows // 128, 1)
+    x = torch.randn(n, d_in, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(G * d_out, d_in, device="cuda", dtype=torch.bfloat16) * 0.1
+    xp = layout.pad(x)
+    # forward
+    y = layout.unpad(gg.grouped_gemm_nt(xp, w, layout, d_out))
+    ops.check_status()
+    ref, off = [], 0
+    for e, c in enumerate(counts):
+        ref.append(x[off:off + c].float() @ w[e * d_out:(e + 1) * d_out].float().t())
+        off += c
+    ref = torch.cat(ref)
+    assert _rel_err(y, ref) < 1e-2
+    # input gradient
+    dy = torch.randn(n, d_out, device="cuda", dtype=torch.bfloat16)
+    dyp = layout.pad(dy)
+    dx = layout.unpad(gg.grouped_gemm_nn(dyp, w, layout, d_out))
+    ops.check_status()
+    ref, off = [], 0
+    for e, c in enumerate(counts):
+        ref.append(dy[off:off + c].float() @ w[e * d_out:(e + 1) * d_out].float())
+        off += c
+    assert _rel_err(dx, torch.cat(ref)) < 1e-2
+    # weight gradient, accumulated into fp32; experts without rows keep their old values
+    acc = torch.randn(G * d_out, d_in, device="cuda", dtype=torch.float32)
+    base = acc.clone()
+    gg.grouped_gemm_tn(dyp, xp, layout, acc, accumulate=True)
+    ops.check_status()
+    off = 0
+    for e, c in enumerate(counts):
+        want = base[e * d_out:(e + 1) * d_out] + dy[off:off + c].float().t() @ x[off:off + c].float()
+        got = acc[e * d_out:(e + 1) * d_out]
+        assert _rel_err(got, want) < 1e-4, (e, c)
+        off += c
+
+
+def test_moe_layer_grouped_experts_match_per_expert_loop():
+    """The MoE layer on the grouped-GEMM path (stacked expert weights in a ParamStore, gradients
+    accumulated into main_grad) against the same layer run expert by expert in plain PyTorch."""
+    import copy
+    import types
+    ops, _ = _ops()
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.param_store import ParamStore
+    from picotron_b200.parallel.expert_parallel import MoELayer
+    pgm.process_group_manager = None
+    cfg = types.SimpleNamespace(hidden_size=256, intermediate_size=128, num_experts=8, num_experts_per_tok=2,
+                                init_std=0.05, num_shared_experts=1)
+    torch.manual_seed(0)
+    layer = MoELayer(cfg, ep_group=False).to("cuda", torch.bfloat16)
+    ref = copy.deepcopy(layer)
+    store = ParamStore(layer)
+    assert any(len(g.mods) == 16 for g in store.fused_groups) and any(len(g.mods) == 8 for g in store.fused_groups)
+    x = torch.randn(2, 192, 256, device="cuda", dtype=torch.bfloat16)
+    xr = x.clone().requires_grad_(True)
+    x.requires_grad_(True)
+    before = ops.launches()
+    y = layer(x)
+    y.float().square().mean().backward()
+    ops.check_status()
+    assert ops.launches() - before > 0
+    import os
+    os.environ["PICO_REFERENCE_OPS"] = "1"
+    try:
+        yr = ref(xr)
+        yr.float().square().mean().backward()
+    finally:
+        os.environ["PICO_REFERENCE_OPS"] = "0"
+    assert _rel_err(y, yr) < 2e-2
+    assert _rel_err(x.grad, xr.grad) < 3e-2
+    for (n, p), (_, q) in zip(layer.named_parameters(), ref.named_parameters()):
+        g = p.main_grad if getattr(p, "main_grad", None) is not None and p.grad is None else p.grad
+        assert _rel_err(g, q.grad) < 5e-2, n
