@@ -9,12 +9,18 @@
 //   warp  8    : tcgen05.mma issue (one thread): S_t(j) = Q_t K_j^T and O_t += P_t(j) V_j
 //   warp  9    : TMA loads (one thread): Q tiles once, K and V blocks into rings
 //
-// Tensor memory: S_A | S_B (128 fp32 columns each) | O_A | O_B (head_dim columns each).
-// A softmax thread owns a whole row, so the row maximum and sum need no exchange between threads;
-// it reads its S row from tensor memory twice (maximum, then exponentials) instead of holding 128
-// values in registers. P_t(j) goes to shared memory as bf16 in the 128-byte swizzled K-major layout
-// the second GEMM reads. The accumulator is rescaled lazily: only when the running maximum grew by
-// more than 2^8, which the fp32 range of the un-normalised probabilities absorbs.
+// Tensor memory: S_A | S_B (128 fp32 columns each) | O_A | O_B (head_dim columns each) and, for
+// head_dim 64, Q_A | Q_B (32 columns each). A softmax thread owns a whole row, so the row maximum
+// and sum need no exchange between threads; it reads its S row from tensor memory twice (maximum,
+// then exponentials) instead of holding 128 values in registers.
+//
+// Shared-memory bandwidth is what the tensor cores run out of first with tiles this small, so
+// operands are kept in tensor memory where possible: P_t(j) is written as packed bf16 pairs over the
+// first 64 columns of S_t and is the TMEM A operand of O_t += P_t V_j; for head_dim 64 the query
+// tile is stored to tensor memory once by the softmax threads and is the TMEM A operand of every
+// S_t = Q_t K_j^T. Only K_j and V_j are read from shared memory then.
+// The accumulator is rescaled lazily: only when the running maximum grew by more than 2^8, which
+// the fp32 range of the un-normalised probabilities absorbs.
 //
 // Issue order of the MMA thread (the tensor pipe executes in order):
 //   S_A(0) | S_B(0) PV_A(0) S_A(1) | PV_B(0) S_B(1) | PV_A(1) S_A(2) | ...
@@ -26,6 +32,7 @@
 #include <math_constants.h>
 
 #include <cstring>
+#include <type_traits>
 
 #include "../common/host.h"
 #include "../common/ptx.cuh"
@@ -47,10 +54,12 @@ struct Cfg {
   static constexpr int kQBytes = kTileM * D * 2;          // one query tile
   static constexpr int kKVBytes = kBlockN * D * 2;        // one K or V block
   static constexpr int kPBytes = kTileM * kBlockN * 2;    // one P tile
-  static constexpr int kKStages = (D == 64) ? 3 : 2;
-  static constexpr int kVStages = (D == 64) ? 3 : 1;
-  static constexpr int kTiles = 2 * kQBytes + (kKStages + kVStages) * kKVBytes + 2 * kPBytes;
-  // q_full[2], k_full/k_empty[kKStages], v_full/v_empty[kVStages], s_full[2], p_ready[2], o_done[2]
+  static constexpr bool kQInTmem = (D == 64);              // no TMEM columns left for it at head_dim 128
+  static constexpr int kKStages = (D == 64) ? 4 : 2;
+  static constexpr int kVStages = (D == 64) ? 4 : 2;
+  static constexpr int kTiles = (kQInTmem ? 0 : 2 * kQBytes) + (kKStages + kVStages) * kKVBytes;
+  // q_full[2] (TMA, or 128 softmax threads when Q goes to TMEM), k_full/k_empty[kKStages],
+  // v_full/v_empty[kVStages], s_full[2], p_ready[2], o_done[2]
   static constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 6;
   static constexpr int kSmemBytes = kTiles + kNumBars * 8 + 16;
   static constexpr int kTmemCols = 512;
@@ -74,7 +83,8 @@ __device__ __forceinline__ int blocks_needed(const PicoAttnParams& p, int first_
 
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
-flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __restrict__ out,
+flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, const __nv_bfloat16* __restrict__ q_ptr,
+                          __nv_bfloat16* __restrict__ out,
                           float* __restrict__ lse, const PicoAttnParams p, int* status) {
   using C = Cfg<D>;
   extern __shared__ uint8_t smem[];
@@ -82,10 +92,9 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
     if (threadIdx.x == 0) report_error(status, PICO_ERR_BOUNDS, 2999, (int)(smem_u32(smem) & 1023u));
     return;
   }
-  uint8_t* sQ = smem;                                   // [2]
-  uint8_t* sK = sQ + 2 * C::kQBytes;                    // [kKStages]
+  uint8_t* sQ = smem;                                   // [2] (absent when Q lives in TMEM)
+  uint8_t* sK = sQ + (C::kQInTmem ? 0 : 2 * C::kQBytes);   // [kKStages]
   uint8_t* sV = sK + C::kKStages * C::kKVBytes;         // [kVStages]
-  uint8_t* sP = sV + C::kVStages * C::kKVBytes;         // [2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kTiles);
   uint64_t* q_full = bars;
   uint64_t* k_full = q_full + 2;
@@ -110,14 +119,13 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
   const int kv_head = head / (p.heads / p.kv_heads);
   const int q0 = q_blk * kCtaM;
 
-  int n_t[2];
-  n_t[0] = blocks_needed(p, q0, min(q0 + kTileM, p.seq_q) - 1);
-  n_t[1] = blocks_needed(p, q0 + kTileM, min(q0 + kCtaM, p.seq_q) - 1);
-  const int n_max = max(n_t[0], n_t[1]);
+  const int n0 = blocks_needed(p, q0, min(q0 + kTileM, p.seq_q) - 1);              // key blocks of tile A
+  const int n1 = blocks_needed(p, q0 + kTileM, min(q0 + kCtaM, p.seq_q) - 1);      // ... of tile B
+  const int n_max = max(n0, n1);
 
   if (threadIdx.x == 0) {
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&q_full[t], 1);
+      mbar_init(&q_full[t], C::kQInTmem ? kGroupThreads : 1);
       mbar_init(&s_full[t], 1);
       mbar_init(&p_ready[t], kGroupThreads);
       mbar_init(&o_done[t], 1);
@@ -157,7 +165,7 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
     // ---------------------------------------------------------------------------- TMA loads
     if (lane == 0 && n_max > 0) {
       for (int t = 0; t < 2; ++t) {
-        if (n_t[t] == 0) continue;
+        if ((t == 0 ? n0 : n1) == 0 || C::kQInTmem) continue;
         mbar_arrive_expect_tx(&q_full[t], C::kQBytes);
 #pragma unroll
         for (int pn = 0; pn < C::kPanels; ++pn)
@@ -183,16 +191,19 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
     }
   } else if (warp == 8) {
     // ---------------------------------------------------------------------------- MMA issue
+    // This thread is the pacemaker of the CTA: everything it does between two products delays
+    // both softmax groups, so the tile index is a compile-time constant (no indexed local arrays)
+    // and ready barriers are only polled when this is the first reader of a block.
     if (lane == 0 && n_max > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(kTileM, kBlockN, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(kTileM, D, 0, 1);
       bool ok = true;
       // S_t(j) = Q_t K_j^T into S_t's columns; releases K_j after its last reader
-      auto issue_s = [&](int t, int j) {
+      auto issue_s = [&](auto tc, int j) {
+        constexpr int t = decltype(tc)::value;
         const int ks = j % C::kKStages;
         // the first tile that reads K_j waits for it to land
-        if ((t == 0 || j >= n_t[0]) &&
-            !mbar_wait(&k_full[ks], (j / C::kKStages) & 1, abort_word, status, 2020)) {
+        if ((t == 0 || j >= n0) && !mbar_wait(&k_full[ks], (j / C::kKStages) & 1, abort_word, status, 2020)) {
           ok = false;
           return;
         }
@@ -202,63 +213,66 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          tc_mma_f16_ss(tmem_base + t * kBlockN, umma_smem_desc(q_addr + off, 16, 1024),
-                        umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+          if (C::kQInTmem)   // 16 bf16 of K per step = 8 packed columns of the query tile
+            tc_mma_f16_ts(tmem_base + t * kBlockN, tmem_base + 2 * kBlockN + 2 * D + t * (D / 2) + kk * 8,
+                          umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+          else
+            tc_mma_f16_ss(tmem_base + t * kBlockN, umma_smem_desc(q_addr + off, 16, 1024),
+                          umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
         }
         tc_commit(&s_full[t]);
-        if (t == 1 || j >= n_t[1]) tc_commit(&k_empty[ks]);   // last reader of K_j
+        if (t == 1 || j >= n1) tc_commit(&k_empty[ks]);   // last reader of K_j
       };
+      // O_t += P_t(j) V_j, then S_t(j+1) (or the completion signal of the tile)
+      auto issue_pv = [&](auto tc, int j) {
+        constexpr int t = decltype(tc)::value;
+        const int vs = j % C::kVStages;
+        if ((t == 0 || j >= n0) && !mbar_wait(&v_full[vs], (j / C::kVStages) & 1, abort_word, status, 2040)) {
+          ok = false;
+          return;
+        }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + vs * C::kKVBytes);
+        const uint32_t o_tmem = tmem_base + 2 * kBlockN + t * D;
+        const uint32_t p_tmem = tmem_base + t * kBlockN;   // packed bf16 pairs over S_t's first 64 columns
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk)
+          tc_mma_f16_ts(o_tmem, p_tmem + kk * 8, umma_smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_o,
+                        (j | kk) != 0 ? 1u : 0u);
+        if (t == 1 || j >= n1) tc_commit(&v_empty[vs]);  // last reader of V_j
+        if (j + 1 < (t == 0 ? n0 : n1))
+          issue_s(tc, j + 1);
+        else
+          tc_commit(&o_done[t]);
+      };
+      using T0 = std::integral_constant<int, 0>;
+      using T1 = std::integral_constant<int, 1>;
       // Start the two tiles half a period apart: S_B(0) is issued only when P_A(0) is ready, so the
       // softmax of one tile runs while the other tile's products execute. Started together the
       // two softmax groups would stay in lock-step, compete for the exponential unit, and then both
       // wait for the tensor cores.
-      const bool both = n_t[0] > 0 && n_t[1] > 0;
-      for (int t = 0; t < 2 && ok; ++t) {
-        if (n_t[t] == 0 || (both && t == 1)) continue;
-        if (!mbar_wait(&q_full[t], 0, abort_word, status, 2000 + t)) {
-          ok = false;
-          break;
-        }
-        issue_s(t, 0);
+      const bool both = n0 > 0 && n1 > 0;
+      if (n0 > 0) {
+        ok = mbar_wait(&q_full[0], 0, abort_word, status, 2000);
+        if (ok) issue_s(T0{}, 0);
+      } else {
+        ok = mbar_wait(&q_full[1], 0, abort_word, status, 2001);
+        if (ok) issue_s(T1{}, 0);
       }
       for (int j = 0; j < n_max && ok; ++j) {
-        const int vs = j % C::kVStages;
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= n_t[t]) continue;
-          PP_STAMP(2);
-          if (!mbar_wait(&p_ready[t], j & 1, abort_word, status, 2030 + t)) {
-            ok = false;
-            break;
-          }
-          PP_STAMP(2);
-          if (both && j == 0 && t == 0) {   // delayed first product of tile B (see above)
-            if (!mbar_wait(&q_full[1], 0, abort_word, status, 2001)) {
-              ok = false;
-              break;
-            }
-            issue_s(1, 0);
+        if (j < n0) {
+          if (!mbar_wait(&p_ready[0], j & 1, abort_word, status, 2030)) break;
+          if (both && j == 0) {   // delayed first product of tile B (see above)
+            if (!mbar_wait(&q_full[1], 0, abort_word, status, 2001)) break;
+            issue_s(T1{}, 0);
             if (!ok) break;
           }
-          if ((t == 0 || j >= n_t[0]) &&
-              !mbar_wait(&v_full[vs], (j / C::kVStages) & 1, abort_word, status, 2040)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t p_addr = smem_u32(sP + t * C::kPBytes);
-          const uint32_t v_addr = smem_u32(sV + vs * C::kKVBytes);
-          const uint32_t o_tmem = tmem_base + 2 * kBlockN + t * D;
-#pragma unroll
-          for (int kk = 0; kk < kBlockN / 16; ++kk) {
-            const uint32_t a_off = (kk >> 2) * 16384 + (kk & 3) * 32;
-            tc_mma_f16_ss(o_tmem, umma_smem_desc(p_addr + a_off, 16, 1024),
-                          umma_smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_o, (j | kk) != 0 ? 1u : 0u);
-          }
-          if (t == 1 || j >= n_t[1]) tc_commit(&v_empty[vs]);  // last reader of V_j
-          if (j + 1 < n_t[t])
-            issue_s(t, j + 1);
-          else
-            tc_commit(&o_done[t]);
+          issue_pv(T0{}, j);
+          if (!ok) break;
+        }
+        if (j < n1) {
+          if (!mbar_wait(&p_ready[1], j & 1, abort_word, status, 2031)) break;
+          issue_pv(T1{}, j);
         }
       }
     }
@@ -273,8 +287,30 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem_base + t * kBlockN + lane_base;
     const uint32_t tmem_o = tmem_base + 2 * kBlockN + t * D + lane_base;
-    const int n_mine = n_t[t];
-    uint8_t* prow = sP + t * C::kPBytes + row * 128;
+    const int n_mine = t == 0 ? n0 : n1;
+    if (C::kQInTmem && n_mine > 0) {
+      // this thread's query row (64 bf16 = 32 packed columns) -> tensor memory, once
+      uint32_t qv[32];
+      if (valid_row) {
+        const uint4* src = reinterpret_cast<const uint4*>(q_ptr + (int64_t)batch * p.q_batch_stride +
+                                                         (int64_t)q_row * p.q_row_stride + head * D);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 v4 = __ldg(src + i);
+          qv[4 * i + 0] = v4.x;
+          qv[4 * i + 1] = v4.y;
+          qv[4 * i + 2] = v4.z;
+          qv[4 * i + 3] = v4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) qv[i] = 0u;
+      }
+      tmem_st_32x32b_x32(tmem_base + 2 * kBlockN + 2 * D + t * (D / 2) + lane_base, qv);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&q_full[t]);
+    }
     float m_run = -CUDART_INF_F;   // running max of the scaled scores (log2 units)
     float l_run = 0.f;
     bool alive = true;
@@ -293,40 +329,43 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
       const int k_base = j * kBlockN;
       const bool need_mask =
           (p.causal && (p.k_pos0 + k_base + kBlockN - 1 > p.q_pos0 + q0 + t * kTileM)) || (k_base + kBlockN > p.seq_k);
-      // The S row is read from tensor memory in 32-column chunks, twice (maximum, then
-      // exponentials). Chunk c+1 is always in flight while chunk c is processed, so the load
-      // latency is hidden behind the arithmetic of the same thread.
-      uint32_t buf[2][32];
-      tmem_ld_32x32b_x32(tmem_s, buf[0]);
-      // ---- pass 1: row maximum
-      float mx = -CUDART_INF_F;
+      // the whole S row (128 fp32) comes into registers with four loads in flight and one wait
+      uint32_t sv[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(tmem_s + ((c + 1) & 3) * 32, buf[(c + 1) & 1]);   // c == 3: chunk 0 for pass 2
-        const uint32_t (&sv)[32] = buf[c & 1];
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tmem_s + c * 32, sv[c]);
+      tmem_ld_wait();
+      if ((threadIdx.x & 127) == 0) PP_STAMP(t);
+      // ---- row maximum (branch-free inner loops: the mask is applied with selects, and only on
+      // blocks that need it)
+      float mx;
+      {
         float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, m2 = -CUDART_INF_F, m3 = -CUDART_INF_F;
         if (need_mask) {
-          const int lim = k_limit - (k_base + c * 32);   // columns [0, lim) are visible
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            m0 = fmaxf(m0, i + 0 < lim ? __uint_as_float(sv[i + 0]) : -CUDART_INF_F);
-            m1 = fmaxf(m1, i + 1 < lim ? __uint_as_float(sv[i + 1]) : -CUDART_INF_F);
-            m2 = fmaxf(m2, i + 2 < lim ? __uint_as_float(sv[i + 2]) : -CUDART_INF_F);
-            m3 = fmaxf(m3, i + 3 < lim ? __uint_as_float(sv[i + 3]) : -CUDART_INF_F);
+          for (int c = 0; c < 4; ++c) {
+            const int lim = k_limit - (k_base + c * 32);   // columns [0, lim) of the chunk are visible
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              m0 = fmaxf(m0, i + 0 < lim ? __uint_as_float(sv[c][i + 0]) : -CUDART_INF_F);
+              m1 = fmaxf(m1, i + 1 < lim ? __uint_as_float(sv[c][i + 1]) : -CUDART_INF_F);
+              m2 = fmaxf(m2, i + 2 < lim ? __uint_as_float(sv[c][i + 2]) : -CUDART_INF_F);
+              m3 = fmaxf(m3, i + 3 < lim ? __uint_as_float(sv[c][i + 3]) : -CUDART_INF_F);
+            }
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(sv[i + 0]));
-            m1 = fmaxf(m1, __uint_as_float(sv[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(sv[i + 2]));
-            m3 = fmaxf(m3, __uint_as_float(sv[i + 3]));
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              m0 = fmaxf(m0, __uint_as_float(sv[c][i + 0]));
+              m1 = fmaxf(m1, __uint_as_float(sv[c][i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(sv[c][i + 2]));
+              m3 = fmaxf(m3, __uint_as_float(sv[c][i + 3]));
+            }
           }
         }
-        mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       }
-      if ((threadIdx.x & 127) == 0) PP_STAMP(t);
       mx *= scale_log2;   // scale > 0, so the maximum commutes with the scaling
       const float m_new = fmaxf(m_run, mx);
       const bool grow = (m_new - m_run > kRescaleThreshold) || (m_run == -CUDART_INF_F);
@@ -334,7 +373,6 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
       const float alpha = (m_run == -CUDART_INF_F) ? 0.f : exp2f(m_run - m_use);
       // PV_t(j-1) completed before S_t(j) was signalled, so O_t is quiescent here
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        tmem_ld_wait();   // chunk 0 of pass 2 (buf[0]) has landed; the loads below use their own registers
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
@@ -348,50 +386,63 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __re
       }
       l_run *= alpha;
       m_run = m_use;
-      // ---- pass 2: probabilities -> bf16 P tile in shared memory, row sum
+      // ---- probabilities -> packed bf16 P over the first 64 columns of S_t, row sum
       // exp2(s*scale - m) is one fused multiply-add per element; a row that has seen no key yet
       // (m = -inf) gets offset 0 and is masked entirely through lim = 0
       const float neg_m = (m_run == -CUDART_INF_F) ? 0.f : -m_run;
       const bool mask2 = need_mask || m_run == -CUDART_INF_F;
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      // P only overwrites S columns 0..63 (chunks 0 and 1), so chunks 2 and 3 are dropped after the
+      // maximum and read again while chunks 0 and 1 are exponentiated; this keeps the live register
+      // count under the limit of this launch configuration
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c < 3) tmem_ld_32x32b_x32(tmem_s + (c + 1) * 32, buf[(c + 1) & 1]);
-        const uint32_t (&sv)[32] = buf[c & 1];
-        float pr[32];
+        if (c == 1) tmem_ld_32x32b_x32(tmem_s + 2 * 32, sv[2]);
+        if (c == 2) {
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(tmem_s + 3 * 32, sv[3]);
+        }
+        if (c == 3) tmem_ld_wait();
+        uint32_t pk[16];
         if (mask2) {
           const int lim = (m_run == -CUDART_INF_F) ? 0 : k_limit - (k_base + c * 32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float e = exp2f(fmaf(__uint_as_float(sv[i]), scale_log2, neg_m));
-            pr[i] = i < lim ? e : 0.f;
+          for (int i = 0; i < 32; i += 4) {
+            float e0 = exp2f(fmaf(__uint_as_float(sv[c][i + 0]), scale_log2, neg_m));
+            float e1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m));
+            float e2 = exp2f(fmaf(__uint_as_float(sv[c][i + 2]), scale_log2, neg_m));
+            float e3 = exp2f(fmaf(__uint_as_float(sv[c][i + 3]), scale_log2, neg_m));
+            e0 = i + 0 < lim ? e0 : 0.f;
+            e1 = i + 1 < lim ? e1 : 0.f;
+            e2 = i + 2 < lim ? e2 : 0.f;
+            e3 = i + 3 < lim ? e3 : 0.f;
+            s0 += e0;
+            s1 += e1;
+            s2 += e2;
+            s3 += e3;
+            pk[i / 2] = pack_bf16x2(e0, e1);
+            pk[i / 2 + 1] = pack_bf16x2(e2, e3);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pr[i] = exp2f(fmaf(__uint_as_float(sv[i]), scale_log2, neg_m));
+          for (int i = 0; i < 32; i += 4) {
+            const float e0 = exp2f(fmaf(__uint_as_float(sv[c][i + 0]), scale_log2, neg_m));
+            const float e1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m));
+            const float e2 = exp2f(fmaf(__uint_as_float(sv[c][i + 2]), scale_log2, neg_m));
+            const float e3 = exp2f(fmaf(__uint_as_float(sv[c][i + 3]), scale_log2, neg_m));
+            s0 += e0;
+            s1 += e1;
+            s2 += e2;
+            s3 += e3;
+            pk[i / 2] = pack_bf16x2(e0, e1);
+            pk[i / 2 + 1] = pack_bf16x2(e2, e3);
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          s0 += pr[i + 0];
-          s1 += pr[i + 1];
-          s2 += pr[i + 2];
-          s3 += pr[i + 3];
-        }
-        uint8_t* panel = prow + (c >> 1) * 16384;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 o;
-          o.x = pack_bf16x2(pr[8 * q4 + 0], pr[8 * q4 + 1]);
-          o.y = pack_bf16x2(pr[8 * q4 + 2], pr[8 * q4 + 3]);
-          o.z = pack_bf16x2(pr[8 * q4 + 4], pr[8 * q4 + 5]);
-          o.w = pack_bf16x2(pr[8 * q4 + 6], pr[8 * q4 + 7]);
-          const int chunk = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(panel + ((chunk ^ (row & 7)) << 4)) = o;
-        }
+        // every S column of this thread's row is already in registers, so P may overwrite them
+        tmem_st_32x32b_x16(tmem_s + c * 16, pk);
       }
       l_run += (s0 + s1) + (s2 + s3);
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_ready[t]);
       if ((threadIdx.x & 127) == 0) PP_STAMP(t);
@@ -475,7 +526,8 @@ static int launch(const void* q, const void* k, const void* v, void* out, float*
     attr_dev = dev;
   }
   dim3 grid(p->heads, p->batch, (p->seq_q + kCtaM - 1) / kCtaM);
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(maps, (__nv_bfloat16*)out, lse, *p, pico_status_buffer());
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(maps, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, lse, *p,
+                                                  pico_status_buffer());
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     pico_host::set_error("attention fwd launch: %s", cudaGetErrorString(e));
