@@ -160,9 +160,11 @@ flash_bwd_kernel(const __grid_constant__ BwdMaps maps, const float* __restrict__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int kv_block = blockIdx.x;
-  const int kv_head = blockIdx.y;
-  const int batch = blockIdx.z;
+  // blocks are dispatched x-fastest: under a causal mask key block 0 has the most query blocks to
+  // walk, so every (head, batch) of the heavy key blocks starts before any light one
+  const int kv_block = blockIdx.z;
+  const int kv_head = blockIdx.x;
+  const int batch = blockIdx.y;
   const int group = p.heads / p.kv_heads;
   const int k0 = kv_block * kBN;
   const int num_q_blocks = (p.seq_q + kBM - 1) / kBM;
@@ -494,7 +496,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
     }
     attr_dev = dev;
   }
-  dim3 grid((p->seq_k + kBN - 1) / kBN, p->kv_heads, p->batch);
+  dim3 grid(p->kv_heads, p->batch, (p->seq_k + kBN - 1) / kBN);
   kern<<<grid, kBwdThreads, Cfg::kSmemBytes, stream>>>(maps, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv,
                                                       *p, dk_batch_stride, dk_row_stride, dv_batch_stride,
                                                       dv_row_stride, pico_status_buffer());

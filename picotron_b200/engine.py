@@ -253,6 +253,8 @@ class TrainEngine:
             self.store = ParamStore(model, pad_to_multiple=max(1, self._grad_group_size()),
                                     allocator=allocator) if self.flat else None
         self._maybe_install_fused_ep()
+        self.fused_tp = None
+        self._maybe_install_fused_tp()
 
     def _split_expert_params(self) -> bool:
         return (self.cfg["distributed"]["ep_as_dp"] and self.pgm.ep_world_size > 1
@@ -283,8 +285,6 @@ class TrainEngine:
         self.fused_ep = EPFused(sg, layers[0].num_local_experts, cap, layers[0].expert_dim)
         for mod in layers:
             mod.fused_ep = self.fused_ep
-        self.fused_tp = None
-        self._maybe_install_fused_tp()
 
     def _maybe_install_fused_tp(self):
         """Switch the sequence-parallel linears to the kernels that carry their collectives through
