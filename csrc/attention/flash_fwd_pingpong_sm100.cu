@@ -335,38 +335,35 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, const __nv_bfloat16
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tmem_s + c * 32, sv[c]);
       tmem_ld_wait();
       if ((threadIdx.x & 127) == 0) PP_STAMP(t);
-      // ---- row maximum (branch-free inner loops: the mask is applied with selects, and only on
-      // blocks that need it)
+      // ---- masking: on the few blocks that need it (diagonal, ragged end) invisible scores become
+      // -inf in place, so the arithmetic below exists only once in the instruction stream
+      // (exp2(-inf) = 0; the kernel is large enough for instruction fetch to matter)
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int lim = k_limit - (k_base + c * 32);   // columns [0, lim) of the chunk are visible
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            sv[c][i] = i < lim ? sv[c][i] : __float_as_uint(-CUDART_INF_F);
+        }
+      }
+      // ---- row maximum
       float mx;
       {
         float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, m2 = -CUDART_INF_F, m3 = -CUDART_INF_F;
-        if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int lim = k_limit - (k_base + c * 32);   // columns [0, lim) of the chunk are visible
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              m0 = fmaxf(m0, i + 0 < lim ? __uint_as_float(sv[c][i + 0]) : -CUDART_INF_F);
-              m1 = fmaxf(m1, i + 1 < lim ? __uint_as_float(sv[c][i + 1]) : -CUDART_INF_F);
-              m2 = fmaxf(m2, i + 2 < lim ? __uint_as_float(sv[c][i + 2]) : -CUDART_INF_F);
-              m3 = fmaxf(m3, i + 3 < lim ? __uint_as_float(sv[c][i + 3]) : -CUDART_INF_F);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              m0 = fmaxf(m0, __uint_as_float(sv[c][i + 0]));
-              m1 = fmaxf(m1, __uint_as_float(sv[c][i + 1]));
-              m2 = fmaxf(m2, __uint_as_float(sv[c][i + 2]));
-              m3 = fmaxf(m3, __uint_as_float(sv[c][i + 3]));
-            }
+          for (int i = 0; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(sv[c][i + 0]));
+            m1 = fmaxf(m1, __uint_as_float(sv[c][i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(sv[c][i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(sv[c][i + 3]));
           }
         }
         mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       }
-      mx *= scale_log2;   // scale > 0, so the maximum commutes with the scaling
+      mx *= scale_log2;   // scale > 0, so the maximum commutes with the scaling (-inf stays -inf)
       const float m_new = fmaxf(m_run, mx);
       const bool grow = (m_new - m_run > kRescaleThreshold) || (m_run == -CUDART_INF_F);
       const float m_use = grow ? m_new : m_run;
@@ -388,9 +385,8 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, const __nv_bfloat16
       m_run = m_use;
       // ---- probabilities -> packed bf16 P over the first 64 columns of S_t, row sum
       // exp2(s*scale - m) is one fused multiply-add per element; a row that has seen no key yet
-      // (m = -inf) gets offset 0 and is masked entirely through lim = 0
+      // (m = -inf) uses offset 0: all its scores are -inf and give 0
       const float neg_m = (m_run == -CUDART_INF_F) ? 0.f : -m_run;
-      const bool mask2 = need_mask || m_run == -CUDART_INF_F;
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       // P only overwrites S columns 0..63 (chunks 0 and 1), so chunks 2 and 3 are dropped after the
       // maximum and read again while chunks 0 and 1 are exponentiated; this keeps the live register
@@ -403,42 +399,27 @@ flash_fwd_pingpong_kernel(const __grid_constant__ Maps maps, const __nv_bfloat16
           tmem_ld_32x32b_x32(tmem_s + 3 * 32, sv[3]);
         }
         if (c == 3) tmem_ld_wait();
-        uint32_t pk[16];
-        if (mask2) {
-          const int lim = (m_run == -CUDART_INF_F) ? 0 : k_limit - (k_base + c * 32);
+        if (c >= 2 && need_mask) {   // the reloaded chunks come unmasked
+          const int lim = k_limit - (k_base + c * 32);
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float e0 = exp2f(fmaf(__uint_as_float(sv[c][i + 0]), scale_log2, neg_m));
-            float e1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m));
-            float e2 = exp2f(fmaf(__uint_as_float(sv[c][i + 2]), scale_log2, neg_m));
-            float e3 = exp2f(fmaf(__uint_as_float(sv[c][i + 3]), scale_log2, neg_m));
-            e0 = i + 0 < lim ? e0 : 0.f;
-            e1 = i + 1 < lim ? e1 : 0.f;
-            e2 = i + 2 < lim ? e2 : 0.f;
-            e3 = i + 3 < lim ? e3 : 0.f;
-            s0 += e0;
-            s1 += e1;
-            s2 += e2;
-            s3 += e3;
-            pk[i / 2] = pack_bf16x2(e0, e1);
-            pk[i / 2 + 1] = pack_bf16x2(e2, e3);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float e0 = exp2f(fmaf(__uint_as_float(sv[c][i + 0]), scale_log2, neg_m));
-            const float e1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m));
-            const float e2 = exp2f(fmaf(__uint_as_float(sv[c][i + 2]), scale_log2, neg_m));
-            const float e3 = exp2f(fmaf(__uint_as_float(sv[c][i + 3]), scale_log2, neg_m));
-            s0 += e0;
-            s1 += e1;
-            s2 += e2;
-            s3 += e3;
-            pk[i / 2] = pack_bf16x2(e0, e1);
-            pk[i / 2 + 1] = pack_bf16x2(e2, e3);
-          }
+          for (int i = 0; i < 32; ++i)
+            sv[c][i] = i < lim ? sv[c][i] : __float_as_uint(-CUDART_INF_F);
         }
-        // every S column of this thread's row is already in registers, so P may overwrite them
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float e0 = exp2f(fmaf(__uint_as_float(sv[c][i + 0]), scale_log2, neg_m));
+          const float e1 = exp2f(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m));
+          const float e2 = exp2f(fmaf(__uint_as_float(sv[c][i + 2]), scale_log2, neg_m));
+          const float e3 = exp2f(fmaf(__uint_as_float(sv[c][i + 3]), scale_log2, neg_m));
+          s0 += e0;
+          s1 += e1;
+          s2 += e2;
+          s3 += e3;
+          pk[i / 2] = pack_bf16x2(e0, e1);
+          pk[i / 2 + 1] = pack_bf16x2(e2, e3);
+        }
+        // every S column of chunks 0 and 1 is already in registers, so P may overwrite them
         tmem_st_32x32b_x16(tmem_s + c * 16, pk);
       }
       l_run += (s0 + s1) + (s2 + s3);

@@ -21,6 +21,7 @@ Internal design (not the reference's):
 """
 from __future__ import annotations
 
+import os
 import types
 from dataclasses import dataclass
 from typing import List, Optional
@@ -232,6 +233,8 @@ class MoELayer(nn.Module):
         return torch.stack([self.local_experts[l](x[l]) for l in range(L)])
 
     def _grouped_ok(self, x: torch.Tensor) -> bool:
+        if os.environ.get("PICO_GROUPED_EXPERTS", "1") == "0":     # A/B switch: per-expert GEMM launches
+            return False
         e0 = self.local_experts[0]
         # the stacked weight-gradient blocks need output widths that are whole 128-row tiles
         return grouped_gemm.kernel_ok(x, self.expert_dim, e0.gate_proj.weight.shape[0]) and \
