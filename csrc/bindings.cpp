@@ -237,6 +237,28 @@ void slot_sum(const at::Tensor& staging, int64_t world, int64_t rows, int64_t co
         "slot_sum");
 }
 
+void slot_sum_from(const at::Tensor& staging, int64_t world, int64_t first_slot, int64_t rows, int64_t cols,
+                   const c10::optional<at::Tensor>& addend, at::Tensor& out, int64_t local_flags, int64_t slot,
+                   int64_t epoch, int64_t timeout_ms) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_contiguous() && (!addend.has_value() || addend->is_contiguous()), "slot_sum_from: contiguous");
+  check(pico_slot_sum_from(staging.data_ptr(), (int)world, (int)first_slot, (int)rows, (int)cols, cptr(addend),
+                           out.data_ptr(), reinterpret_cast<const uint32_t*>(local_flags), (int)slot,
+                           (uint32_t)epoch, (uint32_t)timeout_ms, stream_of(out)),
+        "slot_sum_from");
+}
+
+void scatter_rows(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs,
+                  const std::vector<int64_t>& flag_ptrs, int64_t world, int64_t my_rank, int64_t num_dst,
+                  int64_t rows, int64_t cols, int64_t slot, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kBFloat16, "scatter_rows: contiguous bf16");
+  TORCH_CHECK(src.numel() >= num_dst * rows * cols, "scatter_rows: source too small");
+  check(pico_scatter_rows(src.data_ptr(), table_of(dst_ptrs), table_of(flag_ptrs), (int)world, (int)my_rank,
+                          (int)num_dst, (int)rows, (int)cols, (int)slot, (uint32_t)epoch, stream_of(src)),
+        "scatter_rows");
+}
+
 void zero1_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, at::Tensor& m,
                  at::Tensor& v, const c10::optional<at::Tensor>& master, int64_t shard_start, int64_t shard_len,
                  int64_t world, int64_t my_rank, double lr, double beta1, double beta2, double eps, double wd,
@@ -443,6 +465,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("push_rows", &push_rows);
   m.def("rmsnorm_fwd_push", &rmsnorm_fwd_push);
   m.def("slot_sum", &slot_sum);
+  m.def("slot_sum_from", &slot_sum_from);
+  m.def("scatter_rows", &scatter_rows);
   m.def("gemm_ex", &gemm_ex);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("zero1_adamw", &zero1_adamw);

@@ -40,6 +40,23 @@ __global__ void push_rows_kernel(const uint4* __restrict__ src, PicoPeerTable ds
   raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
 }
 
+// Block o of src goes into slot `my_rank` of rank o's staging buffer, for o < num_dst; the flag is
+// raised on every rank of the group (also on those that received nothing), so all ranks stay in
+// step with the epoch protocol.
+__global__ void scatter_rows_kernel(const uint4* __restrict__ src, PicoPeerTable dst, PicoPeerTable flags,
+                                    int world, int my_rank, int num_dst, int64_t nvec_block, int slot,
+                                    uint32_t epoch, unsigned int* counter) {
+  const int64_t total = (int64_t)num_dst * nvec_block;
+  const int64_t base = (int64_t)my_rank * nvec_block;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int o = (int)(i / nvec_block);
+    const int64_t j = i - (int64_t)o * nvec_block;
+    reinterpret_cast<uint4*>(dst.ptr[o])[base + j] = src[i];
+  }
+  raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
+}
+
 template <int NV>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_push_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
@@ -94,7 +111,7 @@ rmsnorm_fwd_push_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
 }
 
-__global__ void slot_sum_kernel(const uint4* __restrict__ staging, int world, int64_t nvec,
+__global__ void slot_sum_kernel(const uint4* __restrict__ staging, int world, int first_slot, int64_t nvec,
                                 const uint4* __restrict__ addend, uint4* __restrict__ out,
                                 const uint32_t* local_flags, int slot, uint32_t epoch,
                                 uint64_t timeout_ns, int* status) {
@@ -111,8 +128,9 @@ __global__ void slot_sum_kernel(const uint4* __restrict__ staging, int world, in
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
        i += (int64_t)gridDim.x * blockDim.x) {
     float acc[8];
-    unpack8(staging[i], acc);
-    for (int s = 1; s < world; ++s) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = first_slot; s < world; ++s) {
       float f[8];
       unpack8(staging[(int64_t)s * nvec + i], f);
 #pragma unroll
@@ -211,7 +229,41 @@ extern "C" int pico_rmsnorm_fwd_push(const void* x, const void* residual, const 
 extern "C" int pico_slot_sum(const void* staging, int world, int rows, int cols, const void* addend,
                              void* out, const uint32_t* local_flags, int slot, uint32_t epoch,
                              uint32_t timeout_ms, cudaStream_t stream) {
+  return pico_slot_sum_from(staging, world, 0, rows, cols, addend, out, local_flags, slot, epoch, timeout_ms,
+                            stream);
+}
+
+extern "C" int pico_scatter_rows(const void* src, PicoPeerTable dst, PicoPeerTable flags, int world,
+                                 int my_rank, int num_dst, int rows, int cols, int slot, uint32_t epoch,
+                                 cudaStream_t stream) {
+  if (int rc = check_world("scatter_rows", world, slot)) return rc;
+  const int64_t n = (int64_t)rows * cols;
+  if (n % 8 != 0 || num_dst < 0 || num_dst > world) {
+    pico_host::set_error("scatter_rows: rows*cols must be a multiple of 8 and 0 <= num_dst <= world");
+    return -2;
+  }
+  unsigned int* counter = grid_counter();
+  if (!counter) return -1;
+  const int64_t nvec = n / 8;
+  int grid = (int)((nvec * num_dst + 255) / 256);
+  const int cap = pico_host::num_sms() * 4;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  scatter_rows_kernel<<<grid, 256, 0, stream>>>((const uint4*)src, dst, flags, world, my_rank, num_dst, nvec,
+                                                slot, epoch, counter + 2);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) pico_host::set_error("scatter_rows: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+extern "C" int pico_slot_sum_from(const void* staging, int world, int first_slot, int rows, int cols,
+                                  const void* addend, void* out, const uint32_t* local_flags, int slot,
+                                  uint32_t epoch, uint32_t timeout_ms, cudaStream_t stream) {
   if (int rc = check_world("slot_sum", world, slot)) return rc;
+  if (first_slot < 0 || first_slot > world) {
+    pico_host::set_error("slot_sum: first slot %d out of range", first_slot);
+    return -2;
+  }
   const int64_t n = (int64_t)rows * cols;
   if (n % 8 != 0) {
     pico_host::set_error("slot_sum: rows*cols must be a multiple of 8");
@@ -222,7 +274,7 @@ extern "C" int pico_slot_sum(const void* staging, int world, int rows, int cols,
   const int cap = pico_host::num_sms() * 8;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
-  slot_sum_kernel<<<grid, 256, 0, stream>>>((const uint4*)staging, world, nvec, (const uint4*)addend,
+  slot_sum_kernel<<<grid, 256, 0, stream>>>((const uint4*)staging, world, first_slot, nvec, (const uint4*)addend,
                                             (uint4*)out, local_flags, slot, epoch,
                                             (uint64_t)timeout_ms * 1000000ull, pico_status_buffer());
   cudaError_t e = cudaGetLastError();

@@ -35,6 +35,19 @@ int pico_slot_sum(const void* staging, int world, int rows, int cols, const void
                   const uint32_t* local_flags, int slot, uint32_t epoch, uint32_t timeout_ms,
                   cudaStream_t stream);
 
+// Same, summing only slots first_slot .. world-1 (all flags are still awaited). With
+// first_slot == world the result is the addend (or zero).
+int pico_slot_sum_from(const void* staging, int world, int first_slot, int rows, int cols,
+                       const void* addend, void* out, const uint32_t* local_flags, int slot, uint32_t epoch,
+                       uint32_t timeout_ms, cudaStream_t stream);
+
+// Row block o of src[num_dst*rows, cols] (bf16, contiguous) goes into slot `my_rank` of rank o's
+// staging buffer ([world slots][rows][cols]) for o < num_dst; then flag [slot][my_rank] = epoch is
+// raised on every rank. The scatter half of a reduce-scatter whose contributions differ per
+// destination (context parallelism: a rank only holds gradients for the key blocks before its own).
+int pico_scatter_rows(const void* src, PicoPeerTable dst, PicoPeerTable flags, int world, int my_rank,
+                      int num_dst, int rows, int cols, int slot, uint32_t epoch, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -255,6 +255,28 @@ class TrainEngine:
         self._maybe_install_fused_ep()
         self.fused_tp = None
         self._maybe_install_fused_tp()
+        self._maybe_install_fused_cp()
+
+    def _maybe_install_fused_cp(self):
+        """Ring context parallelism exchanges K/V and reduces dK/dV through NVLink peer memory
+        (``ops.fused_cp``) on the flat bf16 path; ``PICO_FUSED_CP=0`` keeps the NCCL point-to-point ring."""
+        import os
+        from .parallel import context_parallel as cpar
+        d, t, m, mc = self.cfg["distributed"], self.cfg["training"], self.pgm, self.model_config
+        self.fused_cp = None
+        cpar.install_fused_cp(None)
+        if not (self.flat and m.cp_world_size > 1 and d["cp_attention"] == "ring"
+                and os.environ.get("PICO_FUSED_CP", "1") != "0"):
+            return
+        from .ops.fused_cp import CPFused
+        from .runtime.symm import SymmGroup
+        head_dim = mc.hidden_size // mc.num_attention_heads
+        kv_heads = mc.num_key_value_heads // m.tp_world_size
+        if head_dim not in (64, 128) or kv_heads < 1:
+            return
+        sg = SymmGroup(m.cp_group, device=self.device)
+        self.fused_cp = CPFused(sg, t["micro_batch_size"], t["seq_length"] // m.cp_world_size, kv_heads * head_dim)
+        cpar.install_fused_cp(self.fused_cp)
 
     def _split_expert_params(self) -> bool:
         return (self.cfg["distributed"]["ep_as_dp"] and self.pgm.ep_world_size > 1

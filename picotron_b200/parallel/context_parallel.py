@@ -120,10 +120,25 @@ def _ring_peer(group, delta: int) -> int:
     return dist.get_global_rank(group, (r + delta) % n)
 
 
+#: optional ``ops.fused_cp.CPFused``: K/V exchange and dK/dV reduction through NVLink peer memory
+_FUSED_CP = None
+
+
+def install_fused_cp(cp) -> None:
+    """Route causal ring attention of matching shapes through the peer-memory gather (``ops.fused_cp``)."""
+    global _FUSED_CP
+    _FUSED_CP = cp
+
+
 def ring_attention_bshd(q, k, v, causal: bool = True, sm_scale=None, group=None):
     group = group if group is not None else pgm.get_pgm().cp_group
     if group_size(group) == 1:
         return attn_ops.attention(q, k, v, causal, sm_scale)
+    cp = _FUSED_CP
+    if cp is not None and causal and cp.sg.group is group and cp.matches(k) and attn_ops.kernel_supports(q, k) \
+            and not attn_ops.reference_ops_forced_():
+        from ..ops.fused_cp import gathered_causal_attention
+        return gathered_causal_attention(q, k, v, sm_scale, cp)
     return _RingAttention.apply(q, k, v, sm_scale, causal, group)
 
 

@@ -275,3 +275,47 @@ def _cp_worker(rank, world):
 
 def test_context_parallel_attention_2gpu():
     run_gpu_ranks(_cp_worker, 2)
+
+
+def _fused_cp_worker(rank, world):
+    """Causal context-parallel attention with the K/V gather and dK/dV reduction through peer memory
+    (``ops.fused_cp``) against single-device attention over the full sequence; several rounds so both
+    copies of the double-buffered symmetric buffers are reused."""
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.ops import attention as A
+    from picotron_b200.ops.fused_cp import CPFused
+    from picotron_b200.parallel import context_parallel as cpar
+    from picotron_b200.runtime.symm import SymmGroup
+    pgm.setup_process_group_manager(tp_size=1, cp_size=world, pp_size=1, dp_size=1)
+    group = pgm.get_pgm().cp_group
+    dev = torch.device("cuda", rank)
+    b, s_loc, H, Hkv, d = 2, 384, 8, 2, 64
+    s = s_loc * world
+    cp = CPFused(SymmGroup(group, device=dev), b, s_loc, Hkv * d)
+    cpar.install_fused_cp(cp)
+    try:
+        for rnd in range(3):
+            torch.manual_seed(rnd)
+            q = torch.randn(b, s, H, d, device=dev, dtype=torch.bfloat16)
+            k = torch.randn(b, s, Hkv, d, device=dev, dtype=torch.bfloat16)
+            v = torch.randn(b, s, Hkv, d, device=dev, dtype=torch.bfloat16)
+            go = torch.randn(b, s, H, d, device=dev, dtype=torch.bfloat16)
+            qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
+            ref = A.attention_ref(qr, kr, vr, True)
+            ref.backward(go.float())
+            sl = slice(rank * s_loc, (rank + 1) * s_loc)
+            ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+            before = cp.n_gather
+            out = cpar.ring_attention_bshd(ql, kl, vl, True)
+            out.backward(go[:, sl].contiguous())
+            ops.check_status("fused cp")
+            assert cp.n_gather == before + 2, "the peer-memory path was not taken"
+            assert _rel(out, ref[:, sl]) < 2e-2, rnd
+            for name, got, want in (("dq", ql.grad, qr.grad), ("dk", kl.grad, kr.grad), ("dv", vl.grad, vr.grad)):
+                assert _rel(got, want[:, sl]) < 3e-2, (name, rnd, _rel(got, want[:, sl]))
+    finally:
+        cpar.install_fused_cp(None)
+
+
+def test_fused_context_parallel_attention_2gpu():
+    run_gpu_ranks(_fused_cp_worker, 2)
