@@ -36,16 +36,65 @@ def time_fn(fn, iters, flush):
     return times[len(times) // 2]
 
 
+def grouped(args, peak, flush):
+    """(experts, rows per expert, in, out): gate+up and down projections of the MoE benchmark config
+    (64 experts of FFN 1024 at h2048, capacity 960 rows per expert and source rank) at EP = 8 and 2,
+    and an uneven dropless split."""
+    from picotron_b200.ops import grouped_gemm as gg
+    cases = [("ep8 gate+up", [7680] * 8, 2048, 2048), ("ep8 down", [7680] * 8, 1024, 2048),
+             ("ep2 gate+up", [1920] * 32, 2048, 2048), ("ep2 down", [1920] * 32, 1024, 2048),
+             ("uneven gate+up", [9000, 300, 4100, 77, 12000, 2500, 640, 5], 2048, 2048)]
+    for name, counts, d_in, d_out in cases:
+        G, n = len(counts), sum(counts)
+        layout = gg.GroupLayout.from_counts(counts, "cuda")
+        x = layout.pad(torch.randn(n, d_in, device="cuda", dtype=torch.bfloat16))
+        dy = layout.pad(torch.randn(n, d_out, device="cuda", dtype=torch.bfloat16))
+        w = torch.randn(G * d_out, d_in, device="cuda", dtype=torch.bfloat16)
+        dw32 = torch.zeros(G * d_out, d_in, device="cuda", dtype=torch.float32)
+        seg = layout.seg_start.tolist()
+        flops = 2.0 * n * d_in * d_out
+
+        def lib_fwd():
+            for e in range(G):
+                torch.matmul(x[seg[e]:seg[e + 1]], w[e * d_out:(e + 1) * d_out].t())
+
+        def lib_dgrad():
+            for e in range(G):
+                torch.matmul(dy[seg[e]:seg[e + 1]], w[e * d_out:(e + 1) * d_out])
+
+        def lib_wgrad():
+            for e in range(G):
+                torch.matmul(dy[seg[e]:seg[e + 1]].t(), x[seg[e]:seg[e + 1]])
+
+        rows = [("fwd", lambda: gg.grouped_gemm_nt(x, w, layout, d_out), lib_fwd),
+                ("dgrad", lambda: gg.grouped_gemm_nn(dy, w, layout, d_out), lib_dgrad),
+                ("wgrad+acc", lambda: gg.grouped_gemm_tn(dy, x, layout, dw32, accumulate=True), lib_wgrad)]
+        for rn, ours, lib in rows:
+            t_ours = time_fn(ours, args.iters, flush)
+            t_lib = time_fn(lib, args.iters, flush)
+            tf = flops / t_ours / 1e6
+            line = (f"{name:15s} G={G:2d} rows={n:6d} {d_in}->{d_out} {rn:10s} grouped {t_ours:8.1f} us {tf:7.1f} TFLOP/s | "
+                    f"{G} cuBLAS calls {t_lib:8.1f} us {flops / t_lib / 1e6:7.1f} TFLOP/s")
+            if peak:
+                line += f" | {tf / peak:.3f} of measured"
+            print(line, flush=True)
+        ops.check_status(name)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true", help="one small shape (for profiler captures)")
+    ap.add_argument("--grouped", action="store_true",
+                    help="grouped expert GEMMs (one launch for all local experts) vs one cuBLAS call per expert")
     args = ap.parse_args()
     peak = None
     pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(pk):
         peak = json.load(open(pk)).get("bf16_tflops")
     flush = torch.empty(64 * 1024 * 1024, device="cuda", dtype=torch.int32)
+    if args.grouped:
+        return grouped(args, peak, flush)
     shapes = [(8192, 6144, 2048), (8192, 2048, 2048), (8192, 16384, 2048), (8192, 2048, 8192),
               (8192, 49152, 2048), (4096, 12288, 4096), (4096, 22016, 4096), (4096, 4096, 11008)]
     if args.small:

@@ -226,3 +226,29 @@ def test_loss_free_bias_reduces_imbalance():
 
     off, on = cumulative_load(0.0), cumulative_load(0.01)
     assert on.std() < 0.5 * off.std(), (off.std().item(), on.std().item())
+
+
+def test_group_layout_pads_expert_segments_to_tiles():
+    """The padded expert-major layout of the grouped expert GEMM: segment starts are multiples of 128,
+    pad/unpad round-trip, padding rows are zero, and the per-expert restatement on the padded rows
+    equals the per-expert loop on the unpadded ones."""
+    from picotron_b200.ops.grouped_gemm import GroupLayout, grouped_linear_ref
+    counts = [5, 0, 300, 129, 128]
+    layout = GroupLayout.from_counts(counts, "cpu")
+    seg = layout.seg_start.tolist()
+    assert seg == [0, 128, 128, 512, 768, 896] and layout.rows == 896
+    assert layout.tile_group.tolist() == [0, 2, 2, 2, 3, 3, 4]
+    torch.manual_seed(0)
+    x = torch.randn(sum(counts), 16)
+    xp = layout.pad(x)
+    assert xp.shape == (896, 16) and torch.equal(layout.unpad(xp), x)
+    assert xp.abs().sum().item() == pytest.approx(x.abs().sum().item(), rel=1e-6)
+    ws = [torch.randn(24, 16) for _ in counts]
+    y = layout.unpad(grouped_linear_ref(xp, ws, layout))
+    ref, off = [], 0
+    for c, w in zip(counts, ws):
+        ref.append(x[off:off + c] @ w.t())
+        off += c
+    assert torch.allclose(y, torch.cat(ref), atol=1e-5)
+    uniform = GroupLayout.uniform(3, 256, "cpu")
+    assert uniform.pad_index is None and uniform.seg_start.tolist() == [0, 256, 512, 768]
