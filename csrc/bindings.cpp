@@ -10,6 +10,7 @@
 #include "attention/attention.h"
 #include "common/host.h"
 #include "elementwise/elementwise.h"
+#include "fused/cp_comm.h"
 #include "fused/dp_zero.h"
 #include "fused/ep_comm.h"
 #include "fused/tp_comm.h"
@@ -259,6 +260,24 @@ void scatter_rows(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs,
         "scatter_rows");
 }
 
+// Ulysses layout exchanges through peer memory; see fused/cp_comm.h. to_seq: src [b, s_local, world*cols]
+// -> peers' [b, world*s_local, cols]; otherwise the inverse.
+void a2a_push(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs, const std::vector<int64_t>& flag_ptrs,
+              int64_t world, int64_t my_rank, int64_t batch, int64_t s_local, int64_t cols, bool to_seq,
+              int64_t slot, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kBFloat16, "a2a_push: contiguous bf16");
+  TORCH_CHECK(src.numel() == batch * s_local * world * cols, "a2a_push: source size mismatch");
+  if (to_seq)
+    check(pico_a2a_heads_to_seq(src.data_ptr(), table_of(dst_ptrs), table_of(flag_ptrs), (int)world, (int)my_rank,
+                                (int)batch, (int)s_local, (int)cols, (int)slot, (uint32_t)epoch, stream_of(src)),
+          "a2a_heads_to_seq");
+  else
+    check(pico_a2a_seq_to_heads(src.data_ptr(), table_of(dst_ptrs), table_of(flag_ptrs), (int)world, (int)my_rank,
+                                (int)batch, (int)s_local, (int)cols, (int)slot, (uint32_t)epoch, stream_of(src)),
+          "a2a_seq_to_heads");
+}
+
 void zero1_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, at::Tensor& m,
                  at::Tensor& v, const c10::optional<at::Tensor>& master, int64_t shard_start, int64_t shard_len,
                  int64_t world, int64_t my_rank, double lr, double beta1, double beta2, double eps, double wd,
@@ -467,6 +486,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("slot_sum", &slot_sum);
   m.def("slot_sum_from", &slot_sum_from);
   m.def("scatter_rows", &scatter_rows);
+  m.def("a2a_push", &a2a_push);
   m.def("gemm_ex", &gemm_ex);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("zero1_adamw", &zero1_adamw);

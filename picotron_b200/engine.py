@@ -258,25 +258,34 @@ class TrainEngine:
         self._maybe_install_fused_cp()
 
     def _maybe_install_fused_cp(self):
-        """Ring context parallelism exchanges K/V and reduces dK/dV through NVLink peer memory
-        (``ops.fused_cp``) on the flat bf16 path; ``PICO_FUSED_CP=0`` keeps the NCCL point-to-point ring."""
+        """Context parallelism through NVLink peer memory on the flat bf16 path: ring attention gathers
+        K/V and reduces dK/dV with ``ops.fused_cp``, Ulysses does its all-to-alls with
+        ``ops.fused_ulysses``; ``PICO_FUSED_CP=0`` keeps the NCCL point-to-point ring / all-to-all."""
         import os
         from .parallel import context_parallel as cpar
         d, t, m, mc = self.cfg["distributed"], self.cfg["training"], self.pgm, self.model_config
+        from .parallel import ulysses as uly
         self.fused_cp = None
         cpar.install_fused_cp(None)
-        if not (self.flat and m.cp_world_size > 1 and d["cp_attention"] == "ring"
-                and os.environ.get("PICO_FUSED_CP", "1") != "0"):
+        uly.install_fused_ulysses(None)
+        if not (self.flat and m.cp_world_size > 1 and os.environ.get("PICO_FUSED_CP", "1") != "0"):
             return
-        from .ops.fused_cp import CPFused
         from .runtime.symm import SymmGroup
         head_dim = mc.hidden_size // mc.num_attention_heads
         kv_heads = mc.num_key_value_heads // m.tp_world_size
+        q_heads = mc.num_attention_heads // m.tp_world_size
         if head_dim not in (64, 128) or kv_heads < 1:
             return
+        s_local = t["seq_length"] // m.cp_world_size
         sg = SymmGroup(m.cp_group, device=self.device)
-        self.fused_cp = CPFused(sg, t["micro_batch_size"], t["seq_length"] // m.cp_world_size, kv_heads * head_dim)
-        cpar.install_fused_cp(self.fused_cp)
+        if d["cp_attention"] == "ring":
+            from .ops.fused_cp import CPFused
+            self.fused_cp = CPFused(sg, t["micro_batch_size"], s_local, kv_heads * head_dim)
+            cpar.install_fused_cp(self.fused_cp)
+        elif q_heads % m.cp_world_size == 0:
+            from .ops.fused_ulysses import UlyssesFused
+            self.fused_cp = UlyssesFused(sg, t["micro_batch_size"], s_local, q_heads * head_dim)
+            uly.install_fused_ulysses(self.fused_cp)
 
     def _split_expert_params(self) -> bool:
         return (self.cfg["distributed"]["ep_as_dp"] and self.pgm.ep_world_size > 1

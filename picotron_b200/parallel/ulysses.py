@@ -44,6 +44,15 @@ class _SeqAllToAll(torch.autograd.Function):
         return _all_to_all(grad.contiguous(), ctx.gather_dim, ctx.scatter_dim, ctx.group), None, None, None
 
 
+#: optional ``ops.fused_ulysses.UlyssesFused``: the all-to-alls as peer-memory store kernels
+_FUSED = None
+
+
+def install_fused_ulysses(u) -> None:
+    global _FUSED
+    _FUSED = u
+
+
 def ulysses_attention_bshd(q, k, v, causal: bool = True, sm_scale=None, group=None):
     """q: [b, s/cp, H, d]; k, v: [b, s/cp, Hkv, d] -> [b, s/cp, H, d]."""
     group = group if group is not None else pgm.get_pgm().cp_group
@@ -54,6 +63,12 @@ def ulysses_attention_bshd(q, k, v, causal: bool = True, sm_scale=None, group=No
     assert H % n == 0, f"Ulysses needs the local head count ({H}) divisible by the CP size ({n})"
     if kvh % n != 0:
         k, v = attn_ops._expand_kv(k, H), attn_ops._expand_kv(v, H)
+    u = _FUSED
+    if u is not None and u.sg.group is group and q.is_cuda and q.dtype == torch.bfloat16 \
+            and u.matches(q, True) and u.matches(k, True) and not attn_ops.reference_ops_forced_():
+        from ..ops import fused_ulysses as fu
+        out = attn_ops.attention(fu.heads_to_seq(q, u), fu.heads_to_seq(k, u), fu.heads_to_seq(v, u), causal, sm_scale)
+        return fu.seq_to_heads(out, u)
     # [b, s/cp, H, d] -> scatter heads (dim 2), gather sequence (dim 1) -> [b, s, H/cp, d]
     qg = _SeqAllToAll.apply(q, 2, 1, group)
     kg = _SeqAllToAll.apply(k, 2, 1, group)

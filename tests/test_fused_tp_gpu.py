@@ -319,3 +319,46 @@ def _fused_cp_worker(rank, world):
 
 def test_fused_context_parallel_attention_2gpu():
     run_gpu_ranks(_fused_cp_worker, 2)
+
+
+def _fused_ulysses_worker(rank, world):
+    """Ulysses attention with the peer-memory all-to-all kernels (``ops.fused_ulysses``) against
+    single-device attention over the full sequence, forward and backward, batch 2, GQA."""
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.ops import attention as A
+    from picotron_b200.ops.fused_ulysses import UlyssesFused
+    from picotron_b200.parallel import ulysses as uly
+    from picotron_b200.runtime.symm import SymmGroup
+    pgm.setup_process_group_manager(tp_size=1, cp_size=world, pp_size=1, dp_size=1)
+    group = pgm.get_pgm().cp_group
+    dev = torch.device("cuda", rank)
+    b, s_loc, H, Hkv, d = 2, 256, 8, 2 * world, 64
+    s = s_loc * world
+    u = UlyssesFused(SymmGroup(group, device=dev), b, s_loc, H * d)
+    uly.install_fused_ulysses(u)
+    try:
+        for rnd in range(3):
+            torch.manual_seed(10 + rnd)
+            q = torch.randn(b, s, H, d, device=dev, dtype=torch.bfloat16)
+            k = torch.randn(b, s, Hkv, d, device=dev, dtype=torch.bfloat16)
+            v = torch.randn(b, s, Hkv, d, device=dev, dtype=torch.bfloat16)
+            go = torch.randn(b, s, H, d, device=dev, dtype=torch.bfloat16)
+            qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
+            ref = A.attention_ref(qr, kr, vr, True)
+            ref.backward(go.float())
+            sl = slice(rank * s_loc, (rank + 1) * s_loc)
+            ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+            before = u.n_seq
+            out = uly.ulysses_attention_bshd(ql, kl, vl, True)
+            out.backward(go[:, sl].contiguous())
+            ops.check_status("fused ulysses")
+            assert u.n_seq == before + 4, "the peer-memory path was not taken"   # q, k, v forward + dout backward
+            assert _rel(out, ref[:, sl]) < 2e-2, rnd
+            for name, got, want in (("dq", ql.grad, qr.grad), ("dk", kl.grad, kr.grad), ("dv", vl.grad, vr.grad)):
+                assert _rel(got, want[:, sl]) < 3e-2, (name, rnd, _rel(got, want[:, sl]))
+    finally:
+        uly.install_fused_ulysses(None)
+
+
+def test_fused_ulysses_attention_2gpu():
+    run_gpu_ranks(_fused_ulysses_worker, 2)
