@@ -44,6 +44,8 @@ def grouped(args, peak, flush):
     cases = [("ep8 gate+up", [7680] * 8, 2048, 2048), ("ep8 down", [7680] * 8, 1024, 2048),
              ("ep2 gate+up", [1920] * 32, 2048, 2048), ("ep2 down", [1920] * 32, 1024, 2048),
              ("uneven gate+up", [9000, 300, 4100, 77, 12000, 2500, 640, 5], 2048, 2048)]
+    if args.small:
+        cases = [("small gate+up", [3072] * 8, 2048, 2048)]
     for name, counts, d_in, d_out in cases:
         G, n = len(counts), sum(counts)
         layout = gg.GroupLayout.from_counts(counts, "cuda")
