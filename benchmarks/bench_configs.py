@@ -49,12 +49,15 @@ def build_cfg(args, world):
             "model": dict(name="moe-ep8-bench", num_hidden_layers=layers, init_std=0.02, num_experts=64,
                           num_experts_per_tok=6, num_shared_experts=0, shared_expert_intermediate_size=2048,
                           ep_capacity_factor=args.capacity, ep_capacity_dropless=args.dropless, ep_fp8_dispatch=True,
-                          ep_num_tiles=4, router_aux_loss_coef=1e-3, router_bias_update_rate=1e-3),
+                          ep_num_tiles=4, router_aux_loss_coef=1e-3, router_bias_update_rate=1e-3,
+                          ep_backend=args.ep_backend),
             "training": dict(seed=1, learning_rate=3e-4, seq_length=args.seq or 4096, micro_batch_size=2,
                              gradient_accumulation_steps=1, num_samples=1 << 14),
             "dataset": dict(name="synthetic"),
         }, (f"ep{world} capacity{args.capacity} {'dropless' if args.dropless else 'drop'} fp8-dispatch"
-            if args.capacity > 0 else f"ep{world} tiled-4 variable-size exchange fp8-dispatch")
+            if args.capacity > 0 else
+            (f"ep{world} dropless, peer-memory exchange with device-side layout" if args.ep_backend == "fused"
+             else f"ep{world} tiled-4 variable-size exchange fp8-dispatch"))
     if args.config == "cp":
         layers = args.layers or 16
         seq = args.seq or 16384 * world
@@ -79,6 +82,8 @@ def main():
     ap.add_argument("--pp-engine", default="interleaved")
     ap.add_argument("--cp-attention", default="ring")
     ap.add_argument("--dropless", action="store_true")
+    ap.add_argument("--ep-backend", default="torch",
+                    help="moe with --capacity 0: 'fused' = dropless exchange through peer memory, layout on device")
     ap.add_argument("--capacity", type=float, default=1.25,
                     help="moe: capacity factor; 0 selects the variable-size tiled exchange")
     args = ap.parse_args()

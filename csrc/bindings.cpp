@@ -13,6 +13,7 @@
 #include "fused/cp_comm.h"
 #include "fused/dp_zero.h"
 #include "fused/ep_comm.h"
+#include "fused/ep_var.h"
 #include "fused/tp_comm.h"
 #include "gemm/gemm.h"
 #include "runtime/symm.h"
@@ -278,6 +279,52 @@ void a2a_push(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs, const
           "a2a_seq_to_heads");
 }
 
+// Dropless expert-parallel exchange with device-side layout; see fused/ep_var.h.
+void ep_var_layout(const at::Tensor& counts_table, int64_t ep, int64_t L, int64_t my_rank, int64_t max_rows,
+                   at::Tensor& send_blocks, at::Tensor& return_blocks, at::Tensor& seg_start, at::Tensor& seg_len,
+                   at::Tensor& tile_group) {
+  c10::cuda::CUDAGuard guard(counts_table.device());
+  for (const at::Tensor* t : std::initializer_list<const at::Tensor*>{&counts_table, &send_blocks, &return_blocks,
+                                                                      &seg_start, &seg_len, &tile_group})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "ep_var_layout: int32 CUDA tensors");
+  TORCH_CHECK(counts_table.numel() >= ep * ep * L && send_blocks.numel() >= ep * L * 4 &&
+                  return_blocks.numel() >= ep * L * 4 && seg_start.numel() >= L + 1 && seg_len.numel() >= L &&
+                  tile_group.numel() >= max_rows / 128,
+              "ep_var_layout: array too small");
+  check(pico_ep_var_layout(counts_table.data_ptr<int>(), (int)ep, (int)L, (int)my_rank, (int)max_rows,
+                           send_blocks.data_ptr<int>(), return_blocks.data_ptr<int>(), seg_start.data_ptr<int>(),
+                           seg_len.data_ptr<int>(), tile_group.data_ptr<int>(), stream_of(counts_table)),
+        "ep_var_layout");
+}
+
+void ep_var_exchange(const at::Tensor& src, const c10::optional<at::Tensor>& row_index, int64_t index_div,
+                     const at::Tensor& blocks, int64_t num_blocks, const std::vector<int64_t>& dst_ptrs,
+                     const std::vector<int64_t>& flag_ptrs, int64_t ep, int64_t my_rank, int64_t d, int64_t slot,
+                     int64_t epoch) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.scalar_type() == at::kBFloat16 && src.is_contiguous() && src.size(-1) == d,
+              "ep_var_exchange: contiguous bf16 rows of width d");
+  TORCH_CHECK(blocks.scalar_type() == at::kInt && blocks.is_contiguous() && blocks.numel() >= num_blocks * 4,
+              "ep_var_exchange: int32 block table");
+  const int32_t* idx = nullptr;
+  if (row_index.has_value() && row_index->defined()) {
+    TORCH_CHECK(row_index->scalar_type() == at::kInt && row_index->is_contiguous(), "ep_var_exchange: int32 row index");
+    idx = row_index->data_ptr<int>();
+  }
+  check(pico_ep_var_exchange(src.data_ptr(), idx, (int)index_div, blocks.data_ptr<int>(), (int)num_blocks,
+                             table_of(dst_ptrs), table_of(flag_ptrs), (int)ep, (int)my_rank, (int)d, (int)slot,
+                             (uint32_t)epoch, stream_of(src)),
+        "ep_var_exchange");
+}
+
+void ep_var_zero_padding(at::Tensor& buf, const at::Tensor& seg_start, const at::Tensor& seg_len, int64_t L, int64_t d) {
+  c10::cuda::CUDAGuard guard(buf.device());
+  TORCH_CHECK(buf.scalar_type() == at::kBFloat16 && buf.is_contiguous(), "ep_var_zero_padding: contiguous bf16");
+  check(pico_ep_var_zero_padding(buf.data_ptr(), seg_start.data_ptr<int>(), seg_len.data_ptr<int>(), (int)L, (int)d,
+                                 stream_of(buf)),
+        "ep_var_zero_padding");
+}
+
 void zero1_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, at::Tensor& m,
                  at::Tensor& v, const c10::optional<at::Tensor>& master, int64_t shard_start, int64_t shard_len,
                  int64_t world, int64_t my_rank, double lr, double beta1, double beta2, double eps, double wd,
@@ -487,6 +534,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("slot_sum_from", &slot_sum_from);
   m.def("scatter_rows", &scatter_rows);
   m.def("a2a_push", &a2a_push);
+  m.def("ep_var_layout", &ep_var_layout);
+  m.def("ep_var_exchange", &ep_var_exchange);
+  m.def("ep_var_zero_padding", &ep_var_zero_padding);
   m.def("gemm_ex", &gemm_ex);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("zero1_adamw", &zero1_adamw);

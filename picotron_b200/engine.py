@@ -298,7 +298,6 @@ class TrainEngine:
         mc, m, t = self.model_config, self.pgm, self.cfg["training"]
         self.fused_ep = None
         if not (self.flat and m.ep_world_size > 1 and getattr(mc, "num_experts", 1) > 1
-                and (getattr(mc, "ep_capacity_factor", 0.0) or 0.0) > 0
                 and os.environ.get("PICO_FUSED_EP", "1") != "0"):
             return
         from .ops.fused_ep import EPFused
@@ -308,6 +307,21 @@ class TrainEngine:
         tokens = t["micro_batch_size"] * (t["seq_length"] // m.cp_world_size)
         if self.cfg["distributed"]["sequence_parallel"] and m.tp_world_size > 1:
             tokens //= m.tp_world_size
+        if (getattr(mc, "ep_capacity_factor", 0.0) or 0.0) <= 0:
+            # dropless: ``ep_backend`` "fused" (or "deepep", whose role it takes here) selects the
+            # peer-memory exchange with the layout computed on the device
+            if getattr(mc, "ep_backend", "torch") not in ("fused", "deepep"):
+                return
+            from .ops.fused_ep_var import EPVarFused
+            layers = [mod for mod in self.model.modules() if isinstance(mod, MoELayer)]
+            if not layers or layers[0].expert_dim % 128 != 0:
+                return
+            sg = SymmGroup(m.ep_group, device=self.device)
+            self.fused_ep = EPVarFused(sg, layers[0].num_local_experts, layers[0].expert_dim,
+                                       tokens * mc.num_experts_per_tok)
+            for mod in layers:
+                mod.fused_ep_var = self.fused_ep
+            return
         cap = compute_capacity(tokens, mc.num_experts_per_tok, mc.num_experts, mc.ep_capacity_factor)
         layers = [mod for mod in self.model.modules() if isinstance(mod, MoELayer)]
         if not layers or layers[0].expert_dim % 8 != 0:

@@ -1,0 +1,137 @@
+"""Dropless expert-parallel dispatch and combine through NVLink peer memory, laid out on the device.
+
+The variable-size exchange of the reference (picotron/expert_parallel/expert_parallel.py:260-269,
+383-400: split sizes by ``all_to_all_single`` followed by ``.tolist()`` on the host, then two
+``all_to_all_single`` calls with those splits) becomes:
+
+1. every rank publishes its per-expert row counts into all peers' count tables (one store kernel);
+2. one small kernel derives the whole layout from the ``[ep, E]`` table: where each outgoing block
+   lands in the receiver's expert-major buffer, the receiver's expert segments padded to 128-row
+   tiles (``seg_start`` / ``tile_group`` — exactly what the grouped expert GEMM reads from device
+   memory), and the way back;
+3. the rows are stored straight into the peers' buffers at those offsets; the outputs return the
+   same way into the sender's expert-sorted order.
+
+Nothing is copied to the host, no row is dropped and no capacity is needed; the receive buffer holds
+``slack`` times the average load of a rank (a load beyond that is reported as an error, never written
+out of bounds). Dispatch and return are each other's backward.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+
+from . import count_launch, ext
+from .grouped_gemm import GroupLayout
+
+COUNT_SLOTS = (50, 51)
+DISPATCH_SLOTS = (52, 53)
+RETURN_SLOTS = (54, 55)
+
+
+@dataclass
+class VarPlan:
+    send_blocks: torch.Tensor      # [E, 4] int32
+    return_blocks: torch.Tensor    # [ep * L, 4] int32
+    seg_start: torch.Tensor        # [L + 1] int32
+    seg_len: torch.Tensor          # [L] int32
+    layout: GroupLayout            # device-side layout of the receive buffer for the grouped GEMM
+
+
+class EPVarFused:
+    def __init__(self, symm_group, num_local_experts: int, dim: int, rows_per_rank: int, slack: float = 1.5):
+        self.sg = symm_group
+        self.ep, self.rank = symm_group.world, symm_group.rank
+        self.L, self.d = num_local_experts, dim
+        self.E = self.ep * self.L
+        self.rows_per_rank = rows_per_rank
+        self.max_rows = (int(slack * rows_per_rank) + self.L * 128 + 127) // 128 * 128
+        self.counts_buf = [symm_group.alloc(self.ep * self.E * 4) for _ in range(2)]
+        self.recv_buf = [symm_group.alloc(self.max_rows * dim * 2) for _ in range(2)]
+        self.ret_buf = [symm_group.alloc(rows_per_rank * dim * 2) for _ in range(2)]
+        for b in self.counts_buf + self.recv_buf + self.ret_buf:
+            b.local.zero_()
+        self.n = {"count": 0, "dispatch": 0, "return": 0}
+        self.timeout_ms = int(os.environ.get("PICO_COMM_TIMEOUT_MS", "20000"))
+        torch.cuda.synchronize()
+        self.sg.barrier()
+
+    def _next(self, kind: str, slots):
+        c = self.n[kind] % 2
+        self.n[kind] += 1
+        return c, slots[c], self.sg.next_epoch(slots[c])
+
+    def plan(self, counts: torch.Tensor) -> VarPlan:
+        """counts: [E] int32 (device), rows of this rank per global expert."""
+        assert counts.dtype == torch.int32 and counts.numel() == self.E
+        c, slot, epoch = self._next("count", COUNT_SLOTS)
+        e = ext()
+        row = counts.contiguous().view(torch.bfloat16).view(1, 2 * self.E)     # raw bytes of the int32 row
+        e.push_rows(row, self.counts_buf[c].ptrs, self.sg.flags.ptrs, self.ep, self.rank, 1, 2 * self.E, slot, epoch)
+        self.sg.wait(slot, epoch, self.timeout_ms)
+        table = self.counts_buf[c].view(torch.int32, (self.ep, self.E))
+        dev = counts.device
+        send_blocks = torch.empty((self.E, 4), device=dev, dtype=torch.int32)
+        return_blocks = torch.empty((self.ep * self.L, 4), device=dev, dtype=torch.int32)
+        seg_start = torch.empty(self.L + 1, device=dev, dtype=torch.int32)
+        seg_len = torch.empty(self.L, device=dev, dtype=torch.int32)
+        tile_group = torch.empty(self.max_rows // 128, device=dev, dtype=torch.int32)
+        e.ep_var_layout(table, self.ep, self.L, self.rank, self.max_rows, send_blocks, return_blocks, seg_start,
+                        seg_len, tile_group)
+        count_launch(3)
+        layout = GroupLayout(self.L, self.max_rows, seg_start, tile_group, None)
+        return VarPlan(send_blocks, return_blocks, seg_start, seg_len, layout)
+
+    def dispatch(self, rows_sorted: torch.Tensor, plan: VarPlan) -> torch.Tensor:
+        """[rows_per_rank, d] in this rank's expert-sorted order -> [max_rows, d] padded expert-major
+        rows of the local experts (padding rows zero; rows past the last segment are unspecified)."""
+        c, slot, epoch = self._next("dispatch", DISPATCH_SLOTS)
+        e = ext()
+        e.ep_var_exchange(rows_sorted, None, 1, plan.send_blocks, self.E, self.recv_buf[c].ptrs, self.sg.flags.ptrs,
+                          self.ep, self.rank, self.d, slot, epoch)
+        self.sg.wait(slot, epoch, self.timeout_ms)
+        buf = self.recv_buf[c].view(torch.bfloat16, (self.max_rows, self.d))
+        e.ep_var_zero_padding(buf, plan.seg_start, plan.seg_len, self.L, self.d)
+        count_launch(3)
+        return buf.clone()
+
+    def give_back(self, rows_padded: torch.Tensor, plan: VarPlan) -> torch.Tensor:
+        """[max_rows, d] padded expert-major rows -> [rows_per_rank, d] in the senders' sorted order."""
+        c, slot, epoch = self._next("return", RETURN_SLOTS)
+        ext().ep_var_exchange(rows_padded, None, 1, plan.return_blocks, self.ep * self.L, self.ret_buf[c].ptrs,
+                              self.sg.flags.ptrs, self.ep, self.rank, self.d, slot, epoch)
+        self.sg.wait(slot, epoch, self.timeout_ms)
+        count_launch(2)
+        return self.ret_buf[c].view(torch.bfloat16, (self.rows_per_rank, self.d)).clone()
+
+
+class _VarDispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows_sorted, plan: VarPlan, epv: EPVarFused):
+        ctx.plan, ctx.epv = plan, epv
+        return epv.dispatch(rows_sorted.contiguous(), plan)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.epv.give_back(g.contiguous(), ctx.plan), None, None
+
+
+class _VarReturn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows_padded, plan: VarPlan, epv: EPVarFused):
+        ctx.plan, ctx.epv = plan, epv
+        return epv.give_back(rows_padded.contiguous(), plan)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.epv.dispatch(g.contiguous(), ctx.plan), None, None
+
+
+def var_dispatch(rows_sorted, plan: VarPlan, epv: EPVarFused):
+    return _VarDispatch.apply(rows_sorted, plan, epv)
+
+
+def var_return(rows_padded, plan: VarPlan, epv: EPVarFused):
+    return _VarReturn.apply(rows_padded, plan, epv)

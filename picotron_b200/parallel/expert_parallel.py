@@ -114,6 +114,8 @@ class MoELayer(nn.Module):
         self._shared_stream = None
         #: optional ``ops.fused_ep.EPFused``: capacity-mode exchanges through NVLink peer memory
         self.fused_ep = None
+        #: optional ``ops.fused_ep_var.EPVarFused``: dropless variable-size exchange through peer memory
+        self.fused_ep_var = None
 
     def reset_parameters(self):
         # experts use the same RNG stream on every EP rank so replicated parameters stay in sync
@@ -256,6 +258,19 @@ class MoELayer(nn.Module):
                                       self.ep_fp8_granularity)
         return epc.all_to_all(rows_sorted, plan.out_splits, plan.in_splits, self.ep_group)
 
+    def _routed_fused_var(self, routed, expert_idx):
+        """Dropless exchange with the layout computed on the device (``ops.fused_ep_var``): no host
+        synchronisation, rows stored straight into the owners' expert-major buffers, experts as grouped
+        GEMMs over the padded segments, outputs returned into this rank's sorted order."""
+        from ..ops import fused_ep_var as fv
+        epv = self.fused_ep_var
+        order, inv = _argsort_inv(expert_idx)
+        counts = torch.bincount(expert_idx, minlength=self.num_experts).to(torch.int32)
+        plan = epv.plan(counts)
+        recv = fv.var_dispatch(routed[order], plan, epv)
+        y_pad = self._experts_on_layout(recv, plan.layout)
+        return fv.var_return(y_pad, plan, epv)[inv]
+
     def _routed_naive(self, routed, expert_idx):
         plan = self.plan(expert_idx)
         x = routed[plan.order]
@@ -286,7 +301,11 @@ class MoELayer(nn.Module):
                                       self.ep_capacity_dropless, self.ep_max_rounds, tokens=latent)
             self.last_dropped_fraction = dropped
         else:
-            if self.ep_world_size > 1 and self.ep_num_tiles > 1:
+            epv = self.fused_ep_var
+            if epv is not None and routed.is_cuda and routed.dtype == torch.bfloat16 \
+                    and routed.shape[0] == epv.rows_per_rank and self._grouped_ok(routed):
+                y_rows = self._routed_fused_var(routed, expert_idx)
+            elif self.ep_world_size > 1 and self.ep_num_tiles > 1:
                 from .tiled_moe import tiled_moe
                 y_rows = tiled_moe(self, routed, expert_idx, self.ep_num_tiles)
             else:

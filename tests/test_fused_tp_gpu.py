@@ -362,3 +362,55 @@ def _fused_ulysses_worker(rank, world):
 
 def test_fused_ulysses_attention_2gpu():
     run_gpu_ranks(_fused_ulysses_worker, 2)
+
+
+def _ep_var_worker(rank, world):
+    """Dropless MoE layer on EP=2 with the variable-size exchange laid out on the device and carried
+    through peer memory (``ops.fused_ep_var``) against the NCCL variable-size all-to-all path of the
+    same layer: outputs and gradients, several rounds with different (skewed) routings so both copies
+    of every buffer are reused and experts with few or no rows occur."""
+    import types
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.ops.fused_ep_var import EPVarFused
+    from picotron_b200.parallel.expert_parallel import MoELayer
+    from picotron_b200.runtime.symm import SymmGroup
+    pgm.setup_process_group_manager(tp_size=1, cp_size=1, pp_size=1, dp_size=1, ep_size=world)
+    dev = torch.device("cuda", rank)
+    sg = SymmGroup(pgm.get_pgm().ep_group, device=dev)
+    cfg = types.SimpleNamespace(hidden_size=512, intermediate_size=256, num_experts=8, num_experts_per_tok=2,
+                                num_shared_experts=1, norm_topk_prob=True, ep_capacity_factor=0.0, init_std=0.05,
+                                ep_overlap=False)
+    torch.manual_seed(3)
+    layer = MoELayer(cfg).to(dev).to(torch.bfloat16)
+    T = 512
+    epv = EPVarFused(sg, layer.num_local_experts, 512, T * 2, slack=2.0)
+    for rnd in range(3):
+        torch.manual_seed(100 * rnd + rank)
+        x = torch.randn(2, 256, 512, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():     # skew the router so that some experts get (almost) nothing
+            layer.expert_bias.zero_()
+            layer.gate.weight[rnd].add_(0.5)
+            layer.gate.weight[7 - rnd].sub_(0.5)
+        outs = []
+        for fused in (False, True):
+            layer.fused_ep_var = epv if fused else None
+            xi = x.clone().requires_grad_(True)
+            layer.zero_grad()
+            before = epv.n["dispatch"]
+            y = layer(xi)
+            y.float().square().mean().backward()
+            assert (epv.n["dispatch"] - before == 2) == fused, "wrong path taken"
+            outs.append((y.detach().float(), xi.grad.float(),
+                         layer.local_experts[0].down_proj.weight.grad.float().clone(),
+                         layer.local_experts[-1].gate_proj.weight.grad.float().clone(),
+                         layer.gate.weight.grad.float().clone()))
+        ops.check_status(f"fused dropless ep round {rnd}")
+        names = ("output", "input grad", "expert down grad", "expert gate grad", "router grad")
+        for n, a, b in zip(names, outs[1], outs[0]):
+            rel = ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+            assert rel < 3e-2, (n, rnd, rel)
+    layer.fused_ep_var = None
+
+
+def test_fused_dropless_ep_2gpu():
+    run_gpu_ranks(_ep_var_worker, 2)
