@@ -299,8 +299,8 @@ void ep_var_layout(const at::Tensor& counts_table, int64_t ep, int64_t L, int64_
 
 void ep_var_exchange(const at::Tensor& src, const c10::optional<at::Tensor>& row_index, int64_t index_div,
                      const at::Tensor& blocks, int64_t num_blocks, const std::vector<int64_t>& dst_ptrs,
-                     const std::vector<int64_t>& flag_ptrs, int64_t ep, int64_t my_rank, int64_t d, int64_t slot,
-                     int64_t epoch) {
+                     const std::vector<int64_t>& scale_ptrs, const std::vector<int64_t>& flag_ptrs, int64_t ep,
+                     int64_t my_rank, int64_t d, bool quant, int64_t slot, int64_t epoch) {
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(src.scalar_type() == at::kBFloat16 && src.is_contiguous() && src.size(-1) == d,
               "ep_var_exchange: contiguous bf16 rows of width d");
@@ -312,9 +312,19 @@ void ep_var_exchange(const at::Tensor& src, const c10::optional<at::Tensor>& row
     idx = row_index->data_ptr<int>();
   }
   check(pico_ep_var_exchange(src.data_ptr(), idx, (int)index_div, blocks.data_ptr<int>(), (int)num_blocks,
-                             table_of(dst_ptrs), table_of(flag_ptrs), (int)ep, (int)my_rank, (int)d, (int)slot,
-                             (uint32_t)epoch, stream_of(src)),
+                             table_of(dst_ptrs), table_of(scale_ptrs), table_of(flag_ptrs), (int)ep, (int)my_rank,
+                             (int)d, quant ? 1 : 0, (int)slot, (uint32_t)epoch, stream_of(src)),
         "ep_var_exchange");
+}
+
+void ep_var_dequant(const at::Tensor& payload, const at::Tensor& scales, at::Tensor& out, const at::Tensor& rows_in_use,
+                    int64_t max_rows, int64_t d) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && rows_in_use.scalar_type() == at::kInt,
+              "ep_var_dequant: bf16 output, int32 row count");
+  check(pico_ep_var_dequant(payload.data_ptr(), (const float*)scales.data_ptr(), out.data_ptr(),
+                            rows_in_use.data_ptr<int>(), (int)max_rows, (int)d, stream_of(out)),
+        "ep_var_dequant");
 }
 
 void ep_var_zero_padding(at::Tensor& buf, const at::Tensor& seg_start, const at::Tensor& seg_len, int64_t L, int64_t d) {
@@ -536,6 +546,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("a2a_push", &a2a_push);
   m.def("ep_var_layout", &ep_var_layout);
   m.def("ep_var_exchange", &ep_var_exchange);
+  m.def("ep_var_dequant", &ep_var_dequant);
   m.def("ep_var_zero_padding", &ep_var_zero_padding);
   m.def("gemm_ex", &gemm_ex);
   m.def("gemm_grouped", &gemm_grouped);

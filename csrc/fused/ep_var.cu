@@ -1,6 +1,7 @@
 #include "ep_var.h"
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "../common/host.h"
 #include "../common/ptx.cuh"
@@ -108,11 +109,15 @@ __device__ __forceinline__ void var_raise_when_done(unsigned int* counter, PicoP
   }
 }
 
-// one warp per row; the rows of every block are spread over all warps of the grid
+// one warp per row; the rows of every block are spread over all warps of the grid.
+// QUANT: rows are quantised to FP8 E4M3 with one fp32 scale per 1 x 128 block while they are being
+// sent (d bytes per row into `dst`, d / 128 floats per row into `scales`).
+template <bool QUANT>
 __global__ void __launch_bounds__(256)
 ep_var_exchange_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ row_index, int index_div,
-                       const int32_t* __restrict__ blocks, int num_blocks, PicoPeerTable dst, PicoPeerTable flags,
-                       int ep, int my_rank, int d, int slot, uint32_t epoch, unsigned int* counter) {
+                       const int32_t* __restrict__ blocks, int num_blocks, PicoPeerTable dst, PicoPeerTable scales,
+                       PicoPeerTable flags, int ep, int my_rank, int d, int slot, uint32_t epoch,
+                       unsigned int* counter) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
   const int gwarp = blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
@@ -123,15 +128,71 @@ ep_var_exchange_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __r
     const int src_row = __ldg(blocks + b * 4 + 1);
     const int dst_rank = __ldg(blocks + b * 4 + 2);
     const int dst_row = __ldg(blocks + b * 4 + 3);
-    uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.ptr[dst_rank]) + (int64_t)dst_row * d);
     for (int j = gwarp; j < cnt; j += nwarps) {
       const int64_t srow = row_index ? (int64_t)(__ldg(row_index + src_row + j) / index_div) : (int64_t)(src_row + j);
       const uint4* in = reinterpret_cast<const uint4*>(src + srow * d);
-      uint4* o = out + (int64_t)j * vec;
-      for (int v = lane; v < vec; v += 32) o[v] = in[v];
+      const int64_t drow = (int64_t)dst_row + j;
+      if (!QUANT) {
+        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.ptr[dst_rank]) + drow * d);
+        for (int v = lane; v < vec; v += 32) o[v] = in[v];
+      } else {
+        uint8_t* out = reinterpret_cast<uint8_t*>(dst.ptr[dst_rank]) + drow * d;
+        float* sc = reinterpret_cast<float*>(scales.ptr[dst_rank]) + drow * (d / 128);
+        for (int v = lane; v < vec; v += 32) {   // d % 256 == 0: all 32 lanes take part in the shuffles
+          const uint4 raw = in[v];
+          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+          float f[8];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 t = __bfloat1622float2(p2[q]);
+            f[2 * q] = t.x;
+            f[2 * q + 1] = t.y;
+          }
+          float amax = 0.f;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
+          // 16 lanes x 8 elements = one 128-element block
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          const float scale = fmaxf(amax, 1e-12f) / 448.f;
+          const float inv = 1.f / scale;
+          uint2 qv;
+          uint8_t* qb = reinterpret_cast<uint8_t*>(&qv);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            qb[q] = (uint8_t)__nv_cvt_float_to_fp8(fminf(fmaxf(f[q] * inv, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+          reinterpret_cast<uint2*>(out)[v] = qv;
+          if ((lane & 15) == 0) sc[v / 16] = scale;
+        }
+      }
     }
   }
   var_raise_when_done(counter, flags, ep, my_rank, slot, epoch);
+}
+
+// payload / scales -> bf16 for the rows in use (their number is read from device memory)
+__global__ void __launch_bounds__(256)
+ep_var_dequant_kernel(const uint8_t* __restrict__ payload, const float* __restrict__ scales,
+                      __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ rows_in_use, int d) {
+  const int64_t rows = *rows_in_use;
+  const int64_t nvec = rows * d / 8;
+  const int vec_per_row = d / 8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / vec_per_row;
+    const int v = (int)(i % vec_per_row);
+    const float scale = scales[row * (d / 128) + v / 16];
+    const uint2 q = reinterpret_cast<const uint2*>(payload)[i];
+    const uint8_t* qb = reinterpret_cast<const uint8_t*>(&q);
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half_raw h0 = __nv_cvt_fp8_to_halfraw(qb[2 * j], __NV_E4M3);
+      const __half_raw h1 = __nv_cvt_fp8_to_halfraw(qb[2 * j + 1], __NV_E4M3);
+      op[j] = __floats2bfloat162_rn(__half2float(__half(h0)) * scale, __half2float(__half(h1)) * scale);
+    }
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
 }
 
 __global__ void ep_var_zero_padding_kernel(__nv_bfloat16* __restrict__ buf, const int32_t* __restrict__ seg_start,
@@ -179,19 +240,44 @@ extern "C" int pico_ep_var_layout(const int32_t* counts_table, int ep, int L, in
 }
 
 extern "C" int pico_ep_var_exchange(const void* src, const int32_t* row_index, int index_div,
-                                    const int32_t* blocks, int num_blocks, PicoPeerTable dst, PicoPeerTable flags,
-                                    int ep, int my_rank, int d, int slot, uint32_t epoch, cudaStream_t stream) {
-  if (ep < 1 || ep > PICO_MAX_PEERS || d % 8 != 0 || slot < 0 || slot >= PICO_FLAG_SLOTS || index_div < 1) {
-    pico_host::set_error("ep_var_exchange: ep %d / d %d (multiple of 8) / slot %d out of range", ep, d, slot);
+                                    const int32_t* blocks, int num_blocks, PicoPeerTable dst, PicoPeerTable scales,
+                                    PicoPeerTable flags, int ep, int my_rank, int d, int quant, int slot,
+                                    uint32_t epoch, cudaStream_t stream) {
+  if (ep < 1 || ep > PICO_MAX_PEERS || d % 8 != 0 || slot < 0 || slot >= PICO_FLAG_SLOTS || index_div < 1 ||
+      (quant && d % 256 != 0)) {
+    pico_host::set_error("ep_var_exchange: ep %d / d %d (multiple of 8; of 256 when quantising) / slot %d out of range",
+                         ep, d, slot);
     return -2;
   }
   unsigned int* counter = var_counter();
   if (!counter) return -1;
   const int grid = pico_host::num_sms() * 2;
-  ep_var_exchange_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)src, row_index, index_div, blocks,
-                                                   num_blocks, dst, flags, ep, my_rank, d, slot, epoch, counter);
+  if (quant)
+    ep_var_exchange_kernel<true><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)src, row_index, index_div, blocks,
+                                                           num_blocks, dst, scales, flags, ep, my_rank, d, slot, epoch,
+                                                           counter);
+  else
+    ep_var_exchange_kernel<false><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)src, row_index, index_div, blocks,
+                                                            num_blocks, dst, scales, flags, ep, my_rank, d, slot, epoch,
+                                                            counter);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) pico_host::set_error("ep_var_exchange: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+extern "C" int pico_ep_var_dequant(const void* payload, const float* scales, void* out, const int32_t* rows_in_use,
+                                   int max_rows, int d, cudaStream_t stream) {
+  if (d % 128 != 0 || max_rows < 1) {
+    pico_host::set_error("ep_var_dequant: row width %d must be a multiple of 128", d);
+    return -2;
+  }
+  int64_t blocks = ((int64_t)max_rows * d / 8 + 255) / 256;
+  const int cap = pico_host::num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  ep_var_dequant_kernel<<<(int)blocks, 256, 0, stream>>>((const uint8_t*)payload, scales, (__nv_bfloat16*)out,
+                                                        rows_in_use, d);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) pico_host::set_error("ep_var_dequant: %s", cudaGetErrorString(e));
   return (int)e;
 }
 

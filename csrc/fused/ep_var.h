@@ -31,11 +31,18 @@ int pico_ep_var_layout(const int32_t* counts_table, int ep, int L, int my_rank, 
 
 // Copy variable-size row blocks into peers' buffers: block b = blocks[b] = {count, src_row, dst_rank,
 // dst_row}; row j of the block is read from src at row (row_index ? row_index[src_row + j] / index_div
-// : src_row + j) and stored to dst.ptr[dst_rank] at row dst_row + j (rows of d bf16). When the last
-// CTA finishes, flag [slot][my_rank] = epoch is raised on every rank.
+// : src_row + j) and stored to dst.ptr[dst_rank] at row dst_row + j (rows of d bf16). With quant = 1
+// the rows are quantised to FP8 E4M3 with one fp32 scale per 1 x 128 block while they are being sent:
+// dst receives d bytes per row and `scales` d / 128 floats per row (d a multiple of 256). When the
+// last CTA finishes, flag [slot][my_rank] = epoch is raised on every rank.
 int pico_ep_var_exchange(const void* src, const int32_t* row_index, int index_div, const int32_t* blocks,
-                         int num_blocks, PicoPeerTable dst, PicoPeerTable flags, int ep, int my_rank, int d,
-                         int slot, uint32_t epoch, cudaStream_t stream);
+                         int num_blocks, PicoPeerTable dst, PicoPeerTable scales, PicoPeerTable flags, int ep,
+                         int my_rank, int d, int quant, int slot, uint32_t epoch, cudaStream_t stream);
+
+// Receiver side of a quantised exchange: payload / scales -> bf16 for rows [0, *rows_in_use) (a device
+// integer, e.g. seg_start[L]); call after the senders' flags have been awaited.
+int pico_ep_var_dequant(const void* payload, const float* scales, void* out, const int32_t* rows_in_use,
+                        int max_rows, int d, cudaStream_t stream);
 
 // Zero the padding rows [seg_start[l] + seg_len[l], seg_start[l+1]) of a [rows, d] bf16 buffer, so
 // that padded tiles contribute exact zeros to the grouped GEMMs.

@@ -318,7 +318,8 @@ class TrainEngine:
                 return
             sg = SymmGroup(m.ep_group, device=self.device)
             self.fused_ep = EPVarFused(sg, layers[0].num_local_experts, layers[0].expert_dim,
-                                       tokens * mc.num_experts_per_tok)
+                                       tokens * mc.num_experts_per_tok,
+                                       fp8_dispatch=bool(getattr(mc, "ep_fp8_dispatch", False)))
             for mod in layers:
                 mod.fused_ep_var = self.fused_ep
             return

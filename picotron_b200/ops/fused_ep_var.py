@@ -41,7 +41,11 @@ class VarPlan:
 
 
 class EPVarFused:
-    def __init__(self, symm_group, num_local_experts: int, dim: int, rows_per_rank: int, slack: float = 1.5):
+    def __init__(self, symm_group, num_local_experts: int, dim: int, rows_per_rank: int, slack: float = 1.5,
+                 fp8_dispatch: bool = False):
+        """``fp8_dispatch``: forward dispatch rows travel as FP8 E4M3 with 1x128 block scales (quantised in
+        the send kernel, dequantised at the receiver); gradients and the return path stay bf16, like the
+        straight-through backward of picotron/expert_parallel/ep_communications.py:59-118."""
         self.sg = symm_group
         self.ep, self.rank = symm_group.world, symm_group.rank
         self.L, self.d = num_local_experts, dim
@@ -51,7 +55,10 @@ class EPVarFused:
         self.counts_buf = [symm_group.alloc(self.ep * self.E * 4) for _ in range(2)]
         self.recv_buf = [symm_group.alloc(self.max_rows * dim * 2) for _ in range(2)]
         self.ret_buf = [symm_group.alloc(rows_per_rank * dim * 2) for _ in range(2)]
-        for b in self.counts_buf + self.recv_buf + self.ret_buf:
+        self.fp8 = bool(fp8_dispatch) and dim % 256 == 0
+        self.q_buf = [symm_group.alloc(self.max_rows * dim) for _ in range(2)] if self.fp8 else []
+        self.q_scales = [symm_group.alloc(self.max_rows * (dim // 128) * 4) for _ in range(2)] if self.fp8 else []
+        for b in self.counts_buf + self.recv_buf + self.ret_buf + self.q_buf + self.q_scales:
             b.local.zero_()
         self.n = {"count": 0, "dispatch": 0, "return": 0}
         self.timeout_ms = int(os.environ.get("PICO_COMM_TIMEOUT_MS", "20000"))
@@ -84,13 +91,24 @@ class EPVarFused:
         layout = GroupLayout(self.L, self.max_rows, seg_start, tile_group, None)
         return VarPlan(send_blocks, return_blocks, seg_start, seg_len, layout)
 
-    def dispatch(self, rows_sorted: torch.Tensor, plan: VarPlan) -> torch.Tensor:
+    def dispatch(self, rows_sorted: torch.Tensor, plan: VarPlan, quant: bool = False) -> torch.Tensor:
         """[rows_per_rank, d] in this rank's expert-sorted order -> [max_rows, d] padded expert-major
         rows of the local experts (padding rows zero; rows past the last segment are unspecified)."""
         c, slot, epoch = self._next("dispatch", DISPATCH_SLOTS)
         e = ext()
-        e.ep_var_exchange(rows_sorted, None, 1, plan.send_blocks, self.E, self.recv_buf[c].ptrs, self.sg.flags.ptrs,
-                          self.ep, self.rank, self.d, slot, epoch)
+        if quant and self.fp8:
+            e.ep_var_exchange(rows_sorted, None, 1, plan.send_blocks, self.E, self.q_buf[c].ptrs,
+                              self.q_scales[c].ptrs, self.sg.flags.ptrs, self.ep, self.rank, self.d, True, slot, epoch)
+            self.sg.wait(slot, epoch, self.timeout_ms)
+            out = torch.empty((self.max_rows, self.d), device=rows_sorted.device, dtype=torch.bfloat16)
+            e.ep_var_dequant(self.q_buf[c].view(torch.uint8, (self.max_rows, self.d)),
+                             self.q_scales[c].view(torch.float32, (self.max_rows, self.d // 128)), out,
+                             plan.seg_start[self.L:], self.max_rows, self.d)
+            e.ep_var_zero_padding(out, plan.seg_start, plan.seg_len, self.L, self.d)
+            count_launch(4)
+            return out
+        e.ep_var_exchange(rows_sorted, None, 1, plan.send_blocks, self.E, self.recv_buf[c].ptrs, [],
+                          self.sg.flags.ptrs, self.ep, self.rank, self.d, False, slot, epoch)
         self.sg.wait(slot, epoch, self.timeout_ms)
         buf = self.recv_buf[c].view(torch.bfloat16, (self.max_rows, self.d))
         e.ep_var_zero_padding(buf, plan.seg_start, plan.seg_len, self.L, self.d)
@@ -100,8 +118,8 @@ class EPVarFused:
     def give_back(self, rows_padded: torch.Tensor, plan: VarPlan) -> torch.Tensor:
         """[max_rows, d] padded expert-major rows -> [rows_per_rank, d] in the senders' sorted order."""
         c, slot, epoch = self._next("return", RETURN_SLOTS)
-        ext().ep_var_exchange(rows_padded, None, 1, plan.return_blocks, self.ep * self.L, self.ret_buf[c].ptrs,
-                              self.sg.flags.ptrs, self.ep, self.rank, self.d, slot, epoch)
+        ext().ep_var_exchange(rows_padded, None, 1, plan.return_blocks, self.ep * self.L, self.ret_buf[c].ptrs, [],
+                              self.sg.flags.ptrs, self.ep, self.rank, self.d, False, slot, epoch)
         self.sg.wait(slot, epoch, self.timeout_ms)
         count_launch(2)
         return self.ret_buf[c].view(torch.bfloat16, (self.rows_per_rank, self.d)).clone()
@@ -111,7 +129,7 @@ class _VarDispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, rows_sorted, plan: VarPlan, epv: EPVarFused):
         ctx.plan, ctx.epv = plan, epv
-        return epv.dispatch(rows_sorted.contiguous(), plan)
+        return epv.dispatch(rows_sorted.contiguous(), plan, quant=True)
 
     @staticmethod
     def backward(ctx, g):
