@@ -72,6 +72,26 @@ def build_cfg(args, world):
     raise SystemExit(f"unknown config {args.config}")
 
 
+def active_params(mc) -> float:
+    """Parameters that take part in one token's forward pass (routed experts count top-k times)."""
+    h, L, v = mc.hidden_size, mc.num_hidden_layers, mc.vocab_size
+    hd = h // mc.num_attention_heads
+    attn = 2 * h * h + 2 * h * mc.num_key_value_heads * hd
+    ffn = 3 * h * mc.intermediate_size
+    experts = getattr(mc, "num_experts", 1) or 1
+    if experts > 1:
+        shared = getattr(mc, "shared_expert_intermediate_size", None) or \
+            mc.intermediate_size * (getattr(mc, "num_shared_experts", 0) or 0)
+        ffn = mc.num_experts_per_tok * 3 * h * mc.intermediate_size + 3 * h * shared + h * experts
+    return L * (attn + ffn) + v * h
+
+
+def mfu_percent(mc, seq_len: int, tokens_per_s_per_gpu: float, peak_flops: float) -> float:
+    """The reference's formula (picotron/utils.py:51-62) on the active parameters."""
+    flops_per_token = 6 * active_params(mc) + 12 * mc.num_hidden_layers * mc.hidden_size * seq_len
+    return 100.0 * tokens_per_s_per_gpu * flops_per_token / peak_flops
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", required=True, choices=["pp", "moe", "cp"])
@@ -119,7 +139,13 @@ def main():
     dist.all_reduce(mem, op=dist.ReduceOp.MAX)
     if rank == 0:
         step_ms = ms.item() / args.steps
-        print(json.dumps({"config": args.config, "layout": label, "n_gpus": world, "layers": cfg["model"]["num_hidden_layers"],
+        from picotron_b200.runtime.timing import measured_peaks
+        tps = eng.tokens_per_step / step_ms * 1e3
+        mfu_b200 = mfu_percent(eng.model_config, cfg["training"]["seq_length"], tps / world,
+                               measured_peaks()["bf16_tflops"] * 1e12)
+        mfu_h100 = mfu_percent(eng.model_config, cfg["training"]["seq_length"], tps / world, 989.5e12)
+        print(json.dumps({"mfu_percent_b200_measured_peak": round(mfu_b200, 2),
+                          "mfu_percent_h100_constant": round(mfu_h100, 2),"config": args.config, "layout": label, "n_gpus": world, "layers": cfg["model"]["num_hidden_layers"],
                           "seq_len": cfg["training"]["seq_length"], "tokens_per_step": eng.tokens_per_step,
                           "ms_per_step": round(step_ms, 2), "tokens_per_s": round(eng.tokens_per_step / step_ms * 1e3, 1),
                           "loss": round(lossv, 4), "peak_mem_gib": round(mem.item(), 1),
