@@ -51,7 +51,7 @@ DEFAULTS: Dict[str, Dict[str, Any]] = {
     "model": dict(name="HuggingFaceTB/SmolLM-360M-Instruct", num_hidden_layers=None, num_attention_heads=None,
                   num_key_value_heads=None, num_experts=1, num_experts_per_tok=2, num_shared_experts=0,
                   norm_topk_prob=True, dtype="bfloat16", use_flash_attention=True, use_fused_adam=True,
-                  ep_overlap=True, ep_num_tiles=1, ep_fp8_dispatch=False, moe_latent_dim=0, ep_backend="torch",
+                  ep_overlap=True, ep_num_tiles=1, ep_fp8_dispatch=False, moe_latent_dim=0, ep_backend="torch", ep_var_slack=3.0,
                   ep_capacity_factor=0.0, ep_capacity_dropless=True, ep_max_rounds=8,
                   router_aux_loss_coef=0.0, router_bias_update_rate=0.0, parallel_block=False, init_std=None,
                   shared_expert_intermediate_size=None),
@@ -121,7 +121,7 @@ def model_config_from(cfg) -> SimpleNamespace:
     base["max_position_embeddings"] = max(int(t["seq_length"]), 1) if m.get("max_position_embeddings") is None \
         else m["max_position_embeddings"]
     for k in ("num_experts", "num_experts_per_tok", "num_shared_experts", "norm_topk_prob", "ep_overlap",
-              "ep_num_tiles", "ep_fp8_dispatch", "moe_latent_dim", "ep_backend", "ep_capacity_factor",
+              "ep_num_tiles", "ep_fp8_dispatch", "moe_latent_dim", "ep_backend", "ep_var_slack", "ep_capacity_factor",
               "ep_capacity_dropless", "ep_max_rounds", "router_aux_loss_coef", "router_bias_update_rate",
               "parallel_block", "init_std", "shared_expert_intermediate_size"):
         base[k] = m[k]

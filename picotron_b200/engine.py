@@ -317,8 +317,11 @@ class TrainEngine:
             if not layers or layers[0].expert_dim % 128 != 0:
                 return
             sg = SymmGroup(m.ep_group, device=self.device)
+            # rows one rank may receive, as a multiple of the balanced load: an untrained router is
+            # skewed (single experts at 3-5x, groups of 8 experts at up to ~1.7x the mean were measured)
+            slack = float(os.environ.get("PICO_EP_VAR_SLACK", getattr(mc, "ep_var_slack", 3.0) or 3.0))
             self.fused_ep = EPVarFused(sg, layers[0].num_local_experts, layers[0].expert_dim,
-                                       tokens * mc.num_experts_per_tok,
+                                       tokens * mc.num_experts_per_tok, slack=min(slack, float(m.ep_world_size)),
                                        fp8_dispatch=bool(getattr(mc, "ep_fp8_dispatch", False)))
             for mod in layers:
                 mod.fused_ep_var = self.fused_ep

@@ -153,3 +153,49 @@ def var_dispatch(rows_sorted, plan: VarPlan, epv: EPVarFused):
 
 def var_return(rows_padded, plan: VarPlan, epv: EPVarFused):
     return _VarReturn.apply(rows_padded, plan, epv)
+
+
+def var_layout_ref(counts_table, L: int, my_rank: int, max_rows: int):
+    """Plain Python restatement of the layout kernel (test oracle). ``counts_table``: [ep][E] integers.
+    Returns (send_blocks [E][4], return_blocks [ep*L][4], seg_start [L+1], seg_len [L], tile_group)."""
+    ep = len(counts_table)
+    E = ep * L
+    pad = lambda n: (n + 127) // 128 * 128      # noqa: E731
+    send = []
+    for e in range(E):
+        r, l = divmod(e, L)
+        seg = 0
+        for l2 in range(l):
+            t = sum(counts_table[s][r * L + l2] for s in range(ep))
+            if seg + pad(t) <= max_rows:
+                seg += pad(t)
+        total = sum(counts_table[s][e] for s in range(ep))
+        before = sum(counts_table[s][e] for s in range(my_rank))
+        fits = seg + pad(total) <= max_rows
+        send.append([counts_table[my_rank][e] if fits else 0, sum(counts_table[my_rank][:e]), r,
+                     seg + before if fits else 0])
+    ret, seg_start, seg_len, seg = [], [], [], 0
+    ret = [[0, 0, 0, 0] for _ in range(ep * L)]
+    for l in range(L):
+        e = my_rank * L + l
+        total = sum(counts_table[s][e] for s in range(ep))
+        fits = seg + pad(total) <= max_rows
+        seg_start.append(seg)
+        seg_len.append(total if fits else 0)
+        within = 0
+        for s in range(ep):
+            c = counts_table[s][e]
+            ret[s * L + l] = [c if fits else 0, seg + within, s, sum(counts_table[s][:e])]
+            within += c
+        if fits:
+            seg += pad(total)
+    seg_start.append(seg)
+    tiles = []
+    for t in range(max_rows // 128):
+        row, g = t * 128, -1
+        if row < seg:
+            for l in range(L):
+                if seg_start[l] <= row < seg_start[l + 1]:
+                    g = l
+        tiles.append(g)
+    return send, ret, seg_start, seg_len, tiles

@@ -195,3 +195,35 @@ def test_moe_layer_grouped_experts_match_per_expert_loop():
     for (n, p), (_, q) in zip(layer.named_parameters(), ref.named_parameters()):
         g = p.main_grad if getattr(p, "main_grad", None) is not None and p.grad is None else p.grad
         assert _rel_err(g, q.grad) < 5e-2, n
+
+
+@pytest.mark.parametrize("my_rank", [0, 1, 3])
+def test_dropless_ep_layout_kernel_matches_reference(my_rank):
+    """The device-side layout of the dropless expert-parallel exchange (offsets of outgoing blocks,
+    padded expert segments, tile -> expert array, return blocks) against its Python restatement, with
+    empty experts, experts that are exact multiples of the tile, and a table that does not fit."""
+    ops, _ = _ops()
+    from picotron_b200.ops.fused_ep_var import var_layout_ref
+    ep, L = 4, 3
+    E = ep * L
+    g = torch.Generator().manual_seed(7)
+    table = torch.randint(0, 300, (ep, E), generator=g, dtype=torch.int32)
+    table[:, 2] = 0                  # an expert nobody routes to
+    table[:, 5] = 32                 # 4 x 32 = exactly one tile
+    for max_rows in (128 * 40, 128 * 6):      # roomy, and too small for some experts
+        dev = table.cuda()
+        send = torch.empty((E, 4), device="cuda", dtype=torch.int32)
+        ret = torch.empty((ep * L, 4), device="cuda", dtype=torch.int32)
+        seg_start = torch.empty(L + 1, device="cuda", dtype=torch.int32)
+        seg_len = torch.empty(L, device="cuda", dtype=torch.int32)
+        tiles = torch.empty(max_rows // 128, device="cuda", dtype=torch.int32)
+        ops.ext().ep_var_layout(dev, ep, L, my_rank, max_rows, send, ret, seg_start, seg_len, tiles)
+        r_send, r_ret, r_seg, r_len, r_tiles = var_layout_ref(table.tolist(), L, my_rank, max_rows)
+        assert send.cpu().tolist() == r_send
+        got_ret, want_ret = ret.cpu().tolist(), r_ret
+        for a, b in zip(got_ret, want_ret):
+            assert a[0] == b[0] and a[2:] == b[2:] and (a[0] == 0 or a[1] == b[1]), (a, b)
+        assert seg_start.cpu().tolist() == r_seg and seg_len.cpu().tolist() == r_len
+        assert tiles.cpu().tolist() == r_tiles
+        words = ops.ext().status_fetch()       # the small table reports the rows it could not place
+        assert (words[0] != 0) == (max_rows == 128 * 6)
