@@ -34,7 +34,7 @@ class RoundCommunicator:
 
     def post_round(self, messages, my_rank_in_pp: int, pp_group_ids: List[int], outgoing: Dict[tuple, torch.Tensor],
                    shape) -> None:
-        """messages: the cross-rank messages produced in this round (``pp_schedules.Message``)."""
+        """messages: the cross-rank messages produced in the current schedule round (``pp_schedules.Message``)."""
         ops, recv_keys = [], []
         mine = [m for m in messages if m.src_rank == my_rank_in_pp or m.dst_rank == my_rank_in_pp]
         mine.sort(key=lambda m: (m.dst_rank if m.src_rank == my_rank_in_pp else m.src_rank, m.kind, m.dst_stage, m.mb))
