@@ -252,3 +252,40 @@ def test_group_layout_pads_expert_segments_to_tiles():
     assert torch.allclose(y, torch.cat(ref), atol=1e-5)
     uniform = GroupLayout.uniform(3, 256, "cpu")
     assert uniform.pad_index is None and uniform.seg_start.tolist() == [0, 256, 512, 768]
+
+
+def test_dropless_layout_reference_is_consistent_across_ranks():
+    """Invariants of the dropless exchange layout (the Python restatement that the layout kernel is
+    tested against): every sender's block for an expert lands inside that expert's segment at the
+    receiver without overlapping another sender's block, segments are 128-aligned and cover exactly
+    the rows sent, and the return blocks of the receiver are the inverse of the senders' blocks."""
+    from picotron_b200.ops.fused_ep_var import var_layout_ref
+    ep, L = 4, 3
+    E = ep * L
+    g = torch.Generator().manual_seed(11)
+    table = torch.randint(0, 400, (ep, E), generator=g).tolist()
+    for s in range(ep):
+        table[s][4] = 0
+    max_rows = 128 * 64
+    layouts = [var_layout_ref(table, L, r, max_rows) for r in range(ep)]
+    for recv in range(ep):
+        _, ret, seg_start, seg_len, tiles = layouts[recv]
+        assert all(x % 128 == 0 for x in seg_start)
+        for l in range(L):
+            e = recv * L + l
+            total = sum(table[s][e] for s in range(ep))
+            assert seg_len[l] == total and seg_start[l + 1] - seg_start[l] == (total + 127) // 128 * 128
+            covered = []
+            for s in range(ep):
+                cnt, src_row, dst_rank, dst_row = layouts[s][0][e]        # sender s's block for expert e
+                assert dst_rank == recv and cnt == table[s][e]
+                assert src_row == sum(table[s][:e])
+                covered.append((dst_row, dst_row + cnt))
+                # the receiver sends the block back to where it came from
+                rc, r_src, r_rank, r_dst = ret[s * L + l]
+                assert (rc, r_src, r_rank, r_dst) == (cnt, dst_row, s, src_row)
+            covered.sort()
+            assert covered[0][0] == seg_start[l] and covered[-1][1] == seg_start[l] + total
+            assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+        used = seg_start[L] // 128
+        assert all(t >= 0 for t in tiles[:used]) and all(t == -1 for t in tiles[used:])
