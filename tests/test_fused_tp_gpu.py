@@ -107,6 +107,13 @@ def _fused_ops_worker(rank, world):
         dwr_ref = x_full.float().reshape(-1, K).t() @ xin_full.float().reshape(-1, N * world)[:, rank * N:(rank + 1) * N]
         assert _rel(wr.grad, dwr_ref) < 1e-2, ("linear_rs dw", it)
         assert _rel(res.grad, go) < 1e-3
+        # the fused reductions sum their slots in rank order: repeating an operation on the same inputs
+        # gives bit-identical results (forward reduce-scatter and the dx reduce-scatter of ag_linear)
+        if it == 0:
+            first_out, first_dx = out.detach().clone(), x_sh.grad.detach().clone()
+        else:
+            assert torch.equal(out.detach(), first_out), "GEMM -> reduce-scatter is not deterministic"
+            assert torch.equal(x_sh.grad, first_dx), "all-gather -> GEMM backward is not deterministic"
     ops.check_status("fused tp")
 
 
