@@ -69,8 +69,8 @@ def main():
     cases = [
         ("rmsnorm_fwd(+residual)", lambda: e.rmsnorm_fwd(x, res, w, y, h, rstd, M, H, 1e-5), M * H * 2 * 4),
         ("rmsnorm_bwd", lambda: e.rmsnorm_bwd(x, h, w, rstd, res, dh, part, dw, None, True, M, H), M * H * 2 * 4),
-        ("swiglu_fwd", lambda: e.swiglu_fwd(gu, 2 * I, act, M, I), M * I * 2 * 3),
-        ("swiglu_bwd", lambda: e.swiglu_bwd(act, gu, 2 * I, dgu, 2 * I, M, I), M * I * 2 * 5),
+        ("swiglu_fwd", lambda: e.swiglu_fwd(gu, 2 * I, act, M, I, None), M * I * 2 * 3),
+        ("swiglu_bwd", lambda: e.swiglu_bwd(act, gu, 2 * I, dgu, 2 * I, M, I, None), M * I * 2 * 5),
         ("rope_inplace", lambda: e.rope_inplace(qk, qk.stride(1), M, M // 4, 0, 32, 64, cos, cos, 1), M * 2048 * 2 * 2),
         ("ce_stats", lambda: e.ce_stats(logits, V, tgt, stats, M, V, 0), M * V * 2),
         ("ce_loss_grad(in place)", lambda: e.ce_loss_grad(logits, V, tgt, stats, loss, logits, V, 1.0, M, V, 0), M * V * 2 * 2),

@@ -88,15 +88,22 @@ void rope_inplace(at::Tensor& x, int64_t row_stride, int64_t rows, int64_t seq, 
         "rope");
 }
 
-void swiglu_fwd(const at::Tensor& gu, int64_t ld_gu, at::Tensor& y, int64_t rows, int64_t I) {
+static const int* rows_dev_ptr(const c10::optional<at::Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->numel() >= 1, "row count: int32 CUDA tensor");
+  return t->data_ptr<int>();
+}
+void swiglu_fwd(const at::Tensor& gu, int64_t ld_gu, at::Tensor& y, int64_t rows, int64_t I,
+                const c10::optional<at::Tensor>& rows_dev) {
   c10::cuda::CUDAGuard guard(gu.device());
-  check(pico_swiglu_fwd(gu.data_ptr(), ld_gu, y.data_ptr(), (int)rows, (int)I, stream_of(gu)), "swiglu_fwd");
+  check(pico_swiglu_fwd(gu.data_ptr(), ld_gu, y.data_ptr(), (int)rows, (int)I, rows_dev_ptr(rows_dev), stream_of(gu)),
+        "swiglu_fwd");
 }
 void swiglu_bwd(const at::Tensor& dy, const at::Tensor& gu, int64_t ld_gu, at::Tensor& dgu,
-                int64_t ld_dgu, int64_t rows, int64_t I) {
+                int64_t ld_dgu, int64_t rows, int64_t I, const c10::optional<at::Tensor>& rows_dev) {
   c10::cuda::CUDAGuard guard(gu.device());
   check(pico_swiglu_bwd(dy.data_ptr(), gu.data_ptr(), ld_gu, dgu.data_ptr(), ld_dgu, (int)rows, (int)I,
-                        stream_of(gu)),
+                        rows_dev_ptr(rows_dev), stream_of(gu)),
         "swiglu_bwd");
 }
 
@@ -327,6 +334,17 @@ void ep_var_dequant(const at::Tensor& payload, const at::Tensor& scales, at::Ten
         "ep_var_dequant");
 }
 
+void ep_var_copy_rows(const at::Tensor& src, at::Tensor& dst, const at::Tensor& rows_in_use, int64_t max_rows, int64_t d) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  TORCH_CHECK(src.scalar_type() == at::kBFloat16 && dst.scalar_type() == at::kBFloat16 && src.is_contiguous() &&
+                  dst.is_contiguous() && src.numel() >= max_rows * d && dst.numel() >= max_rows * d &&
+                  rows_in_use.scalar_type() == at::kInt,
+              "ep_var_copy_rows: contiguous bf16 [max_rows, d] buffers and an int32 row count");
+  check(pico_ep_var_copy_rows(src.data_ptr(), dst.data_ptr(), rows_in_use.data_ptr<int>(), (int)max_rows, (int)d,
+                              stream_of(dst)),
+        "ep_var_copy_rows");
+}
+
 void ep_var_zero_padding(at::Tensor& buf, const at::Tensor& seg_start, const at::Tensor& seg_len, int64_t L, int64_t d) {
   c10::cuda::CUDAGuard guard(buf.device());
   TORCH_CHECK(buf.scalar_type() == at::kBFloat16 && buf.is_contiguous(), "ep_var_zero_padding: contiguous bf16");
@@ -547,6 +565,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_var_layout", &ep_var_layout);
   m.def("ep_var_exchange", &ep_var_exchange);
   m.def("ep_var_dequant", &ep_var_dequant);
+  m.def("ep_var_copy_rows", &ep_var_copy_rows);
   m.def("ep_var_zero_padding", &ep_var_zero_padding);
   m.def("gemm_ex", &gemm_ex);
   m.def("gemm_grouped", &gemm_grouped);

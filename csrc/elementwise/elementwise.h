@@ -28,11 +28,14 @@ int pico_rope_inplace(void* x, int64_t row_stride, int rows, int seq, int pos_of
                       int d, const float* cos, const float* sin, int sign, cudaStream_t stream);
 
 // ---- SwiGLU ------------------------------------------------------------------------------
-// gu: [rows, 2*I] (gate | up, row stride ld_gu); y[rows, I] = silu(gate) * up
-int pico_swiglu_fwd(const void* gu, int64_t ld_gu, void* y, int rows, int I, cudaStream_t stream);
+// gu: [rows, 2*I] (gate | up, row stride ld_gu); y[rows, I] = silu(gate) * up.
+// rows_dev (optional, device): when given, only min(rows, *rows_dev) rows are processed - for buffers
+// whose row count is known only on the device; the remaining rows of the output are left untouched.
+int pico_swiglu_fwd(const void* gu, int64_t ld_gu, void* y, int rows, int I, const int* rows_dev,
+                    cudaStream_t stream);
 // dgu[rows, 2*I] from dy[rows, I] and the saved gu
 int pico_swiglu_bwd(const void* dy, const void* gu, int64_t ld_gu, void* dgu, int64_t ld_dgu,
-                    int rows, int I, cudaStream_t stream);
+                    int rows, int I, const int* rows_dev, cudaStream_t stream);
 
 // ---- cross entropy on a vocabulary shard ---------------------------------------------------
 // stats[row] = {max_j l[row,j], sum_j exp(l - max), l[row,target] or 0 if target is not in

@@ -76,7 +76,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, int64_t row_stride, i
 
 // ------------------------------------------------------------------------------ SwiGLU
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ld_gu,
-                                  __nv_bfloat16* __restrict__ y, int rows, int I) {
+                                  __nv_bfloat16* __restrict__ y, int rows, int I, const int* __restrict__ rows_dev) {
+  if (rows_dev) rows = min(rows, *rows_dev);   // row count known only on the device (dropless MoE buffers)
   const int vec_per_row = I / 8;
   const int64_t total = (int64_t)rows * vec_per_row;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
@@ -94,7 +95,9 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, int64_t 
 
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                   const __nv_bfloat16* __restrict__ gu, int64_t ld_gu,
-                                  __nv_bfloat16* __restrict__ dgu, int64_t ld_dgu, int rows, int I) {
+                                  __nv_bfloat16* __restrict__ dgu, int64_t ld_dgu, int rows, int I,
+                                  const int* __restrict__ rows_dev) {
+  if (rows_dev) rows = min(rows, *rows_dev);
   const int vec_per_row = I / 8;
   const int64_t total = (int64_t)rows * vec_per_row;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
@@ -260,7 +263,7 @@ extern "C" int pico_rope_inplace(void* x, int64_t row_stride, int rows, int seq,
   return finish("rope");
 }
 
-extern "C" int pico_swiglu_fwd(const void* gu, int64_t ld_gu, void* y, int rows, int I,
+extern "C" int pico_swiglu_fwd(const void* gu, int64_t ld_gu, void* y, int rows, int I, const int* rows_dev,
                                cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (I % 8 != 0 || ld_gu % 8 != 0) {
@@ -268,19 +271,19 @@ extern "C" int pico_swiglu_fwd(const void* gu, int64_t ld_gu, void* y, int rows,
     return -2;
   }
   swiglu_fwd_kernel<<<grid_for((int64_t)rows * (I / 8), 256), 256, 0, stream>>>(
-      (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)y, rows, I);
+      (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)y, rows, I, rows_dev);
   return finish("swiglu_fwd");
 }
 
 extern "C" int pico_swiglu_bwd(const void* dy, const void* gu, int64_t ld_gu, void* dgu,
-                               int64_t ld_dgu, int rows, int I, cudaStream_t stream) {
+                               int64_t ld_dgu, int rows, int I, const int* rows_dev, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (I % 8 != 0 || ld_gu % 8 != 0 || ld_dgu % 8 != 0) {
     pico_host::set_error("swiglu: width and strides must be multiples of 8");
     return -2;
   }
   swiglu_bwd_kernel<<<grid_for((int64_t)rows * (I / 8), 256), 256, 0, stream>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)dgu, ld_dgu, rows, I);
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)dgu, ld_dgu, rows, I, rows_dev);
   return finish("swiglu_bwd");
 }
 

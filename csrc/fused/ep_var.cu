@@ -207,6 +207,14 @@ __global__ void ep_var_zero_padding_kernel(__nv_bfloat16* __restrict__ buf, cons
   }
 }
 
+// rows [0, *rows_in_use) of src -> dst (16-byte vectors)
+__global__ void ep_var_copy_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                        const int32_t* __restrict__ rows_in_use, int vec_per_row) {
+  const int64_t n = (int64_t)(*rows_in_use) * vec_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = src[i];
+}
+
 constexpr int kVarMaxDev = 64;
 static unsigned int* g_var_counters[kVarMaxDev] = {nullptr};
 static unsigned int* var_counter() {
@@ -278,6 +286,21 @@ extern "C" int pico_ep_var_dequant(const void* payload, const float* scales, voi
                                                         rows_in_use, d);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) pico_host::set_error("ep_var_dequant: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+extern "C" int pico_ep_var_copy_rows(const void* src, void* dst, const int32_t* rows_in_use, int max_rows, int d,
+                                     cudaStream_t stream) {
+  if (d % 8 != 0 || max_rows < 1) {
+    pico_host::set_error("ep_var_copy_rows: row width %d must be a multiple of 8", d);
+    return -2;
+  }
+  int64_t blocks = ((int64_t)max_rows * (d / 8) + 255) / 256;
+  const int cap = pico_host::num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  ep_var_copy_rows_kernel<<<(int)blocks, 256, 0, stream>>>((const uint4*)src, (uint4*)dst, rows_in_use, d / 8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) pico_host::set_error("ep_var_copy_rows: %s", cudaGetErrorString(e));
   return (int)e;
 }
 

@@ -44,6 +44,11 @@ int pico_ep_var_exchange(const void* src, const int32_t* row_index, int index_di
 int pico_ep_var_dequant(const void* payload, const float* scales, void* out, const int32_t* rows_in_use,
                         int max_rows, int d, cudaStream_t stream);
 
+// dst[0 .. *rows_in_use) = src[0 .. *rows_in_use) for [max_rows, d] bf16 buffers (the fill level is a device
+// integer): copies the used part of a receive buffer out of symmetric memory.
+int pico_ep_var_copy_rows(const void* src, void* dst, const int32_t* rows_in_use, int max_rows, int d,
+                          cudaStream_t stream);
+
 // Zero the padding rows [seg_start[l] + seg_len[l], seg_start[l+1]) of a [rows, d] bf16 buffer, so
 // that padded tiles contribute exact zeros to the grouped GEMMs.
 int pico_ep_var_zero_padding(void* buf, const int32_t* seg_start, const int32_t* seg_len, int L, int d,

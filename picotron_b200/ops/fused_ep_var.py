@@ -111,9 +111,11 @@ class EPVarFused:
                           self.sg.flags.ptrs, self.ep, self.rank, self.d, False, slot, epoch)
         self.sg.wait(slot, epoch, self.timeout_ms)
         buf = self.recv_buf[c].view(torch.bfloat16, (self.max_rows, self.d))
-        e.ep_var_zero_padding(buf, plan.seg_start, plan.seg_len, self.L, self.d)
-        count_launch(3)
-        return buf.clone()
+        out = torch.empty((self.max_rows, self.d), device=rows_sorted.device, dtype=torch.bfloat16)
+        e.ep_var_copy_rows(buf, out, plan.seg_start[self.L:], self.max_rows, self.d)   # only the rows in use
+        e.ep_var_zero_padding(out, plan.seg_start, plan.seg_len, self.L, self.d)
+        count_launch(4)
+        return out
 
     def give_back(self, rows_padded: torch.Tensor, plan: VarPlan) -> torch.Tensor:
         """[max_rows, d] padded expert-major rows -> [rows_per_rank, d] in the senders' sorted order."""

@@ -242,14 +242,15 @@ class MoELayer(nn.Module):
         return grouped_gemm.kernel_ok(x, self.expert_dim, e0.gate_proj.weight.shape[0]) and \
             self.expert_dim % 128 == 0 and e0.gate_proj.weight.dtype == torch.bfloat16
 
-    def _experts_on_layout(self, xp: torch.Tensor, layout) -> torch.Tensor:
+    def _experts_on_layout(self, xp: torch.Tensor, layout, rows_in_use=None) -> torch.Tensor:
         """SwiGLU feed-forward of every local expert over the padded expert-major rows ``xp``: two
         grouped GEMM launches around one SwiGLU kernel (the reference's fused-MoE composition,
         picotron/expert_parallel/megakernel.py:294-357)."""
         experts = list(self.local_experts)
         inter = experts[0].gate_proj.weight.shape[0]
         gu = grouped_gemm.grouped_linear(xp, [m for e in experts for m in (e.gate_proj, e.up_proj)], layout, 2 * inter)
-        return grouped_gemm.grouped_linear(swiglu_ops.swiglu(gu), [e.down_proj for e in experts], layout,
+        # rows_in_use: device-side fill level of a buffer sized for the worst case (dropless exchange)
+        return grouped_gemm.grouped_linear(swiglu_ops.swiglu(gu, rows_in_use), [e.down_proj for e in experts], layout,
                                            experts[0].down_proj.weight.shape[0])
 
     def _dispatch(self, rows_sorted, plan: RoutePlan):
@@ -268,7 +269,7 @@ class MoELayer(nn.Module):
         counts = torch.bincount(expert_idx, minlength=self.num_experts).to(torch.int32)
         plan = epv.plan(counts)
         recv = fv.var_dispatch(routed[order], plan, epv)
-        y_pad = self._experts_on_layout(recv, plan.layout)
+        y_pad = self._experts_on_layout(recv, plan.layout, rows_in_use=plan.seg_start[self.num_local_experts:])
         return fv.var_return(y_pad, plan, epv)[inv]
 
     def _routed_naive(self, routed, expert_idx):

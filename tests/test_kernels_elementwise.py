@@ -81,6 +81,21 @@ def test_swiglu():
     assert _rel(y, yr) < 1e-2 and _rel(gu.grad, gr.grad) < 1e-2
 
 
+def test_swiglu_with_device_side_row_count():
+    """Rows at or past a fill level that lives on the device are skipped, forward and backward."""
+    from picotron_b200.ops import swiglu
+    torch.manual_seed(5)
+    gu = torch.randn(300, 2 * 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    n = torch.tensor([129], device="cuda", dtype=torch.int32)
+    y = swiglu.swiglu(gu, rows_in_use=n)
+    g = torch.randn_like(y)
+    y[:129].backward(g[:129])
+    gr = gu.detach().float().requires_grad_(True)
+    yr = swiglu.swiglu_ref(gr)
+    yr[:129].backward(g[:129].float())
+    assert _rel(y[:129], yr[:129]) < 1e-2 and _rel(gu.grad[:129], gr.grad[:129]) < 1e-2
+
+
 @pytest.mark.parametrize("rows,V", [(64, 4096), (300, 49152), (17, 32000)])
 def test_cross_entropy(rows, V):
     from picotron_b200.ops import cross_entropy as ce
