@@ -157,7 +157,10 @@ def result_line(args, layout, world, ms_total, e2e_ms_total, h2d, d2h, clocks, l
     line = {
         "metric": "training throughput, SmolLM-1.7B (tokens/s, whole job)", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_per_step, 3), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
+        # 1, 2 and 4 GPUs split the same global batch of 32 sequences (tensor parallelism: total work fixed);
+        # 8 GPUs add a data-parallel replica and double the global batch
+        "scaling": "strong" if world <= 4 else "weak",
         "vs_baseline": round(per_gpu * fpt / H100_PEAK * 100.0 / PUBLISHED_MFU_PERCENT, 4),
         "dtype": "bf16", "data": "synthetic seeded uniform tokens, random-init N(0,0.02) weights",
         "impl": impl,
@@ -169,6 +172,8 @@ def result_line(args, layout, world, ms_total, e2e_ms_total, h2d, d2h, clocks, l
                    "parallelism": f"dp{layout['dp']}xtp{layout['tp']}"
                                   + ("+sp+vocab_ce" if layout["tp"] > 1 else "")
                                   + ("+zero1" if layout["dp"] > 1 else ""),
+                   "scaling_note": "global batch 32 sequences at 1/2/4 GPUs (fixed total work, tp1/tp2/tp4); "
+                                   "64 at 8 GPUs (dp2 x tp4: per-replica work fixed)",
                    "l2": "per-step working set (GBs of parameters and activations) exceeds the 126 MB L2; no explicit flush",
                    "vs_baseline_note": "per-GPU MFU by the reference formula (H100 constant) / published ~50% MFU on 8xH100"},
         "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
@@ -227,6 +232,7 @@ def run_ours(args):
     if rank == 0:
         print(json.dumps(result_line(args, layout, world, ms, e2e_ms, h2d, d2h, clocks, launches, "picotron_b200",
                                      {"final_loss": last.get("loss")})), flush=True)
+    engine.close()
     dist.destroy_process_group()
 
 

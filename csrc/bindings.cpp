@@ -161,6 +161,14 @@ void accumulate_bf16_into_f32(const at::Tensor& src, at::Tensor& dst, int64_t n)
         "accumulate");
 }
 
+void scale_unless_one(at::Tensor& x, const at::Tensor& scale) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && scale.scalar_type() == at::kFloat &&
+                  scale.is_cuda() && scale.numel() == 1, "scale_unless_one: contiguous bf16 tensor, fp32 device scalar");
+  check(pico_scale_unless_one(x.data_ptr(), x.numel(), (const float*)scale.data_ptr(), stream_of(x)),
+        "scale_unless_one");
+}
+
 void fill_u32(at::Tensor& dst, int64_t value, int64_t n_words) {
   c10::cuda::CUDAGuard guard(dst.device());
   check(pico_fill_u32(dst.data_ptr(), (uint32_t)value, n_words, stream_of(dst)), "fill");
@@ -211,6 +219,20 @@ void wait_flags(int64_t local_flags, int64_t world, int64_t slot, int64_t epoch,
   check(pico_wait_flags(reinterpret_cast<const uint32_t*>(local_flags), (int)world, (int)slot,
                         (uint32_t)epoch, (uint32_t)timeout_ms, at::cuda::getCurrentCUDAStream().stream()),
         "wait_flags");
+}
+
+void epoch_base_add(int64_t local_flags, const std::vector<int64_t>& slots, const std::vector<int64_t>& deltas) {
+  TORCH_CHECK(slots.size() == deltas.size() && slots.size() <= PICO_MAX_EPOCH_DELTAS, "epoch_base_add: at most ",
+              PICO_MAX_EPOCH_DELTAS, " (slot, delta) pairs");
+  PicoEpochDeltas d;
+  memset(&d, 0, sizeof(d));
+  d.n = (int)slots.size();
+  for (size_t i = 0; i < slots.size(); ++i) {
+    d.slot[i] = (int)slots[i];
+    d.delta[i] = (uint32_t)deltas[i];
+  }
+  check(pico_epoch_base_add(reinterpret_cast<uint32_t*>(local_flags), &d, at::cuda::getCurrentCUDAStream().stream()),
+        "epoch_base_add");
 }
 
 void push_rows(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs,
@@ -351,6 +373,33 @@ void ep_var_zero_padding(at::Tensor& buf, const at::Tensor& seg_start, const at:
   check(pico_ep_var_zero_padding(buf.data_ptr(), seg_start.data_ptr<int>(), seg_len.data_ptr<int>(), (int)L, (int)d,
                                  stream_of(buf)),
         "ep_var_zero_padding");
+}
+
+void ce_stats_push(const at::Tensor& logits, int64_t ldl, const at::Tensor& targets, int64_t rows, int64_t V,
+                   int64_t vocab_start, const std::vector<int64_t>& dst_ptrs, const std::vector<int64_t>& flag_ptrs,
+                   int64_t world, int64_t my_rank, int64_t slot, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(targets.scalar_type() == at::kLong && logits.scalar_type() == at::kBFloat16, "ce: dtypes");
+  check(pico_ce_stats_push(logits.data_ptr(), ldl, (const int64_t*)targets.data_ptr(), (int)rows, (int)V,
+                           (int)vocab_start, table_of(dst_ptrs), table_of(flag_ptrs), (int)world, (int)my_rank,
+                           (int)slot, (uint32_t)epoch, stream_of(logits)),
+        "ce_stats_push");
+}
+
+void ce_loss_grad_gathered(const at::Tensor& logits, int64_t ldl, const at::Tensor& targets,
+                           const at::Tensor& gathered, const c10::optional<at::Tensor>& loss,
+                           const c10::optional<at::Tensor>& dlogits, int64_t ldd, double grad_scale, int64_t rows,
+                           int64_t V, int64_t vocab_start, int64_t local_flags, int64_t world, int64_t slot,
+                           int64_t epoch, int64_t timeout_ms) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(gathered.scalar_type() == at::kFloat && gathered.numel() >= world * rows * 3,
+              "ce_loss_grad_gathered: fp32 [world, rows, 3] table");
+  check(pico_ce_loss_grad_gathered(logits.data_ptr(), ldl, (const int64_t*)targets.data_ptr(),
+                                   (const float*)gathered.data_ptr(), (float*)mptr(loss), mptr(dlogits), ldd,
+                                   (float)grad_scale, (int)rows, (int)V, (int)vocab_start,
+                                   reinterpret_cast<const uint32_t*>(local_flags), (int)world, (int)slot,
+                                   (uint32_t)epoch, (uint32_t)timeout_ms, stream_of(logits)),
+        "ce_loss_grad_gathered");
 }
 
 void zero1_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, at::Tensor& m,
@@ -546,6 +595,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_bwd", &embedding_bwd);
   m.def("accumulate_bf16_into_f32", &accumulate_bf16_into_f32);
   m.def("fill_u32", &fill_u32);
+  m.def("scale_unless_one", &scale_unless_one);
   m.def("status_fetch", &status_fetch);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);
@@ -556,6 +606,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("signal_peers", &signal_peers);
   m.def("wait_flags", &wait_flags);
+  m.def("epoch_base_add", &epoch_base_add);
   m.def("push_rows", &push_rows);
   m.def("rmsnorm_fwd_push", &rmsnorm_fwd_push);
   m.def("slot_sum", &slot_sum);
@@ -570,6 +621,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_ex", &gemm_ex);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("zero1_adamw", &zero1_adamw);
+  m.def("ce_stats_push", &ce_stats_push);
+  m.def("ce_loss_grad_gathered", &ce_loss_grad_gathered);
   m.def("ep_dispatch", &ep_dispatch);
   m.def("ep_dequant", &ep_dequant);
   m.def("ep_block_exchange", &ep_block_exchange);

@@ -3,6 +3,8 @@
 // 0 on success, message in pico_last_error() otherwise. bf16 tensors are passed as void*.
 #pragma once
 #include <cuda_runtime.h>
+
+#include "../runtime/symm.h"
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -48,6 +50,20 @@ int pico_ce_loss_grad(const void* logits, int64_t ldl, const int64_t* targets, c
                       float* loss, void* dlogits, int64_t ldd, float grad_scale, int rows, int V,
                       int vocab_start, cudaStream_t stream);
 
+// Vocabulary-parallel form without a collective call: every rank writes the triples of its shard
+// into block my_rank of the [world][rows][3] fp32 table of all ranks (`dst`, symmetric memory) and
+// raises flag [slot][my_rank] = epoch; pico_ce_loss_grad_gathered waits (bounded) for all world
+// flags, merges the world triples of each row in rank order (max, rescaled sum, sum) and proceeds
+// like pico_ce_loss_grad.
+int pico_ce_stats_push(const void* logits, int64_t ldl, const int64_t* targets, int rows, int V,
+                       int vocab_start, PicoPeerTable dst, PicoPeerTable flags, int world, int my_rank,
+                       int slot, uint32_t epoch, cudaStream_t stream);
+int pico_ce_loss_grad_gathered(const void* logits, int64_t ldl, const int64_t* targets,
+                               const float* gathered_stats, float* loss, void* dlogits, int64_t ldd,
+                               float grad_scale, int rows, int V, int vocab_start,
+                               const uint32_t* local_flags, int world, int slot, uint32_t epoch,
+                               uint32_t timeout_ms, cudaStream_t stream);
+
 // ---- AdamW over flat buffers ----------------------------------------------------------------
 // p (bf16) / master (fp32, optional) / g (fp32) / m, v (fp32), n elements. Decoupled weight
 // decay as torch.optim.AdamW. g is multiplied by grad_scale first and zeroed afterwards when
@@ -67,6 +83,8 @@ int pico_embedding_bwd(const void* dout, const int64_t* ids, float* dW, int rows
 // ---- misc ---------------------------------------------------------------------------------
 // dst_f32 += src_bf16 (n elements); used to fold bf16 gradients into fp32 accumulators.
 int pico_accumulate_bf16_into_f32(const void* src, float* dst, int64_t n, cudaStream_t stream);
+// x (bf16, n elements, contiguous) *= *scale_dev, skipped entirely when the device scalar is 1
+int pico_scale_unless_one(void* x_bf16, int64_t n, const float* scale_dev, cudaStream_t stream);
 // writes a buffer larger than L2 (cache flush between timed iterations)
 int pico_fill_u32(void* dst, uint32_t value, int64_t n_words, cudaStream_t stream);
 

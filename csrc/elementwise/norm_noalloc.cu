@@ -3,6 +3,7 @@
 // this and for the rules of use.
 #include "no_alloc.h"
 
+#include <atomic>
 #include <mutex>
 
 #include "../common/host.h"
@@ -15,7 +16,8 @@ namespace {
 static __device__ __align__(256) float g_dw_scratch[PICO_NOALLOC_MAX_PARTIALS * PICO_NOALLOC_MAX_HIDDEN];
 
 constexpr int kMaxDevices = 64;
-float* g_scratch_ptr[kMaxDevices] = {nullptr};
+// written once per device under the mutex, read without it: hence atomic
+std::atomic<float*> g_scratch_ptr[kMaxDevices];
 std::mutex g_setup_mu;
 
 // Device address of the scratch on the current device, resolved once per device.
@@ -27,9 +29,9 @@ float* scratch_for_current_device() {
                          cudaGetErrorString(e));
     return nullptr;
   }
-  if (g_scratch_ptr[dev]) return g_scratch_ptr[dev];
+  if (float* known = g_scratch_ptr[dev].load(std::memory_order_acquire)) return known;
   std::lock_guard<std::mutex> lk(g_setup_mu);
-  if (g_scratch_ptr[dev]) return g_scratch_ptr[dev];
+  if (float* known = g_scratch_ptr[dev].load(std::memory_order_acquire)) return known;
   float* ptr = nullptr;
   e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_dw_scratch);
   if (e != cudaSuccess || ptr == nullptr) {
@@ -37,7 +39,7 @@ float* scratch_for_current_device() {
                          cudaGetErrorString(e));
     return nullptr;
   }
-  g_scratch_ptr[dev] = ptr;
+  g_scratch_ptr[dev].store(ptr, std::memory_order_release);
   return ptr;
 }
 

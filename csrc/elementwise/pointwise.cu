@@ -247,6 +247,33 @@ __global__ void fill_kernel(uint32_t* __restrict__ dst, uint32_t value, int64_t 
 
 using namespace pico;
 
+// x *= *scale unless *scale == 1 (the usual case costs one scalar load per thread and no traffic)
+__global__ void scale_unless_one_kernel(uint4* __restrict__ x, int64_t nvec, const float* __restrict__ scale) {
+  const float sc = *scale;
+  if (sc == 1.0f) return;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 v = x[i];
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(p[j]);
+      p[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    }
+    x[i] = v;
+  }
+}
+
+extern "C" int pico_scale_unless_one(void* x_bf16, int64_t n, const float* scale_dev, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 8 != 0) {
+    pico_host::set_error("scale_unless_one: %lld elements, need a multiple of 8", (long long)n);
+    return -2;
+  }
+  scale_unless_one_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>((uint4*)x_bf16, n / 8, scale_dev);
+  return finish("scale_unless_one");
+}
+
 extern "C" int pico_rope_inplace(void* x, int64_t row_stride, int rows, int seq, int pos_offset,
                                  int nheads, int d, const float* cos, const float* sin, int sign,
                                  cudaStream_t stream) {

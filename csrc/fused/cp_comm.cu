@@ -7,24 +7,6 @@
 
 namespace pico {
 
-// Grid-wide completion: the last CTA to finish raises this rank's flag on every peer.
-__device__ __forceinline__ void a2a_raise_flags(unsigned int* counter, PicoPeerTable flags, int world,
-                                                int my_rank, int slot, uint32_t epoch) {
-  __threadfence_system();
-  __syncthreads();
-  __shared__ bool last;
-  if (threadIdx.x == 0) {
-    const unsigned int done = atomicAdd(counter, 1u) + 1u;
-    last = (done == gridDim.x);
-    if (last) *counter = 0;
-  }
-  __syncthreads();
-  if (last && threadIdx.x < world) {
-    __threadfence_system();
-    st_release_sys(flag_word(flags.ptr[threadIdx.x], slot, my_rank), epoch);
-  }
-}
-
 // TO_SEQ: src[b][s][r][c] -> dst_r[b][my_rank * s_local + s][c]
 // else  : src[b][r][s][c] -> dst_r[b][s][my_rank][c]
 // c counts 16-byte vectors (vec = cols / 8).
@@ -54,7 +36,7 @@ __global__ void a2a_kernel(const uint4* __restrict__ src, PicoPeerTable dst, Pic
       reinterpret_cast<uint4*>(dst.ptr[r])[o] = src[i];
     }
   }
-  a2a_raise_flags(counter, flags, world, my_rank, slot, epoch);
+  raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
 }
 
 constexpr int kMaxDevA2A = 64;

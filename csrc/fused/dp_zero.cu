@@ -13,16 +13,7 @@ zero1_adamw_kernel(PicoPeerTable grads, PicoPeerTable params, float* __restrict_
                    float beta1, float beta2, float eps, float wd, float bc1, float bc2, float grad_scale,
                    const uint32_t* local_flags, int ready_slot, uint32_t epoch, uint64_t timeout_ns,
                    int* status) {
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = 1;
-  __syncthreads();
-  if (threadIdx.x < world) {
-    if (!wait_flag_ge(local_flags + ready_slot * PICO_MAX_PEERS + threadIdx.x, epoch, timeout_ns, status,
-                      800 + threadIdx.x))
-      ok = 0;
-  }
-  __syncthreads();
-  if (!ok) return;
+  if (!wait_slot_all(local_flags, ready_slot, world, epoch, timeout_ns, status, 800)) return;
   const float step_size = lr / bc1;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
   const float decay = 1.f - lr * wd;

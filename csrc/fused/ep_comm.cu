@@ -8,23 +8,6 @@
 
 namespace pico {
 
-__device__ __forceinline__ void ep_raise_when_done(unsigned int* counter, PicoPeerTable flags, int world,
-                                                   int my_rank, int slot, uint32_t epoch) {
-  __threadfence_system();
-  __syncthreads();
-  __shared__ bool last;
-  if (threadIdx.x == 0) {
-    const unsigned int done = atomicAdd(counter, 1u) + 1u;
-    last = (done == gridDim.x);
-    if (last) *counter = 0;
-  }
-  __syncthreads();
-  if (last && threadIdx.x < world) {
-    __threadfence_system();
-    st_release_sys(flag_word(flags.ptr[threadIdx.x], slot, my_rank), epoch);
-  }
-}
-
 // one warp per slot row; each lane handles 8 consecutive elements per step (d % 256 == 0 for
 // the quantised path so that a 128-element block is covered by 16 lanes)
 __global__ void __launch_bounds__(256)
@@ -82,21 +65,14 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ tokens, const int32_t* __re
       }
     }
   }
-  ep_raise_when_done(counter, flags, ep, my_rank, slot, epoch);
+  raise_flags_when_grid_done(counter, flags, ep, my_rank, slot, epoch);
 }
 
 __global__ void __launch_bounds__(256)
 ep_dequant_kernel(const uint8_t* __restrict__ payload, const float* __restrict__ scales,
                   __nv_bfloat16* __restrict__ out, int64_t rows, int d, const uint32_t* local_flags, int ep,
                   int slot, uint32_t epoch, uint64_t timeout_ns, int* status) {
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = 1;
-  __syncthreads();
-  if (threadIdx.x < ep &&
-      !wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + threadIdx.x, epoch, timeout_ns, status, 600 + threadIdx.x))
-    ok = 0;
-  __syncthreads();
-  if (!ok) return;
+  if (!wait_slot_all(local_flags, slot, ep, epoch, timeout_ns, status, 600)) return;
   const int64_t nvec = rows * d / 8;
   const int vec_per_row = d / 8;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
@@ -139,7 +115,7 @@ ep_block_exchange_kernel(const uint4* __restrict__ src, PicoPeerTable dst, PicoP
     }
     reinterpret_cast<uint4*>(dst.ptr[dest])[dblk * block_vecs + within] = src[i];
   }
-  ep_raise_when_done(counter, flags, ep, my_rank, slot, epoch);
+  raise_flags_when_grid_done(counter, flags, ep, my_rank, slot, epoch);
 }
 
 constexpr int kEpMaxDev = 64;

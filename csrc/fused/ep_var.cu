@@ -92,23 +92,6 @@ __global__ void ep_var_layout_kernel(const int32_t* __restrict__ counts, int ep,
   }
 }
 
-__device__ __forceinline__ void var_raise_when_done(unsigned int* counter, PicoPeerTable flags, int world,
-                                                    int my_rank, int slot, uint32_t epoch) {
-  __threadfence_system();
-  __syncthreads();
-  __shared__ bool last;
-  if (threadIdx.x == 0) {
-    const unsigned int done = atomicAdd(counter, 1u) + 1u;
-    last = (done == gridDim.x);
-    if (last) *counter = 0;
-  }
-  __syncthreads();
-  if (last && threadIdx.x < world) {
-    __threadfence_system();
-    st_release_sys(flag_word(flags.ptr[threadIdx.x], slot, my_rank), epoch);
-  }
-}
-
 // one warp per row; the rows of every block are spread over all warps of the grid.
 // QUANT: rows are quantised to FP8 E4M3 with one fp32 scale per 1 x 128 block while they are being
 // sent (d bytes per row into `dst`, d / 128 floats per row into `scales`).
@@ -167,7 +150,7 @@ ep_var_exchange_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __r
       }
     }
   }
-  var_raise_when_done(counter, flags, ep, my_rank, slot, epoch);
+  raise_flags_when_grid_done(counter, flags, ep, my_rank, slot, epoch);
 }
 
 // payload / scales -> bf16 for the rows in use (their number is read from device memory)

@@ -8,26 +8,6 @@
 
 namespace pico {
 
-// Grid-wide completion: the last CTA to finish raises the flags. `counter` is a device word that
-// returns to zero after each use.
-__device__ __forceinline__ void raise_flags_when_grid_done(unsigned int* counter, PicoPeerTable flags,
-                                                           int world, int my_rank, int slot,
-                                                           uint32_t epoch) {
-  __threadfence_system();
-  __syncthreads();
-  __shared__ bool last;
-  if (threadIdx.x == 0) {
-    const unsigned int done = atomicAdd(counter, 1u) + 1u;
-    last = (done == gridDim.x);
-    if (last) *counter = 0;
-  }
-  __syncthreads();
-  if (last && threadIdx.x < world) {
-    __threadfence_system();
-    st_release_sys(flag_word(flags.ptr[threadIdx.x], slot, my_rank), epoch);
-  }
-}
-
 __global__ void push_rows_kernel(const uint4* __restrict__ src, PicoPeerTable dst, PicoPeerTable flags,
                                  int world, int my_rank, int64_t nvec, int slot, uint32_t epoch,
                                  unsigned int* counter) {
@@ -115,16 +95,7 @@ __global__ void slot_sum_kernel(const uint4* __restrict__ staging, int world, in
                                 const uint4* __restrict__ addend, uint4* __restrict__ out,
                                 const uint32_t* local_flags, int slot, uint32_t epoch,
                                 uint64_t timeout_ns, int* status) {
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = 1;
-  __syncthreads();
-  if (threadIdx.x < world) {
-    if (!wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + threadIdx.x, epoch, timeout_ns, status,
-                      700 + threadIdx.x))
-      ok = 0;
-  }
-  __syncthreads();
-  if (!ok) return;
+  if (!wait_slot_all(local_flags, slot, world, epoch, timeout_ns, status, 700)) return;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
        i += (int64_t)gridDim.x * blockDim.x) {
     float acc[8];

@@ -207,8 +207,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (comm.a_flags != nullptr) {
           const int blk = m0 / comm.a_rows_per_block;
           if (blk != comm.a_skip_block && !((ready_blocks >> blk) & 1u)) {
-            if (!wait_flag_ge(comm.a_flags + comm.a_slot * PICO_MAX_PEERS + blk, comm.a_epoch,
-                              comm.timeout_ns, status, 500 + blk)) {
+            if (!wait_flag_ge(comm.a_flags + comm.a_slot * PICO_MAX_PEERS + blk,
+                              epoch_base(comm.a_flags, comm.a_slot) + comm.a_epoch, comm.timeout_ns, status,
+                              500 + blk)) {
               *abort_word = 1;
               break;
             }

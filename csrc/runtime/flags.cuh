@@ -20,6 +20,14 @@ __device__ __forceinline__ uint32_t* flag_word(void* flags_base, int slot, int s
   return reinterpret_cast<uint32_t*>(flags_base) + slot * PICO_MAX_PEERS + src;
 }
 
+// Epochs reach the kernels as an offset from a per-slot base word kept behind the flag words of
+// this rank's own flag buffer. Eager launches run with the host's mirror of that word, so the sum
+// is the absolute epoch; a captured CUDA graph keeps its offsets and a node at its end advances
+// the base by the number of epochs the graph used, which makes every replay continue the count.
+__device__ __forceinline__ uint32_t epoch_base(const void* local_flags, int slot) {
+  return __ldcg(reinterpret_cast<const uint32_t*>(local_flags) + PICO_FLAG_SLOTS * PICO_MAX_PEERS + slot);
+}
+
 // Spin until *p >= epoch or `timeout_ns` passes. On timeout records error 2 and returns false.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t epoch, uint64_t timeout_ns,
                                              int* status, int site) {
@@ -35,6 +43,45 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t epoch, 
       }
       __nanosleep(200);
     }
+  }
+}
+
+// Waits for words [slot][src] >= base + rel_epoch for src = threadIdx.x < world (call with all
+// threads of the CTA; returns false in every thread if any wait gave up).
+__device__ __forceinline__ bool wait_slot_all(const uint32_t* local_flags, int slot, int world,
+                                              uint32_t rel_epoch, uint64_t timeout_ns, int* status,
+                                              int site) {
+  __shared__ int pico_wait_ok;
+  if (threadIdx.x == 0) pico_wait_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const uint32_t epoch = epoch_base(local_flags, slot) + rel_epoch;
+    if (!wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + threadIdx.x, epoch, timeout_ns, status,
+                      site + threadIdx.x))
+      pico_wait_ok = 0;
+  }
+  __syncthreads();
+  return pico_wait_ok != 0;
+}
+
+// Grid-wide completion: the last CTA to finish raises flag [slot][my_rank] = base + rel_epoch on
+// every rank of `flags`. `counter` is a device word that returns to zero after each use.
+__device__ __forceinline__ void raise_flags_when_grid_done(unsigned int* counter, PicoPeerTable flags,
+                                                           int world, int my_rank, int slot,
+                                                           uint32_t rel_epoch) {
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool pico_last_cta;
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(counter, 1u) + 1u;
+    pico_last_cta = (done == gridDim.x);
+    if (pico_last_cta) *counter = 0;
+  }
+  __syncthreads();
+  if (pico_last_cta && (int)threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(flag_word(flags.ptr[threadIdx.x], slot, my_rank),
+                   epoch_base(flags.ptr[my_rank], slot) + rel_epoch);
   }
 }
 

@@ -12,17 +12,40 @@ __global__ void signal_peers_kernel(PicoPeerTable flags, int world, int my_rank,
   // make every earlier write of this stream (also those to peer memory) visible first
   __threadfence_system();
   const int t = threadIdx.x;
-  if (t < world) st_release_sys(flag_word(flags.ptr[t], slot, my_rank), epoch);
+  if (t < world)
+    st_release_sys(flag_word(flags.ptr[t], slot, my_rank), epoch_base(flags.ptr[my_rank], slot) + epoch);
 }
 
 __global__ void wait_flags_kernel(const uint32_t* local_flags, int world, int slot, uint32_t epoch,
                                   uint64_t timeout_ns, int* status) {
   const int t = threadIdx.x;
   if (t < world)
-    wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + t, epoch, timeout_ns, status, 900 + t);
+    wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + t, epoch_base(local_flags, slot) + epoch, timeout_ns,
+                 status, 900 + t);
+}
+
+__global__ void epoch_base_add_kernel(uint32_t* local_flags, PicoEpochDeltas d) {
+  const int t = threadIdx.x;
+  if (t < d.n) local_flags[PICO_FLAG_SLOTS * PICO_MAX_PEERS + d.slot[t]] += d.delta[t];
 }
 
 }  // namespace pico
+
+extern "C" int pico_epoch_base_add(uint32_t* local_flags, const PicoEpochDeltas* deltas, cudaStream_t stream) {
+  if (deltas->n < 0 || deltas->n > PICO_MAX_EPOCH_DELTAS) {
+    pico_host::set_error("epoch_base_add: %d entries (at most %d)", deltas->n, PICO_MAX_EPOCH_DELTAS);
+    return -2;
+  }
+  for (int i = 0; i < deltas->n; ++i)
+    if (deltas->slot[i] < 0 || deltas->slot[i] >= PICO_FLAG_SLOTS) {
+      pico_host::set_error("epoch_base_add: slot %d out of range", deltas->slot[i]);
+      return -2;
+    }
+  pico::epoch_base_add_kernel<<<1, 32, 0, stream>>>(local_flags, *deltas);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) pico_host::set_error("epoch_base_add: %s", cudaGetErrorString(e));
+  return (int)e;
+}
 
 extern "C" int pico_symm_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
   cudaError_t e = cudaMalloc(ptr, bytes);

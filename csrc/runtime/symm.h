@@ -10,12 +10,20 @@
 // source rank. A rank signals by storing a new, larger epoch into its own word on every peer
 // (release, system scope); a consumer waits (acquire, system scope, bounded) until the words it
 // needs reach the epoch. Epochs only grow, so flags are never cleared.
+//
+// The flag buffer of a rank is PICO_FLAG_BYTES long: the flag words, then one "epoch base" word
+// per slot. Every kernel adds the base word of its slot (read from its own rank's buffer) to the
+// epoch it is launched with. Outside CUDA graphs the host keeps a mirror of the base and passes
+// the difference, so nothing changes; a captured graph ends with pico_epoch_base_add, which moves
+// the base past the epochs the graph used, so the same graph can be replayed any number of times.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #define PICO_MAX_PEERS 8
 #define PICO_FLAG_SLOTS 256
+#define PICO_FLAG_BYTES ((PICO_FLAG_SLOTS * PICO_MAX_PEERS + PICO_FLAG_SLOTS) * 4)
+#define PICO_MAX_EPOCH_DELTAS 24
 
 #ifdef __cplusplus
 extern "C" {
@@ -24,6 +32,12 @@ extern "C" {
 typedef struct {
   void* ptr[PICO_MAX_PEERS];
 } PicoPeerTable;
+
+typedef struct {
+  int n;
+  int slot[PICO_MAX_EPOCH_DELTAS];
+  uint32_t delta[PICO_MAX_EPOCH_DELTAS];
+} PicoEpochDeltas;
 
 // cudaMalloc `bytes` (zero-filled) and export its IPC handle (64 bytes).
 int pico_symm_alloc(size_t bytes, void** ptr, unsigned char* handle64);
@@ -39,6 +53,9 @@ int pico_signal_peers(PicoPeerTable flags, int world, int my_rank, int slot, uin
 // [0, world). Gives up after timeout_ms (error code 2 in the status words); returns normally.
 int pico_wait_flags(const uint32_t* local_flags, int world, int slot, uint32_t epoch,
                     uint32_t timeout_ms, cudaStream_t stream);
+
+// base[slot[i]] += delta[i] in the epoch-base words of this rank's flag buffer (stream ordered).
+int pico_epoch_base_add(uint32_t* local_flags, const PicoEpochDeltas* deltas, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,1 @@
+"""``picotron.data_parallel``: see the modules of this package (aliases of ``picotron_b200.parallel``)."""

@@ -1,0 +1,1 @@
+"""``picotron.tensor_parallel``: see the modules of this package (aliases of ``picotron_b200.parallel``)."""

@@ -14,8 +14,11 @@ Added on top, all ignorable by a reader of the reference format:
 * files are written to ``*.tmp`` and renamed, and a ``manifest.json`` lists the files a complete
   checkpoint must contain; ``load_checkpoint`` refuses an incomplete one
 * extra keys ``rng_state`` and ``data_loader`` allow an exact resume of the data stream
-* ZeRO-sharded flat optimizer state is saved per data-parallel rank in
-  ``optimizer_dp_rank={dp}_{dp_ws}_<same suffix>.pth``
+* ZeRO-sharded optimizer state differs on every rank of the gradient-reduction group (data
+  parallel x context parallel, and expert parallel when it doubles as data parallelism), so
+  each of those ranks writes ``optimizer_dp_rank={dp}_{dp_ws}_cp_rank={cp}_{cp_ws}_<same
+  suffix>.pth``; the manifest lists these files too and a load refuses a missing shard or one
+  written for another group size
 
 ``init_model_with_dematerialized_weights`` / ``init_model_with_materialized_weights`` give the
 meta-device construction path of the reference (checkpoint.py:17-121): build without memory,
@@ -93,31 +96,38 @@ class CheckpointManager:
         self.pp_rank, self.pp_ws = m.pp_rank, m.pp_world_size
         self.ep_rank, self.ep_ws = m.ep_rank, m.ep_world_size
         self.dp_rank, self.dp_ws = m.dp_rank, m.dp_world_size
-        self.cp_rank = m.cp_rank
+        self.cp_rank, self.cp_ws = m.cp_rank, m.cp_world_size
         self.cp_dp_world_size = m.cp_dp_world_size
 
-    def _suffix(self) -> str:
-        s = (f"tp_rank_world_size={self.tp_rank}_{self.tp_ws}_"
-             f"pp_rank_world_size={self.pp_rank}_{self.pp_ws}")
+    def _suffix_of(self, tp: int, pp: int, ep: int) -> str:
+        s = f"tp_rank_world_size={tp}_{self.tp_ws}_pp_rank_world_size={pp}_{self.pp_ws}"
         if self.ep_ws > 1:
-            s += f"_ep_rank_world_size={self.ep_rank}_{self.ep_ws}"
+            s += f"_ep_rank_world_size={ep}_{self.ep_ws}"
         return s
+
+    def _suffix(self) -> str:
+        return self._suffix_of(self.tp_rank, self.pp_rank, self.ep_rank)
 
     def _get_checkpoint_path(self, out_dir: str) -> str:
         return os.path.join(out_dir, f"weights_{self._suffix()}.pth")
 
-    def _optimizer_shard_path(self, out_dir: str) -> str:
-        return os.path.join(out_dir, f"optimizer_dp_rank={self.dp_rank}_{self.dp_ws}_{self._suffix()}.pth")
+    def _shard_name(self, dp: int, cp: int, suffix: str) -> str:
+        return f"optimizer_dp_rank={dp}_{self.dp_ws}_cp_rank={cp}_{self.cp_ws}_{suffix}.pth"
 
-    def expected_files(self):
+    def _optimizer_shard_path(self, out_dir: str) -> str:
+        return os.path.join(out_dir, self._shard_name(self.dp_rank, self.cp_rank, self._suffix()))
+
+    def expected_files(self, sharded_optimizer: bool = False):
+        """Every file of a complete checkpoint: one weights file per (tp, pp, ep) coordinate and,
+        with a sharded optimizer, one optimizer shard per rank of the whole grid."""
         names = []
         for tp in range(self.tp_ws):
             for pp in range(self.pp_ws):
                 for ep in range(self.ep_ws):
-                    s = f"tp_rank_world_size={tp}_{self.tp_ws}_pp_rank_world_size={pp}_{self.pp_ws}"
-                    if self.ep_ws > 1:
-                        s += f"_ep_rank_world_size={ep}_{self.ep_ws}"
+                    s = self._suffix_of(tp, pp, ep)
                     names.append(f"weights_{s}.pth")
+                    if sharded_optimizer:
+                        names += [self._shard_name(dp, cp, s) for dp in range(self.dp_ws) for cp in range(self.cp_ws)]
         return names
 
     @staticmethod
@@ -134,8 +144,11 @@ class CheckpointManager:
                         data_loader=None, sharded_optimizer: bool = False):
         os.makedirs(out_dir, exist_ok=True)
         raw = self._unwrap(model)
-        if sharded_optimizer and optimizer is not None and self.cp_rank == 0:
-            self._atomic_save({"optimizer": optimizer.state_dict()}, self._optimizer_shard_path(out_dir))
+        if sharded_optimizer and optimizer is not None:
+            # every rank: the optimizer is sharded over data x context (x expert) parallel ranks
+            self._atomic_save({"optimizer": optimizer.state_dict(),
+                               "grid": [self.dp_ws, self.cp_ws, self.ep_ws, self.tp_ws, self.pp_ws]},
+                              self._optimizer_shard_path(out_dir))
         if self.dp_rank == 0 and self.cp_rank == 0:
             payload = {
                 "model": raw.state_dict(),
@@ -149,7 +162,8 @@ class CheckpointManager:
         if dist.is_initialized():
             dist.barrier()
         if (not dist.is_initialized()) or dist.get_rank() == 0:
-            manifest = {"files": self.expected_files(), "trained_steps": trained_steps,
+            manifest = {"files": self.expected_files(sharded_optimizer and optimizer is not None),
+                        "trained_steps": trained_steps,
                         "trained_tokens": trained_tokens}
             tmp = os.path.join(out_dir, "manifest.json.tmp")
             with open(tmp, "w") as fh:
@@ -176,8 +190,15 @@ class CheckpointManager:
             for k, v in ckpt["model"].items():
                 own[k].copy_(v)          # in place: parameters may be views of a flat buffer
         if optimizer is not None:
-            if sharded_optimizer and os.path.exists(self._optimizer_shard_path(out_dir)):
-                sd = torch.load(self._optimizer_shard_path(out_dir), map_location="cpu", weights_only=False)
+            if sharded_optimizer:
+                shard = self._optimizer_shard_path(out_dir)
+                if not os.path.exists(shard):
+                    raise FileNotFoundError(f"optimizer shard of this rank not found: {shard} (the checkpoint was "
+                                            "written with a different parallel layout or is incomplete)")
+                sd = torch.load(shard, map_location="cpu", weights_only=False)
+                grid = [self.dp_ws, self.cp_ws, self.ep_ws, self.tp_ws, self.pp_ws]
+                if sd.get("grid", grid) != grid:
+                    raise ValueError(f"optimizer shard {shard} was written for grid {sd['grid']}, this run has {grid}")
                 optimizer.load_state_dict(sd["optimizer"])
             elif ckpt.get("optimizer") is not None:
                 optimizer.load_state_dict(ckpt["optimizer"])

@@ -56,10 +56,12 @@ DEFAULTS: Dict[str, Dict[str, Any]] = {
                   router_aux_loss_coef=0.0, router_bias_update_rate=0.0, parallel_block=False, init_std=None,
                   shared_expert_intermediate_size=None),
     "training": dict(seed=42, learning_rate=3e-4, total_train_steps=200, seq_length=1024, micro_batch_size=32,
-                     gradient_accumulation_steps=1, num_samples=400000, max_tokens=None, weight_decay=0.01),
+                     gradient_accumulation_steps=1, num_samples=400000, max_tokens=None, weight_decay=0.01,
+                     cuda_graph=True),
     "dataset": dict(name="roneneldan/TinyStories", subset_name=None, num_workers=0, num_proc=4, split="train"),
     "checkpoint": dict(save_dir="ckpt", save_frequency=300, load_path=""),
-    "logging": dict(use_wandb=False, project_name="picotron", run_name=None, metrics_jsonl=None),
+    "logging": dict(use_wandb=False, project_name="picotron", run_name=None, metrics_jsonl=None,
+                    step_breakdown=False),
     "environment": dict(OMP_NUM_THREADS="1", TOKENIZERS_PARALLELISM="false", FLASH_ATTEN="1", HF_TOKEN=None),
 }
 

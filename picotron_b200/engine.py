@@ -201,6 +201,14 @@ class TrainEngine:
         self._build_optimizer()
         self.trained_steps = 0
         self.trained_tokens = 0
+        #: optional ``runtime.timing.EventTimer``: when set, every step records the device time of its
+        #: sections ("micro_batches" = forward + backward of all micro-batches, or "forward" /
+        #: "backward" separately on the eager path, and "optimizer" = gradient reduction + update +
+        #: parameter gather); ``timer.collect()`` returns the milliseconds, MAX over ranks
+        self.timer = None
+
+    def _section(self, name: str):
+        return self.timer.section(name) if self.timer is not None else contextlib.nullcontext()
 
     # ------------------------------------------------------------------------------ build
     def _build_model(self):
@@ -219,7 +227,7 @@ class TrainEngine:
             model = wrap_pipeline(model, self.model_config, d["pp_engine"], d["num_virtual_stages"])
         if m.cp_world_size > 1:
             from .parallel.context_parallel import apply_context_parallel
-            apply_context_parallel(model, attention=d["cp_attention"])
+            apply_context_parallel(model, attention=d["cp_attention"], seq_length=self.cfg["training"]["seq_length"])
         # (re-)initialise in canonical module order from the configured seed: tensor-parallel
         # layers draw the full master weight and keep their slice, so a TP run starts from
         # exactly the weights of the single-device run (reference: checkpoint.py:114-119)
@@ -229,6 +237,8 @@ class TrainEngine:
         model.to(self.dtype).to(self.device)
         self.model = model
         self.flat = self.device.type == "cuda" and self.dtype == torch.bfloat16
+        self._symm_groups = []         # symmetric-memory groups whose kernels run inside a micro-batch
+        self._mb_graph = None
         self.dp_symm = None
         allocator = None
         if self.flat and self._use_fused_dp():
@@ -278,6 +288,7 @@ class TrainEngine:
             return
         s_local = t["seq_length"] // m.cp_world_size
         sg = SymmGroup(m.cp_group, device=self.device)
+        self._symm_groups.append(sg)
         if d["cp_attention"] == "ring":
             from .ops.fused_cp import CPFused
             self.fused_cp = CPFused(sg, t["micro_batch_size"], s_local, kv_heads * head_dim)
@@ -317,6 +328,7 @@ class TrainEngine:
             if not layers or layers[0].expert_dim % 128 != 0:
                 return
             sg = SymmGroup(m.ep_group, device=self.device)
+            self._symm_groups.append(sg)
             # rows one rank may receive, as a multiple of the balanced load: an untrained router is
             # skewed (single experts at 3-5x, groups of 8 experts at up to ~1.7x the mean were measured)
             slack = float(os.environ.get("PICO_EP_VAR_SLACK", getattr(mc, "ep_var_slack", 3.0) or 3.0))
@@ -331,6 +343,7 @@ class TrainEngine:
         if not layers or layers[0].expert_dim % 8 != 0:
             return
         sg = SymmGroup(m.ep_group, device=self.device)
+        self._symm_groups.append(sg)
         self.fused_ep = EPFused(sg, layers[0].num_local_experts, cap, layers[0].expert_dim)
         for mod in layers:
             mod.fused_ep = self.fused_ep
@@ -342,6 +355,7 @@ class TrainEngine:
         ``PICO_FUSED_TP=0`` keeps the NCCL collectives."""
         import os
         d, t, m = self.cfg["distributed"], self.cfg["training"], self.pgm
+        ce_ops.install_peer_exchange(m.tp_group, None)
         if not (self.flat and m.tp_world_size > 1 and d["sequence_parallel"] and not d["overlap_comm"]):
             return
         if os.environ.get("PICO_FUSED_TP", "1") == "0":
@@ -353,8 +367,10 @@ class TrainEngine:
         if not TPFused.usable(m_local):
             return
         sg = SymmGroup(m.tp_group, device=self.device)
+        self._symm_groups.append(sg)
         self.fused_tp = TPFused(sg, m_local, self.model_config.hidden_size)
         install_fused_tp(self.model, self.fused_tp)
+        ce_ops.install_peer_exchange(m.tp_group, self.fused_tp.ce_exchange)
 
     def _use_fused_dp(self) -> bool:
         """ZeRO-1 through the peer-memory optimizer kernel (``csrc/fused/dp_zero.cu``): needs the
@@ -430,7 +446,11 @@ class TrainEngine:
         ga = dl.grad_acc_steps
         if m.pp_world_size > 1:
             from .parallel.pipeline_parallel import run_pipeline_step
-            loss = run_pipeline_step(self, device_batches)
+            with self._section("micro_batches"):
+                loss = run_pipeline_step(self, device_batches)
+        elif self._graph_wanted():
+            with self._section("micro_batches"):
+                loss = self._graphed_micro_batches(device_batches)
         else:
             loss = torch.zeros((), device=self.device, dtype=torch.float32)
             for i in range(ga):
@@ -441,16 +461,137 @@ class TrainEngine:
                     input_ids = batch["input_ids"].to(self.device, non_blocking=True)
                     target_ids = batch["target_ids"].to(self.device, non_blocking=True)
                 self._sync_context(i == ga - 1)
-                logits = self.dp_model(input_ids=input_ids)
-                mb_loss = loss_fn(self.model, logits, target_ids, divisor=ga)
-                aux = self._aux_loss()
-                total = mb_loss + aux / ga if aux is not None else mb_loss
-                total.backward()
-                loss += mb_loss.detach().float()
-        self._optimizer_step()
+                loss += self._micro_batch(input_ids, target_ids, ga)
+        with self._section("optimizer"):
+            self._optimizer_step()
         self.trained_steps += 1
         self.trained_tokens += self.tokens_per_step
         return loss
+
+    def _micro_batch(self, input_ids, target_ids, ga: int) -> torch.Tensor:
+        """Forward + backward of one micro-batch; gradients accumulate; returns its detached loss / ga."""
+        timed = self.timer is not None and not (self.device.type == "cuda"
+                                                and torch.cuda.is_current_stream_capturing())
+        with (self.timer.section("forward") if timed else contextlib.nullcontext()):
+            logits = self.dp_model(input_ids=input_ids)
+            mb_loss = loss_fn(self.model, logits, target_ids, divisor=ga)
+            aux = self._aux_loss()
+            total = mb_loss + aux / ga if aux is not None else mb_loss
+        with (self.timer.section("backward") if timed else contextlib.nullcontext()):
+            total.backward()
+        return mb_loss.detach().float()
+
+    # ------------------------------------------------------------------------------ CUDA graph
+    def _graph_wanted(self) -> bool:
+        """The micro-batch (forward + backward) is replayed from a CUDA graph on the flat bf16 path:
+        its few hundred to few thousand launches then cost the host one call, which is what keeps
+        small per-rank kernels (tensor parallelism over 4 GPUs and more) from being bound by launch
+        overhead. ``training.cuda_graph: false`` or ``PICO_CUDA_GRAPH=0`` keeps eager launches; so do
+        the paths that synchronise with the host inside a micro-batch (tiled / NCCL expert exchange,
+        NCCL context parallelism, the hook-based data-parallel wrappers)."""
+        import os
+        if self._mb_graph is False:
+            return False
+        if self._mb_graph is not None:
+            return True
+        t, m, mc = self.cfg["training"], self.pgm, self.model_config
+        from .ops import reference_ops_forced
+        ok = self.flat and t.get("cuda_graph", True) and os.environ.get("PICO_CUDA_GRAPH", "1") != "0" \
+            and not reference_ops_forced()
+        if ok and getattr(mc, "num_experts", 1) > 1:
+            ok = self._moe_graph_safe()
+        if ok and m.cp_world_size > 1:
+            ok = self.fused_cp is not None
+        if ok and m.tp_world_size > 1:
+            ok = self.fused_tp is not None
+        if not ok:
+            self._mb_graph = False
+        return ok
+
+    def _moe_graph_safe(self) -> bool:
+        """Mixture-of-experts layers can be captured only on the paths whose routing and exchange
+        never read a device value on the host."""
+        return False
+
+    def _graphed_micro_batches(self, device_batches) -> torch.Tensor:
+        from . import ops
+        dl = self.data_loader
+        ga = dl.grad_acc_steps
+        if self._mb_graph is None and self.trained_steps < 1:
+            # first step eagerly: lazily created buffers (scratch, tables, counters) must exist
+            # before a capture, which may not allocate outside its pool
+            loss = torch.zeros((), device=self.device, dtype=torch.float32)
+            for i in range(ga):
+                inp, tgt = self._fetch(device_batches, i)
+                loss += self._micro_batch(inp.to(self.device, non_blocking=True),
+                                          tgt.to(self.device, non_blocking=True), ga)
+            return loss
+        if self._mb_graph is None:
+            self._capture_micro_batch(ga)
+        g = self._mb_graph
+        g["loss"].zero_()
+        for i in range(ga):
+            inp, tgt = self._fetch(device_batches, i)
+            g["input_ids"].copy_(inp, non_blocking=True)
+            g["target_ids"].copy_(tgt, non_blocking=True)
+            for rec in g["epochs"]:
+                rec.before_replay()
+            g["graph"].replay()
+            for rec in g["epochs"]:
+                rec.after_replay()
+            ops.count_launch(g["launches"])
+        return g["loss"].clone()
+
+    def _fetch(self, device_batches, i):
+        """Micro-batch i of this step: the caller's device tensors, or the next (pinned host) batch
+        of the data loader."""
+        if device_batches is not None:
+            return device_batches[i]
+        batch = next(self.data_loader)
+        return batch["input_ids"], batch["target_ids"]
+
+    def _capture_micro_batch(self, ga: int):
+        from . import ops
+        dl = self.data_loader
+        shape = (dl.micro_batch_size, dl.seq_length_per_gpu)
+        inp = torch.zeros(shape, dtype=torch.long, device=self.device)
+        tgt = torch.zeros(shape, dtype=torch.long, device=self.device)
+        loss = torch.zeros((), device=self.device, dtype=torch.float32)
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        l0 = ops.launches()
+        # thread-local capture mode: the process group's watchdog thread may query its events while
+        # this thread captures
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            for sg in self._symm_groups:
+                sg.begin_graph()
+                sg.barrier()
+            loss.add_(self._micro_batch(inp, tgt, ga))
+            recs = []
+            for sg in self._symm_groups:
+                sg.barrier()
+                recs.append(sg.end_graph())
+        launches = ops.launches() - l0
+        ops.count_launch(-launches)          # a capture launches nothing
+        # The fused paths alternate between two copies of each buffer, which is safe while a rank
+        # is never two operations ahead of a peer. The group barriers at both ends of the graph
+        # keep that true across replays and across eager launches around them, whichever copy
+        # comes first.
+        self._mb_graph = {"graph": graph, "input_ids": inp, "target_ids": tgt, "loss": loss, "epochs": recs,
+                          "launches": launches}
+
+    def close(self):
+        """Release the symmetric-memory buffers (peer mappings and this rank's allocations). Collective
+        over each group; the engine must not be used afterwards."""
+        self._mb_graph = False
+        if torch.cuda.is_available() and self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        groups = list(self._symm_groups)
+        if self.dp_symm is not None:
+            groups.append(self.dp_symm)
+        for sg in groups:
+            sg.close()
+        self._symm_groups = []
 
     @property
     def optimizer_is_sharded(self) -> bool:

@@ -13,8 +13,6 @@ the loss. The reference keeps a full ``[N, V/tp]`` softmax for the backward
 """
 from __future__ import annotations
 
-import os
-
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
@@ -25,6 +23,33 @@ from . import count_launch, ext, use_kernels
 def cross_entropy_ref(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     """Per-token loss, dense vocabulary."""
     return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.view(-1), reduction="none")
+
+
+#: process group -> object with ``stats_loss_grad(l2, targets, loss, dlogits, scale, vocab_start)`` that
+#: exchanges the per-shard triples through NVLink peer memory inside the two loss kernels
+#: (``ops.fused_tp.PeerStatsExchange``); installed by the engine for its tensor-parallel group
+_PEER_EXCHANGE = {}
+
+
+def install_peer_exchange(group, exchange) -> None:
+    if exchange is None:
+        _PEER_EXCHANGE.pop(group, None)
+    else:
+        _PEER_EXCHANGE[group] = exchange
+
+
+def _stats_loss_grad(l2, t, loss, dlogits, scale, vocab_start, group):
+    """The two kernel passes of the fused loss: statistics, then loss + gradient over the logits."""
+    rows, V = l2.shape
+    ex = _PEER_EXCHANGE.get(group) if group is not None else None
+    if ex is not None and ex.fits(rows):
+        ex.stats_loss_grad(l2, t, loss, dlogits, scale, vocab_start)
+        return
+    stats = torch.empty((rows, 3), device=l2.device, dtype=torch.float32)
+    ext().ce_stats(l2, l2.stride(0), t, stats, rows, V, vocab_start)
+    stats = combine_stats(stats, group)
+    ext().ce_loss_grad(l2, l2.stride(0), t, stats, loss, dlogits, dlogits.stride(0), scale, rows, V, vocab_start)
+    count_launch(2)
 
 
 def combine_stats(stats: torch.Tensor, group) -> torch.Tensor:
@@ -91,14 +116,9 @@ class _FusedCEFn(torch.autograd.Function):
         t = targets.reshape(-1)
         if not t.is_contiguous():
             t = t.contiguous()
-        stats = torch.empty((rows, 3), device=logits.device, dtype=torch.float32)
-        ext().ce_stats(l2, l2.stride(0), t, stats, rows, V, vocab_start)
-        stats = combine_stats(stats, group)
         loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
         dlogits = l2 if inplace else torch.empty_like(l2)
-        ext().ce_loss_grad(l2, l2.stride(0), t, stats, loss, dlogits, dlogits.stride(0), 1.0, rows, V,
-                           vocab_start)
-        count_launch(2)
+        _stats_loss_grad(l2, t, loss, dlogits, 1.0, vocab_start, group)
         ctx.save_for_backward(dlogits)
         ctx.shape = logits.shape
         return loss.view(targets.shape)
@@ -114,11 +134,11 @@ class _FusedCEFn(torch.autograd.Function):
 
 class _FusedMeanCEFn(torch.autograd.Function):
     """Scalar ``mean(loss) / divisor``. The gradient of that scalar w.r.t. the logits,
-    ``(softmax - onehot) / (rows * divisor)``, is written over the logits during the forward pass
-    and handed out unchanged in backward: the result must be the quantity ``backward()`` is called
-    on (possibly added to other losses), i.e. its incoming gradient must be exactly 1. This saves
-    the extra pass over the ``[rows, V]`` gradient that a late scaling costs.
-    ``PICO_CE_CHECK_UNIT_GRAD=1`` verifies the contract (with a device synchronisation)."""
+    ``(softmax - onehot) / (rows * divisor)``, is written over the logits during the forward pass.
+    When the result is what ``backward()`` is called on (incoming gradient 1, the training loop's
+    case) backward hands that buffer out untouched; any other incoming gradient is applied by a
+    kernel that first reads the scalar on the device and returns at once when it is 1, so the
+    common case costs no pass over ``[rows, V]`` and no host synchronisation."""
 
     @staticmethod
     def forward(ctx, logits, targets, vocab_start, group, divisor):
@@ -129,13 +149,9 @@ class _FusedMeanCEFn(torch.autograd.Function):
         t = targets.reshape(-1)
         if not t.is_contiguous():
             t = t.contiguous()
-        stats = torch.empty((rows, 3), device=logits.device, dtype=torch.float32)
-        ext().ce_stats(l2, l2.stride(0), t, stats, rows, V, vocab_start)
-        stats = combine_stats(stats, group)
         loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
         scale = 1.0 / (rows * divisor)
-        ext().ce_loss_grad(l2, l2.stride(0), t, stats, loss, l2, l2.stride(0), scale, rows, V, vocab_start)
-        count_launch(2)
+        _stats_loss_grad(l2, t, loss, l2, scale, vocab_start, group)
         ctx.save_for_backward(l2)
         ctx.shape = logits.shape
         return loss.sum() * scale
@@ -143,8 +159,11 @@ class _FusedMeanCEFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         (dlogits,) = ctx.saved_tensors
-        if os.environ.get("PICO_CE_CHECK_UNIT_GRAD", "0") == "1":
-            assert float(dloss) == 1.0, "mean_cross_entropy must be the root of backward (incoming gradient 1)"
+        if dlogits.is_contiguous():
+            ext().scale_unless_one(dlogits, dloss.reshape(1).float())
+            count_launch()
+        else:
+            dlogits.mul_(dloss.to(dlogits.dtype))
         return dlogits.view(ctx.shape), None, None, None, None
 
 

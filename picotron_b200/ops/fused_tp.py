@@ -32,6 +32,40 @@ from . import gemm as gemm_ops
 BM = 128
 GATHER_SLOTS = (0, 1)
 SCATTER_SLOTS = (2, 3)
+CE_SLOTS = (4, 5)
+
+
+class PeerStatsExchange:
+    """Vocabulary-parallel cross entropy without a collective call: the statistics kernel stores
+    each row's (max, sum, target logit) of this rank's vocabulary shard into every rank's
+    ``[world, rows, 3]`` table and raises a flag; the loss/gradient kernel waits for all ranks'
+    flags and merges the triples itself. Replaces the three all-reduces of
+    picotron/tensor_parallel/tp_communications.py:150,160,166."""
+
+    def __init__(self, symm_group, max_rows: int, timeout_ms: int):
+        self.sg = symm_group
+        self.world, self.rank = symm_group.world, symm_group.rank
+        self.max_rows = max_rows
+        self.tables = [symm_group.alloc(self.world * max_rows * 3 * 4) for _ in range(2)]
+        self.n = 0
+        self.timeout_ms = timeout_ms
+
+    def fits(self, rows: int) -> bool:
+        return rows <= self.max_rows
+
+    def stats_loss_grad(self, l2, targets, loss, dlogits, scale, vocab_start):
+        rows, V = l2.shape
+        b = self.n % 2
+        self.n += 1
+        slot = CE_SLOTS[b]
+        epoch = self.sg.next_epoch(slot)
+        ext().ce_stats_push(l2, l2.stride(0), targets, rows, V, vocab_start, self.tables[b].ptrs,
+                            self.sg.flags.ptrs, self.world, self.rank, slot, epoch)
+        table = self.tables[b].view(torch.float32, (self.world, rows, 3))
+        ext().ce_loss_grad_gathered(l2, l2.stride(0), targets, table, loss, dlogits, dlogits.stride(0), scale, rows,
+                                    V, vocab_start, self.sg.flags.local_ptr, self.world, slot, epoch,
+                                    self.timeout_ms)
+        count_launch(2)
 
 
 class TPFused:
@@ -46,6 +80,7 @@ class TPFused:
         self.n_gather = 0
         self.n_scatter = 0
         self.timeout_ms = int(os.environ.get("PICO_COMM_TIMEOUT_MS", "20000"))
+        self.ce_exchange = PeerStatsExchange(symm_group, self.m_full, self.timeout_ms)
 
     @staticmethod
     def usable(m_local: int) -> bool:
@@ -209,6 +244,58 @@ class _LinearRSFused(torch.autograd.Function):
         dw = gemm_ops.wgrad_into(w, buf, x2)
         dx = from_rank_major(dx2, tp.world, ctx.b) if ctx.batch_major_in else dx2
         return dx, dw, None, None, None, (dy if ctx.has_addend else None)
+
+
+class _EmbeddingRSFused(torch.autograd.Function):
+    """Vocabulary-parallel embedding under sequence parallelism without a collective call: every
+    rank looks its vocabulary shard up for the whole sequence (rows of ids it does not own are
+    zero), stores row block o into its slot of rank o's staging buffer and sums the slots it
+    received; backward gathers the output gradient by pushing and scatters it into the table's
+    gradient. ids: [b, s] (full sequence); returns [b, s/tp, H]."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, vocab_start, tp: TPFused):
+        b, s = ids.shape
+        V, H = weight.shape
+        ids_rm = ids.view(b, tp.world, s // tp.world).transpose(0, 1).reshape(-1).contiguous()
+        part = torch.empty((tp.m_full, H), device=weight.device, dtype=weight.dtype)
+        ext().embedding_fwd(weight, ids_rm, part, tp.m_full, H, V, vocab_start)
+        sb = tp.n_scatter % 2
+        tp.n_scatter += 1
+        slot = SCATTER_SLOTS[sb]
+        epoch = tp.sg.next_epoch(slot)
+        ext().scatter_rows(part, tp.staging[sb].ptrs, tp.sg.flags.ptrs, tp.world, tp.rank, tp.world, tp.m_local, H,
+                           slot, epoch)
+        count_launch(2)
+        y = tp.scatter_sum(sb, slot, epoch, H)
+        ctx.save_for_backward(ids_rm, weight)
+        ctx.tp, ctx.vocab_start, ctx.shape = tp, vocab_start, (b, s // tp.world, H)
+        return y.view(b, s // tp.world, H)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ids_rm, weight = ctx.saved_tensors
+        tp = ctx.tp
+        V, H = weight.shape
+        dy2 = dy.reshape(-1, H)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        buf, slot, epoch = tp.gather_push(dy2)
+        tp.wait_gather(slot, epoch)
+        main_grad = getattr(weight, "main_grad", None)
+        acc = main_grad if main_grad is not None else torch.zeros((V, H), device=weight.device, dtype=torch.float32)
+        ext().embedding_bwd(buf, ids_rm, acc, tp.m_full, H, V, ctx.vocab_start)
+        count_launch()
+        if main_grad is not None:
+            hook = getattr(weight, "grad_ready_hook", None)
+            if hook is not None:
+                hook()
+            return None, None, None, None
+        return None, acc.to(weight.dtype), None, None
+
+
+def embedding_rs(ids, weight, vocab_start: int, tp: TPFused):
+    return _EmbeddingRSFused.apply(ids, weight, vocab_start, tp)
 
 
 def ag_linear(x, tp: TPFused, mods, batch_major: bool):

@@ -159,9 +159,12 @@ def update_rope_for_context_parallel(cos, sin, cp_rank=None, cp_world_size=None)
     return cos[cp_rank * per:(cp_rank + 1) * per], sin[cp_rank * per:(cp_rank + 1) * per]
 
 
-def apply_context_parallel(model, attention: str = "ring", group=None):
+def apply_context_parallel(model, attention: str = "ring", group=None, seq_length: int = None):
     """Install ring or Ulysses attention on every layer and offset RoPE positions to this rank's
-    slice of the sequence. Returns the model."""
+    slice of the sequence: rank r holds positions ``[r * s_local, (r + 1) * s_local)`` with
+    ``s_local = seq_length / cp``. ``seq_length`` is the training sequence length; it defaults to
+    the model's ``max_position_embeddings`` (the reference slices its tables by that,
+    context_parallel.py:326-334), which is only right when the two are equal. Returns the model."""
     m = pgm.get_pgm()
     group = group if group is not None else m.cp_group
     n, rank = group_size(group), group_rank(group)
@@ -177,7 +180,10 @@ def apply_context_parallel(model, attention: str = "ring", group=None):
             return ring_attention_bshd(q, k, v, causal, sm_scale, group)
     for layer in model.decoder_layers_iter():
         layer.attention.core = core
-    s_total = model.rope.max_positions
+    s_total = model.rope.max_positions if seq_length is None else int(seq_length)
+    assert s_total <= model.rope.max_positions, \
+        f"sequence length {s_total} exceeds max_position_embeddings {model.rope.max_positions}"
+    assert s_total % n == 0, "sequence length must be divisible by the context-parallel size"
     model.rope.pos_offset = rank * (s_total // n)
     model.cp_group = group
     model.cp_attention = attention

@@ -178,6 +178,13 @@ def run_schedule(engine: str, model, data_loader, tensor_shapes, device, dtype, 
     last_b = max(i for i, a in enumerate(my_actions) if a[0] == sched.B)
     if has_dp_hooks:
         model.require_backward_grad_sync = False
+    # With one model chunk per rank the hooks reduce gradients during this rank's very last
+    # backward. With several chunks (interleaved 1F1B) that last backward belongs to one chunk only;
+    # the other chunks finished earlier with synchronisation off, so everything is reduced once at
+    # the end instead (as for the schedules that split off weight gradients). The reference turns
+    # synchronisation on for the last backward only (pp_schedules.py:347) and leaves the other
+    # chunk's gradients un-reduced.
+    sync_at_end = split_w or v > 1
     gemm_ops.set_zero_bubble(split_w)
     saved: Dict[tuple, tuple] = {}          # (chunk, mb) -> (input, output, aux)
     local_act: Dict[tuple, torch.Tensor] = {}   # hand-offs between chunks on the same rank
@@ -223,7 +230,7 @@ def run_schedule(engine: str, model, data_loader, tensor_shapes, device, dtype, 
                         grad = local_grad.pop((s, i))
                     else:
                         grad = comm.take(("grad", s, i))
-                    if has_dp_hooks and not split_w and n_done == last_b:
+                    if has_dp_hooks and not sync_at_end and n_done == last_b:
                         model.require_backward_grad_sync = True
                     extra_t = [aux] if aux is not None else []
                     extra_g = [torch.full_like(aux, 1.0 / m)] if aux is not None else []
@@ -246,7 +253,7 @@ def run_schedule(engine: str, model, data_loader, tensor_shapes, device, dtype, 
     finally:
         gemm_ops.set_zero_bubble(False)
     assert not saved and not deferred
-    if has_dp_hooks and split_w and hasattr(model, "sync_all"):
+    if has_dp_hooks and sync_at_end and hasattr(model, "sync_all"):
         model.sync_all()
     return total_loss
 

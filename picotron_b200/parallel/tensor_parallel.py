@@ -158,6 +158,9 @@ def install_fused_tp(model, tp_ctx) -> int:
                 and not mod.overlap_comm and mod.tp_world_size > 1:
             mod.fused = tp_ctx
             n += 1
+        elif isinstance(mod, VocabParallelEmbedding) and mod.sequence_parallel and mod.tp_world_size > 1:
+            mod.fused = tp_ctx
+            n += 1
     return n
 
 
@@ -254,6 +257,12 @@ class VocabParallelEmbedding(nn.Module):
             self.weight.copy_(master[self.vocab_start_index:self.vocab_end_index])
 
     def forward(self, input_ids):
+        tp = getattr(self, "fused", None)
+        if tp is not None and self.sequence_parallel and input_ids.is_cuda and input_ids.dim() == 2 \
+                and input_ids.numel() == tp.m_full and self.weight.dtype == torch.bfloat16 \
+                and self.embedding_dim <= tp.max_cols and self.embedding_dim % 8 == 0:
+            from ..ops import fused_tp
+            return fused_tp.embedding_rs(input_ids, self.weight, self.vocab_start_index, tp)
         out = emb_ops.embedding(input_ids, self.weight, self.vocab_start_index)
         if self.tp_world_size == 1:
             return out

@@ -18,6 +18,8 @@ from .. import ops
 
 FLAG_SLOTS = 256
 MAX_PEERS = 8
+FLAG_BYTES = (FLAG_SLOTS * MAX_PEERS + FLAG_SLOTS) * 4   # flag words, then one epoch-base word per slot
+MAX_EPOCH_DELTAS = 24
 
 
 class SymmBuffer:
@@ -37,6 +39,28 @@ class SymmBuffer:
         return [p + offset_bytes for p in self.ptrs]
 
 
+class GraphEpochs:
+    """What a captured graph assumed about a group's epochs: ``used[slot]`` epochs per replay,
+    starting ``rel0[slot]`` above the slot's base word."""
+
+    def __init__(self, group: "SymmGroup", used, rel0):
+        self.group, self.used, self.rel0 = group, used, rel0
+
+    def before_replay(self) -> None:
+        """Eager kernels that used one of the graph's slots since the last replay moved the epoch
+        without moving the base: re-align the base (one tiny launch, only when that happened)."""
+        g = self.group
+        slots = [s for s in self.used if g._epochs[s] - g._base[s] != self.rel0[s]]
+        if slots:
+            g._add_base(slots, [g._epochs[s] - g._base[s] - self.rel0[s] for s in slots])
+
+    def after_replay(self) -> None:
+        g = self.group
+        for s, n in self.used.items():
+            g._epochs[s] += n
+            g._base[s] += n
+
+
 class SymmGroup:
     def __init__(self, group=None, device=None):
         self.group = group
@@ -45,8 +69,11 @@ class SymmGroup:
         assert self.world <= MAX_PEERS, f"at most {MAX_PEERS} GPUs per symmetric group"
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self._buffers: List[SymmBuffer] = []
-        self.flags = self.alloc(FLAG_SLOTS * MAX_PEERS * 4)
-        self._epochs = [0] * FLAG_SLOTS
+        self.flags = self.alloc(FLAG_BYTES)
+        self._epochs = [0] * FLAG_SLOTS          # absolute epoch last used per slot
+        self._base = [0] * FLAG_SLOTS            # host mirror of the device's epoch-base words
+        self._recording = None                   # slot -> epochs used, while a graph is being captured
+        self._closed = False
 
     def alloc(self, nbytes: int) -> SymmBuffer:
         """Collective over the group: every rank must call it with the same size."""
@@ -65,9 +92,61 @@ class SymmGroup:
         self._buffers.append(buf)
         return buf
 
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's. Collective in effect: every rank must stop
+        using the group's buffers before any rank closes (callers synchronise and barrier first)."""
+        if self._closed:
+            return
+        self._closed = True
+        e = ops.ext()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for buf in self._buffers:
+                for r, p in enumerate(buf.ptrs):
+                    if r != self.rank and p != buf.local_ptr:
+                        e.symm_close(p)
+            if self.world > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)       # nobody frees memory a peer still has mapped
+            for buf in self._buffers:
+                e.symm_free(buf.local_ptr)
+        self._buffers.clear()
+
     def next_epoch(self, slot: int) -> int:
+        """The next epoch of ``slot`` as kernels take it: relative to the slot's device-side base
+        word (zero until a CUDA graph over this group has been replayed)."""
         self._epochs[slot] += 1
-        return self._epochs[slot]
+        if self._recording is not None:
+            self._recording[slot] = self._recording.get(slot, 0) + 1
+        return self._epochs[slot] - self._base[slot]
+
+    # -- CUDA graph support ---------------------------------------------------------------------
+    def begin_graph(self) -> None:
+        """Call right after stream capture starts: epochs handed out from now on belong to the graph."""
+        assert self._recording is None, "nested graph capture over one symmetric group"
+        self._recording = {}
+        self._rel0 = {}
+
+    def end_graph(self) -> "GraphEpochs":
+        """Call at the end of the captured region (still capturing): appends the node that moves the
+        device-side bases past the epochs the graph used, and returns the record ``replay`` needs."""
+        used = dict(self._recording)
+        self._recording = None
+        slots = sorted(used)
+        assert len(slots) <= MAX_EPOCH_DELTAS, "too many flag slots in one graph"
+        rel0 = {s: self._epochs[s] - used[s] - self._base[s] for s in slots}
+        if slots:
+            ops.ext().epoch_base_add(self.flags.local_ptr, slots, [used[s] for s in slots])
+            ops.count_launch()
+        # the capture itself executed nothing: take the epochs back until the first replay
+        for s in slots:
+            self._epochs[s] -= used[s]
+        return GraphEpochs(self, used, rel0)
+
+    def _add_base(self, slots, deltas) -> None:
+        ops.ext().epoch_base_add(self.flags.local_ptr, list(slots), list(deltas))
+        ops.count_launch()
+        for s, d in zip(slots, deltas):
+            self._base[s] += d
 
     def signal(self, slot: int, epoch: int) -> None:
         ops.ext().signal_peers(self.flags.ptrs, self.world, self.rank, slot, epoch)

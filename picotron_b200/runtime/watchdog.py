@@ -1,10 +1,15 @@
 """Host-side failure detection: per-rank step heartbeats through the rendezvous store.
 
-Every rank publishes ``(step, wall time)`` after each optimizer step; a daemon thread on every
-rank reads all peers' entries and, when some rank has not advanced for ``timeout_s`` seconds
-while this rank has, calls ``on_failure(stale_ranks)`` — by default it prints which ranks are
-missing and exits the process with status 3 so the launcher can restart from the last complete
-checkpoint. Nothing here touches the GPU: a hung or dead peer is noticed on the host before the
+Every rank publishes its step counter after each optimizer step; a daemon thread on every rank
+reads all peers' entries and notes, on its own clock, when each entry last changed. A peer is
+stale when its entry has not changed for ``timeout_s`` seconds and it is not ahead of this rank.
+Two cases follow: the peer is behind (it died or hung between steps), or the whole job sits in
+the same step because one rank hung inside it and the others block in its collectives — then
+every rank sees every other rank stale and its own last step equally old. Either way
+``on_failure(stale_ranks)`` is called — by default it prints which ranks are missing and exits
+the process with status 3 so the launcher can restart from the last complete checkpoint. Ages are
+measured with the reader's monotonic clock from the moment it saw the value change, so clock
+differences between hosts do not matter. Nothing here touches the GPU: a hung or dead peer is noticed on the host before the
 next collective is issued (the reference only has the 3-minute process-group timeout,
 train.py:137-143).
 """
@@ -27,6 +32,8 @@ class StepWatchdog:
         self._stop = threading.Event()
         self._thread = None
         self._my_step = -1
+        self._my_beat_at = time.monotonic()
+        self._seen = {}            # peer rank -> (last value read, local time it was first seen)
         self.failed_ranks: List[int] = []
         if store is not None and world_size > 1:
             self.beat(-1)
@@ -44,29 +51,33 @@ class StepWatchdog:
 
     def beat(self, step: int) -> None:
         self._my_step = step
+        self._my_beat_at = time.monotonic()
         if self.store is not None:
-            self.store.set(f"{self.prefix}/{self.rank}", f"{step}:{time.time()}")
+            self.store.set(f"{self.prefix}/{self.rank}", str(step))
 
     def _read(self, r: int):
         try:
-            raw = self.store.get(f"{self.prefix}/{r}").decode()
-            step, ts = raw.split(":")
-            return int(step), float(ts)
+            return int(self.store.get(f"{self.prefix}/{r}").decode().split(":")[0])
         except Exception:
             return None
 
     def check_once(self, now: Optional[float] = None) -> List[int]:
-        """Ranks whose heartbeat is older than the timeout and behind this rank's step."""
-        now = time.time() if now is None else now
+        """Ranks that have made no progress for ``timeout_s``: behind this rank, or in the same step
+        while this rank has been stuck there for as long. ``now``: this rank's monotonic time."""
+        now = time.monotonic() if now is None else now
         stale = []
         for r in range(self.world_size):
             if r == self.rank:
                 continue
-            hb = self._read(r)
-            if hb is None:
+            step = self._read(r)
+            if step is None:
                 continue
-            step, ts = hb
-            if step < self._my_step and now - ts > self.timeout_s:
+            seen = self._seen.get(r)
+            if seen is None or seen[0] != step:
+                self._seen[r] = seen = (step, now)
+            if now - seen[1] <= self.timeout_s:
+                continue
+            if step < self._my_step or (step == self._my_step and now - self._my_beat_at > self.timeout_s):
                 stale.append(r)
         return stale
 

@@ -22,20 +22,39 @@ class FakeStore(dict):
 def test_watchdog_flags_a_rank_that_stopped_beating():
     from picotron_b200.runtime.watchdog import StepWatchdog
     store = FakeStore()
-    seen = []
     a = StepWatchdog(store, rank=0, world_size=1, timeout_s=0.2)          # no thread for world 1
     a.world_size = 3
-    a.on_failure = seen.append
-    now = time.time()
-    store.set("pico_hb/1", f"5:{now}")            # rank 1 keeps up
-    store.set("pico_hb/2", f"2:{now - 10}")       # rank 2 fell behind long ago
+    t0 = 1000.0                                   # the reader's own (monotonic) clock
+    store.set("pico_hb/1", "5")                   # rank 1 keeps up
+    store.set("pico_hb/2", "2")                   # rank 2 is behind
     a.beat(5)
-    assert a.check_once(now) == [2]
-    store.set("pico_hb/2", f"5:{now}")            # it recovers
-    assert a.check_once(now) == []
-    store.set("pico_hb/2", f"1:{now - 10}")
-    a._my_step = 1                                # not behind us: slow start, not a failure
-    assert a.check_once(now) == []
+    assert a.check_once(t0) == []                 # first sighting: nobody is stale yet
+    store.set("pico_hb/1", "6")
+    assert a.check_once(t0 + 10) == [2]           # rank 2 has not moved for longer than the timeout
+    store.set("pico_hb/2", "6")                   # it recovers
+    assert a.check_once(t0 + 10.1) == []
+    a._my_step = 1                                # peers that are ahead of us are never failures
+    assert a.check_once(t0 + 30) == []
+
+
+def test_watchdog_flags_a_job_stuck_inside_one_step():
+    """One rank hangs inside a step and the others block in its collectives: every heartbeat carries
+    the same step number. A rank whose own last beat is as old as its peers' flags them all."""
+    from picotron_b200.runtime.watchdog import StepWatchdog
+    store = FakeStore()
+    a = StepWatchdog(store, rank=0, world_size=1, timeout_s=0.2)
+    a.world_size = 3
+    store.set("pico_hb/1", "7")
+    store.set("pico_hb/2", "7")
+    a.beat(7)
+    t0 = 2000.0
+    a._my_beat_at = t0
+    assert a.check_once(t0) == []
+    assert a.check_once(t0 + 0.1) == []           # everyone in step 7, but not for long yet
+    assert a.check_once(t0 + 10) == [1, 2]        # nobody, this rank included, has moved since
+    a.beat(8)                                     # this rank did make progress: peers in step 7 are behind
+    a._my_beat_at = t0 + 10
+    assert a.check_once(t0 + 10.05) == [1, 2]
 
 
 def _stalled_rank_worker(rank, world):

@@ -166,6 +166,14 @@ def _engine_worker(rank, world):
     for a, b in zip(losses["1"], losses["0"]):
         assert abs(a - b) < 3e-2, losses
     assert losses["1"][-1] < losses["1"][0]
+    # the fused path replays its micro-batch from a CUDA graph (flag epochs advance on the device);
+    # eager launches of the same kernels must give the same bits
+    os.environ["PICO_FUSED_TP"] = "1"
+    cfg["training"]["cuda_graph"] = False
+    eng = TrainEngine(cfg, device=torch.device("cuda", rank))
+    eager = [eng.train_step().item() for _ in range(3)]
+    ops.check_status("engine eager")
+    assert eager == losses["1"], (eager, losses["1"])
 
 
 def test_engine_fused_tp_matches_nccl_path_2gpu():

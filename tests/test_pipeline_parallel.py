@@ -81,6 +81,52 @@ def test_pp4(engine):
     run_distributed(_pp_worker, 4, engine, 8)
 
 
+def _pp_dp_worker(rank, world, engine, dp_cls_name):
+    """pp=2 x dp=2 on the hook-based data-parallel wrappers: every chunk's gradients must come out
+    averaged over the two replicas (each replica sees different micro-batches), i.e. equal to the
+    full model's gradient over all micro-batches of both replicas divided by 2."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.parallel import data_parallel as dp_mod
+    from picotron_b200.parallel.pipeline_parallel import run_schedule, wrap_pipeline
+
+    pgm.setup_process_group_manager(tp_size=1, cp_size=1, pp_size=2, dp_size=2)
+    m_pg = pgm.get_pgm()
+    cfg = tiny_config()
+    m = 4
+    torch.manual_seed(11)
+    ref = Llama(cfg)
+    for replica in range(2):
+        loader = FakeDataLoader(cfg.vocab_size, 2, 8, m, seed=100 + replica)
+        for _ in range(m):
+            b = next(loader)
+            loss = torch.nn.functional.cross_entropy(ref(b["input_ids"]).view(-1, cfg.vocab_size),
+                                                     b["target_ids"].view(-1)) / (m * 2)
+            loss.backward()
+    ref_grads = {n: p.grad.clone() for n, p in ref.named_parameters()}
+
+    torch.manual_seed(11)
+    full = Llama(cfg)
+    full.load_state_dict(ref.state_dict())
+    stage = wrap_pipeline(full, cfg, engine, 2)
+    model = getattr(dp_mod, dp_cls_name)(stage, group=m_pg.cp_dp_group)
+    loader = FakeDataLoader(cfg.vocab_size, 2, 8, m, seed=100 + m_pg.dp_rank)
+    run_schedule(engine, model, loader, (2, 8, cfg.hidden_size), torch.device("cpu"), torch.float32)
+    n_checked = 0
+    for n, p in stage.named_parameters():
+        assert p.grad is not None, (engine, n)
+        err = (p.grad - ref_grads[n]).abs().max().item()
+        assert err < 1e-5, (engine, dp_cls_name, n, err)
+        n_checked += 1
+    assert n_checked > 0
+
+
+@pytest.mark.parametrize("dp_cls", ["DataParallelNaive", "DataParallelBucket"])
+@pytest.mark.parametrize("engine", ["interleaved", "1f1b"])
+def test_pp2_dp2_every_chunk_is_reduced(engine, dp_cls):
+    run_distributed(_pp_dp_worker, 4, engine, dp_cls)
+
+
 def test_planner_places_every_action_once():
     from picotron_b200.parallel import pp_schedules as S
     for engine in S.SCHEDULES:

@@ -169,6 +169,71 @@ def test_checkpoint_resume_reproduces_next_loss(tmp_path):
     run_distributed(_ckpt_worker, 2, str(tmp_path))
 
 
+def _ckpt_cp_zero_worker(rank, world, tmp):
+    """cp=2 with ZeRO-1: the optimizer is sharded over the context-parallel ranks, so each of them
+    owns different Adam state; a resume must restore every rank's own shard bit for bit."""
+    from picotron_b200.checkpoint import CheckpointManager
+    from picotron_b200.engine import TrainEngine
+    dist_kw = dict(cp_size=2, zero_stage=1, cp_attention="ring")
+    engine = TrainEngine(tiny_cfg(**dist_kw), device=torch.device("cpu"))
+    assert engine.optimizer_is_sharded
+    for _ in range(2):
+        engine.train_step()
+    ckpt = CheckpointManager()
+    out = os.path.join(tmp, "2")
+    ckpt.save_checkpoint(engine.model, engine.optimizer, engine.trained_steps, engine.trained_tokens, out,
+                         data_loader=engine.data_loader, sharded_optimizer=True)
+    saved_state = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in _flat_state(engine.optimizer).items()}
+    want = [engine.average_loss(engine.train_step()) for _ in range(2)]
+    engine2 = TrainEngine(tiny_cfg(**dist_kw), device=torch.device("cpu"))
+    ckpt.load_checkpoint(engine2.model, engine2.optimizer, out, data_loader=engine2.data_loader,
+                         sharded_optimizer=True)
+    engine2.trained_steps, engine2.trained_tokens = 2, 2 * engine.tokens_per_step
+    got_state = _flat_state(engine2.optimizer)
+    assert saved_state.keys() == got_state.keys() and len(saved_state) > 0
+    for k in saved_state:
+        a, b = saved_state[k], got_state[k]
+        assert torch.equal(a, b) if torch.is_tensor(a) else a == b, (rank, k)
+    got = [engine2.average_loss(engine2.train_step()) for _ in range(2)]
+    assert got == want, (got, want)
+    dist.barrier()
+    if rank == 0:
+        names = sorted(os.listdir(out))
+        manifest = json.load(open(os.path.join(out, "manifest.json")))
+        for cp in range(2):
+            n = f"optimizer_dp_rank=0_1_cp_rank={cp}_2_tp_rank_world_size=0_1_pp_rank_world_size=0_1.pth"
+            assert n in names and n in manifest["files"], names
+        # a missing shard makes the checkpoint incomplete
+        os.remove(os.path.join(out, "optimizer_dp_rank=0_1_cp_rank=1_2_tp_rank_world_size=0_1_pp_rank_world_size=0_1.pth"))
+    dist.barrier()
+    try:
+        ckpt.load_checkpoint(engine2.model, engine2.optimizer, out, sharded_optimizer=True)
+        raise AssertionError("a checkpoint with a missing optimizer shard was accepted")
+    except FileNotFoundError:
+        pass
+
+
+def _flat_state(optimizer):
+    """{name: tensor or number} of every entry of an optimizer state dict, nested dicts flattened."""
+    out = {}
+
+    def walk(prefix, obj):
+        if isinstance(obj, dict):
+            for k, v in obj.items():
+                walk(f"{prefix}.{k}", v)
+        elif isinstance(obj, (list, tuple)):
+            for i, v in enumerate(obj):
+                walk(f"{prefix}[{i}]", v)
+        elif torch.is_tensor(obj) or isinstance(obj, (int, float)):
+            out[prefix] = obj
+    walk("", optimizer.state_dict())
+    return out
+
+
+def test_checkpoint_resume_cp2_zero1_restores_every_shard(tmp_path):
+    run_distributed(_ckpt_cp_zero_worker, 2, str(tmp_path))
+
+
 def test_create_config_and_train_cli(tmp_path):
     out = subprocess.run([sys.executable, os.path.join(REPO, "create_config.py"), "--out_dir", str(tmp_path),
                           "--exp_name", "cli", "--model_name", "tiny-llama-test", "--use_cpu", "--dataset", "synthetic",

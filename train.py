@@ -22,6 +22,7 @@ from picotron_b200 import process_group_manager as pgm
 from picotron_b200.checkpoint import CheckpointManager
 from picotron_b200.config import load_config, world_size_of
 from picotron_b200.engine import TrainEngine
+from picotron_b200.runtime.status import raise_if_failed
 from picotron_b200.runtime.watchdog import StepWatchdog
 from picotron_b200.utils import (get_mfu, get_num_params, measured_peak_flops, print, set_all_seed,
                                  to_readable_format)
@@ -74,6 +75,10 @@ def main():
                                              sharded_optimizer=engine.optimizer_is_sharded)
         engine.trained_steps, engine.trained_tokens = steps, tokens
     metrics_path = cfg["logging"].get("metrics_jsonl")
+    if cfg["logging"].get("step_breakdown") and metrics_path:
+        # per-step device time of forward+backward / optimizer sections, MAX over ranks, in the JSONL
+        from picotron_b200.runtime.timing import EventTimer
+        engine.timer = EventTimer(device)
     watchdog = StepWatchdog.from_env(rank, world)
     prof = None
     if args.profile > 0:
@@ -93,11 +98,17 @@ def main():
         if device.type == "cuda":
             end.record()
             end.synchronize()
+            # a kernel that gave up a bounded wait (peer flag, mbarrier) or overflowed a dropless
+            # expert buffer only records that and returns: stop here, before the state it left
+            # behind is trained on or written to a checkpoint (the device is already idle, so this
+            # costs one small read)
+            raise_if_failed(f"train step {engine.trained_steps}")
             step_ms = torch.tensor([start.elapsed_time(end)], device=device)
         else:
             step_ms = torch.tensor([(time.perf_counter() - t0) * 1e3])
         dist.all_reduce(step_ms, op=dist.ReduceOp.MAX)
         loss = engine.average_loss(loss_t)
+        sections = engine.timer.collect() if engine.timer is not None else None
         step = engine.trained_steps
         watchdog.beat(step)
         step_s = float(step_ms.item()) / 1e3
@@ -122,7 +133,7 @@ def main():
                                                                   num_layers=model_cfg.num_hidden_layers,
                                                                   hidden_size=model_cfg.hidden_size,
                                                                   seq_len=t["seq_length"]),
-                                     "memory_gb": mem}) + "\n")
+                                     "memory_gb": mem, **({"sections_ms": sections} if sections else {})}) + "\n")
         if wandb is not None:
             wandb.log({"loss": loss, "tokens_per_step": engine.tokens_per_step, "tokens_per_second": tok_s,
                        "mfu": mfu, "tokens_per_second_per_gpu": tok_s_gpu, "memory_usage": mem,
@@ -130,6 +141,8 @@ def main():
         if prof is not None:
             prof.step()
         if step % cfg["checkpoint"]["save_frequency"] == 0:
+            if device.type == "cuda":
+                raise_if_failed("before saving a checkpoint")
             ckpt.save_checkpoint(engine.model, engine.optimizer, step, engine.trained_tokens,
                                  os.path.join(cfg["checkpoint"]["save_dir"], str(step)),
                                  data_loader=engine.data_loader, sharded_optimizer=engine.optimizer_is_sharded)
@@ -140,6 +153,7 @@ def main():
     if wandb is not None:
         wandb.finish()
     watchdog.stop()
+    engine.close()
     dist.destroy_process_group()
 
 
