@@ -67,8 +67,23 @@ def main():
             engine.train_step()
             torch.cuda.synchronize()
         if local == 0:
-            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=28, max_name_column_width=70),
+            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70),
                   flush=True)
+            # busy time (union of kernel intervals) against the span from first to last kernel
+            iv = sorted((ev.time_range.start, ev.time_range.end) for ev in prof.events()
+                        if ev.device_type == torch.autograd.DeviceType.CUDA)
+            if iv:
+                busy, cur_s, cur_e = 0.0, iv[0][0], iv[0][1]
+                for a, b in iv[1:]:
+                    if a > cur_e:
+                        busy += cur_e - cur_s
+                        cur_s, cur_e = a, b
+                    else:
+                        cur_e = max(cur_e, b)
+                busy += cur_e - cur_s
+                span = iv[-1][1] - iv[0][0]
+                print(f"device busy {busy / 1e3:.1f} ms of a {span / 1e3:.1f} ms span "
+                      f"({100.0 * busy / span:.1f} %), {len(iv)} kernels/copies", flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -237,25 +237,13 @@ void epoch_base_add(int64_t local_flags, const std::vector<int64_t>& slots, cons
 
 void push_rows(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs,
                const std::vector<int64_t>& flag_ptrs, int64_t world, int64_t my_rank, int64_t rows,
-               int64_t cols, int64_t slot, int64_t epoch) {
+               int64_t cols, int64_t slot, int64_t epoch, int64_t skip_self, int64_t piece_rows) {
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kBFloat16, "push_rows: contiguous bf16");
   check(pico_push_rows(src.data_ptr(), table_of(dst_ptrs), table_of(flag_ptrs), (int)world, (int)my_rank,
-                       (int)rows, (int)cols, (int)slot, (uint32_t)epoch, stream_of(src)),
+                       (int)rows, (int)cols, (int)piece_rows, (int)slot, (uint32_t)epoch, (int)skip_self,
+                       stream_of(src)),
         "push_rows");
-}
-
-void rmsnorm_fwd_push(const at::Tensor& x, const c10::optional<at::Tensor>& residual, const at::Tensor& w,
-                      const c10::optional<at::Tensor>& y_local, const c10::optional<at::Tensor>& h_out,
-                      const c10::optional<at::Tensor>& rstd, const std::vector<int64_t>& dst_ptrs,
-                      const std::vector<int64_t>& flag_ptrs, int64_t world, int64_t my_rank, int64_t rows,
-                      int64_t H, double eps, int64_t slot, int64_t epoch) {
-  c10::cuda::CUDAGuard guard(x.device());
-  check(pico_rmsnorm_fwd_push(x.data_ptr(), cptr(residual), w.data_ptr(), mptr(y_local), mptr(h_out),
-                              (float*)mptr(rstd), table_of(dst_ptrs), table_of(flag_ptrs), (int)world,
-                              (int)my_rank, (int)rows, (int)H, (float)eps, (int)slot, (uint32_t)epoch,
-                              stream_of(x)),
-        "rmsnorm_fwd_push");
 }
 
 void slot_sum(const at::Tensor& staging, int64_t world, int64_t rows, int64_t cols,
@@ -281,12 +269,13 @@ void slot_sum_from(const at::Tensor& staging, int64_t world, int64_t first_slot,
 
 void scatter_rows(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs,
                   const std::vector<int64_t>& flag_ptrs, int64_t world, int64_t my_rank, int64_t num_dst,
-                  int64_t rows, int64_t cols, int64_t slot, int64_t epoch) {
+                  int64_t rows, int64_t cols, int64_t slot, int64_t epoch, int64_t piece_rows) {
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kBFloat16, "scatter_rows: contiguous bf16");
   TORCH_CHECK(src.numel() >= num_dst * rows * cols, "scatter_rows: source too small");
   check(pico_scatter_rows(src.data_ptr(), table_of(dst_ptrs), table_of(flag_ptrs), (int)world, (int)my_rank,
-                          (int)num_dst, (int)rows, (int)cols, (int)slot, (uint32_t)epoch, stream_of(src)),
+                          (int)num_dst, (int)rows, (int)cols, (int)piece_rows, (int)slot, (uint32_t)epoch,
+                          stream_of(src)),
         "scatter_rows");
 }
 
@@ -456,21 +445,21 @@ void ep_block_exchange(const at::Tensor& src, const std::vector<int64_t>& dst_pt
 void gemm_ex(const at::Tensor& A, const at::Tensor& B, const c10::optional<at::Tensor>& D, int64_t M,
              int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldd, bool a_mn_major, bool b_mn_major,
              int64_t out_mode, int64_t max_ctas, int64_t a_flags, int64_t a_slot, int64_t a_epoch,
-             int64_t a_rows_per_block, int64_t a_skip_block, const std::vector<int64_t>& d_ptrs,
-             int64_t d_rows_per_block, int64_t m_rotate_rows, int64_t timeout_ms) {
+             int64_t a_skip_block, const std::vector<int64_t>& d_ptrs, int64_t blk_rows, int64_t num_blocks,
+             int64_t first_block, int64_t timeout_ms) {
   c10::cuda::CUDAGuard guard(A.device());
   PicoGemmComm c;
   memset(&c, 0, sizeof(c));
   c.a_flags = reinterpret_cast<const unsigned int*>(a_flags);
   c.a_slot = (int)a_slot;
   c.a_epoch = (unsigned int)a_epoch;
-  c.a_rows_per_block = (int)a_rows_per_block;
   c.a_skip_block = (int)a_skip_block;
   c.d_num_dest = (int)d_ptrs.size();
-  c.d_rows_per_block = (int)d_rows_per_block;
   TORCH_CHECK(d_ptrs.size() <= 8, "gemm_ex: at most 8 destinations");
   for (size_t i = 0; i < d_ptrs.size(); ++i) c.d_ptrs[i] = reinterpret_cast<void*>(d_ptrs[i]);
-  c.m_rotate_rows = (int)m_rotate_rows;
+  c.blk_rows = (int)blk_rows;
+  c.num_blocks = (int)num_blocks;
+  c.first_block = (int)first_block;
   c.timeout_ms = (unsigned int)timeout_ms;
   void* dptr = D.has_value() && D->defined() ? D->data_ptr() : nullptr;
   TORCH_CHECK(dptr != nullptr || !d_ptrs.empty(), "gemm_ex: no output");
@@ -608,7 +597,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wait_flags", &wait_flags);
   m.def("epoch_base_add", &epoch_base_add);
   m.def("push_rows", &push_rows);
-  m.def("rmsnorm_fwd_push", &rmsnorm_fwd_push);
   m.def("slot_sum", &slot_sum);
   m.def("slot_sum_from", &slot_sum_from);
   m.def("scatter_rows", &scatter_rows);

@@ -9,84 +9,40 @@
 namespace pico {
 
 __global__ void push_rows_kernel(const uint4* __restrict__ src, PicoPeerTable dst, PicoPeerTable flags,
-                                 int world, int my_rank, int64_t nvec, int slot, uint32_t epoch,
-                                 unsigned int* counter) {
-  const int64_t base = (int64_t)my_rank * nvec;
+                                 int world, int my_rank, int64_t nvec, int64_t nvec_piece, int slot,
+                                 uint32_t epoch, unsigned int* counter, int skip_self) {
+  // piece p of the source (nvec_piece vectors) is piece p * world + my_rank of the destination
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
        i += (int64_t)gridDim.x * blockDim.x) {
     const uint4 v = src[i];
-    for (int r = 0; r < world; ++r) reinterpret_cast<uint4*>(dst.ptr[r])[base + i] = v;
+    const int64_t p = i / nvec_piece;
+    const int64_t o = (p * world + my_rank) * nvec_piece + (i - p * nvec_piece);
+    if (skip_self == 2) {
+      reinterpret_cast<uint4*>(dst.ptr[my_rank])[o] = v;
+    } else {
+      for (int r = 0; r < world; ++r)
+        if (!(skip_self && r == my_rank)) reinterpret_cast<uint4*>(dst.ptr[r])[o] = v;
+    }
   }
-  raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
+  if (skip_self != 2) raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
 }
 
 // Block o of src goes into slot `my_rank` of rank o's staging buffer, for o < num_dst; the flag is
 // raised on every rank of the group (also on those that received nothing), so all ranks stay in
 // step with the epoch protocol.
 __global__ void scatter_rows_kernel(const uint4* __restrict__ src, PicoPeerTable dst, PicoPeerTable flags,
-                                    int world, int my_rank, int num_dst, int64_t nvec_block, int slot,
-                                    uint32_t epoch, unsigned int* counter) {
+                                    int world, int my_rank, int num_dst, int64_t nvec_block, int64_t nvec_piece,
+                                    int slot, uint32_t epoch, unsigned int* counter) {
+  // the source is a sequence of pieces (nvec_piece vectors); piece p goes to destination
+  // p % num_dst as that destination's (p / num_dst)-th piece
   const int64_t total = (int64_t)num_dst * nvec_block;
   const int64_t base = (int64_t)my_rank * nvec_block;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int o = (int)(i / nvec_block);
-    const int64_t j = i - (int64_t)o * nvec_block;
+    const int64_t p = i / nvec_piece;
+    const int o = (int)(p % num_dst);
+    const int64_t j = (p / num_dst) * nvec_piece + (i - p * nvec_piece);
     reinterpret_cast<uint4*>(dst.ptr[o])[base + j] = src[i];
-  }
-  raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
-}
-
-template <int NV>
-__global__ void __launch_bounds__(kNormThreads)
-rmsnorm_fwd_push_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
-                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y_local,
-                        __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out,
-                        PicoPeerTable dst, PicoPeerTable flags, int world, int my_rank, int rows, int H,
-                        float eps, int slot, uint32_t epoch, unsigned int* counter) {
-  __shared__ float red[kNormThreads / 32];
-  const int nvec = H / 8;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
-    const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + (size_t)row * H) : nullptr;
-    float vals[NV][8];
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int v = threadIdx.x + i * kNormThreads;
-      if (v < nvec) {
-        unpack8(xr[v], vals[i]);
-        if (rr) {
-          float r[8];
-          unpack8(rr[v], r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
-          uint4 hv = pack8(vals[i]);
-          unpack8(hv, vals[i]);
-          if (h_out) reinterpret_cast<uint4*>(h_out + (size_t)row * H)[v] = hv;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
-      }
-    }
-    ss = block_sum(ss, red);
-    const float rstd = rsqrtf(ss / (float)H + eps);
-    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
-    const size_t grow = (size_t)my_rank * rows + row;  // row in the gathered tensor
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int v = threadIdx.x + i * kNormThreads;
-      if (v < nvec) {
-        float wv[8], o[8];
-        unpack8(reinterpret_cast<const uint4*>(w)[v], wv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wv[j];
-        const uint4 packed = pack8(o);
-        if (y_local) reinterpret_cast<uint4*>(y_local + (size_t)row * H)[v] = packed;
-        for (int r = 0; r < world; ++r)
-          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.ptr[r]) + grow * H)[v] = packed;
-      }
-    }
   }
   raise_flags_when_grid_done(counter, flags, world, my_rank, slot, epoch);
 }
@@ -146,12 +102,13 @@ static int check_world(const char* what, int world, int slot) {
 }
 
 extern "C" int pico_push_rows(const void* src, PicoPeerTable dst, PicoPeerTable flags, int world,
-                              int my_rank, int rows, int cols, int slot, uint32_t epoch,
-                              cudaStream_t stream) {
+                              int my_rank, int rows, int cols, int piece_rows, int slot, uint32_t epoch,
+                              int skip_self, cudaStream_t stream) {
   if (int rc = check_world("push_rows", world, slot)) return rc;
   const int64_t n = (int64_t)rows * cols;
-  if (n % 8 != 0) {
-    pico_host::set_error("push_rows: rows*cols must be a multiple of 8");
+  if (piece_rows <= 0) piece_rows = rows;
+  if (n % 8 != 0 || rows % piece_rows != 0 || ((int64_t)piece_rows * cols) % 8 != 0) {
+    pico_host::set_error("push_rows: rows*cols and piece_rows*cols must be multiples of 8, rows a multiple of piece_rows");
     return -2;
   }
   unsigned int* counter = grid_counter();
@@ -161,39 +118,10 @@ extern "C" int pico_push_rows(const void* src, PicoPeerTable dst, PicoPeerTable 
   const int cap = pico_host::num_sms() * 4;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
-  push_rows_kernel<<<grid, 256, 0, stream>>>((const uint4*)src, dst, flags, world, my_rank, nvec, slot,
-                                             epoch, counter);
+  push_rows_kernel<<<grid, 256, 0, stream>>>((const uint4*)src, dst, flags, world, my_rank, nvec,
+                                             (int64_t)piece_rows * cols / 8, slot, epoch, counter, skip_self);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) pico_host::set_error("push_rows: %s", cudaGetErrorString(e));
-  return (int)e;
-}
-
-extern "C" int pico_rmsnorm_fwd_push(const void* x, const void* residual, const void* w, void* y_local,
-                                     void* h_out, float* rstd, PicoPeerTable dst, PicoPeerTable flags,
-                                     int world, int my_rank, int rows, int H, float eps, int slot,
-                                     uint32_t epoch, cudaStream_t stream) {
-  if (int rc = check_world("rmsnorm_fwd_push", world, slot)) return rc;
-  if (H % 8 != 0 || H > kNormThreads * 8 * 4) {
-    pico_host::set_error("rmsnorm_fwd_push: hidden size %d must be a multiple of 8 and <= %d", H,
-                         kNormThreads * 8 * 4);
-    return -2;
-  }
-  unsigned int* counter = grid_counter();
-  if (!counter) return -1;
-  const int cap = pico_host::num_sms() * 8;
-  const int grid = rows < cap ? rows : cap;
-  const int need = (H / 8 + kNormThreads - 1) / kNormThreads;
-#define PICO_LAUNCH(NV)                                                                            \
-  rmsnorm_fwd_push_kernel<NV><<<grid, kNormThreads, 0, stream>>>(                                  \
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,            \
-      (__nv_bfloat16*)y_local, (__nv_bfloat16*)h_out, rstd, dst, flags, world, my_rank, rows, H,  \
-      eps, slot, epoch, counter + 1)
-  if (need <= 1) PICO_LAUNCH(1);
-  else if (need <= 2) PICO_LAUNCH(2);
-  else PICO_LAUNCH(4);
-#undef PICO_LAUNCH
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) pico_host::set_error("rmsnorm_fwd_push: %s", cudaGetErrorString(e));
   return (int)e;
 }
 
@@ -205,12 +133,15 @@ extern "C" int pico_slot_sum(const void* staging, int world, int rows, int cols,
 }
 
 extern "C" int pico_scatter_rows(const void* src, PicoPeerTable dst, PicoPeerTable flags, int world,
-                                 int my_rank, int num_dst, int rows, int cols, int slot, uint32_t epoch,
-                                 cudaStream_t stream) {
+                                 int my_rank, int num_dst, int rows, int cols, int piece_rows, int slot,
+                                 uint32_t epoch, cudaStream_t stream) {
   if (int rc = check_world("scatter_rows", world, slot)) return rc;
   const int64_t n = (int64_t)rows * cols;
-  if (n % 8 != 0 || num_dst < 0 || num_dst > world) {
-    pico_host::set_error("scatter_rows: rows*cols must be a multiple of 8 and 0 <= num_dst <= world");
+  if (piece_rows <= 0) piece_rows = rows;
+  if (n % 8 != 0 || num_dst < 0 || num_dst > world || rows % piece_rows != 0 ||
+      ((int64_t)piece_rows * cols) % 8 != 0) {
+    pico_host::set_error("scatter_rows: rows*cols and piece_rows*cols must be multiples of 8, rows a multiple of "
+                         "piece_rows, 0 <= num_dst <= world");
     return -2;
   }
   unsigned int* counter = grid_counter();
@@ -221,7 +152,7 @@ extern "C" int pico_scatter_rows(const void* src, PicoPeerTable dst, PicoPeerTab
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   scatter_rows_kernel<<<grid, 256, 0, stream>>>((const uint4*)src, dst, flags, world, my_rank, num_dst, nvec,
-                                                slot, epoch, counter + 2);
+                                                (int64_t)piece_rows * cols / 8, slot, epoch, counter + 2);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) pico_host::set_error("scatter_rows: %s", cudaGetErrorString(e));
   return (int)e;

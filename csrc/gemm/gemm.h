@@ -18,24 +18,28 @@ int pico_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, i
                    cudaStream_t stream);
 
 // Collective fusion (see csrc/runtime/symm.h for the symmetric-memory model).
-//   all-gather -> GEMM : A (K-major) is this GPU's gather buffer; row block b (a_rows_per_block
-//     rows) is written by rank b and announced by flag [a_slot][b] >= a_epoch in a_flags (local
-//     flag buffer). The kernel starts on block a_skip_block (this rank's own rows) and loads the
+//   Row geometry: the M rows are pieces of blk_rows rows (a multiple of 128); piece p belongs to
+//   block p % num_blocks and is that block's (p / num_blocks)-th piece. One piece per block is the
+//   plain split "rank r owns rows [r*M/n, (r+1)*M/n)"; several pieces per block describe a
+//   [batch, sequence] tensor whose sequence dimension is split over the ranks (blk_rows = sequence
+//   length per rank), which is how the sequence-parallel layers use it.
+//   all-gather -> GEMM : A (K-major) is this GPU's gather buffer; block b was written by rank b and
+//     is announced by flag [a_slot][b] >= a_epoch in a_flags (local flag buffer). The kernel visits
+//     block first_block first (this rank's own rows, a_skip_block: never waited for) and loads the
 //     other blocks as their flags arrive, so the transfer overlaps the math tile by tile.
-//   GEMM -> reduce-scatter : output row block b (d_rows_per_block rows) is stored through
-//     d_ptrs[b] — the slot reserved for this rank in rank b's staging buffer — instead of D;
-//     the owner sums the slots afterwards (pico_slot_sum / pico_slot_sum_add_rmsnorm).
-//   m_rotate_rows shifts the order in which row blocks are visited.
+//   GEMM -> reduce-scatter : the rows of block b are stored through d_ptrs[b] — the slot reserved
+//     for this rank in rank b's staging buffer ([M / num_blocks, N], pieces in order) — instead of
+//     D; the owner sums the slots afterwards (pico_slot_sum).
 typedef struct {
   const unsigned int* a_flags;
   int a_slot;
   unsigned int a_epoch;
-  int a_rows_per_block;
   int a_skip_block;
   int d_num_dest;
-  int d_rows_per_block;
   void* d_ptrs[8];
-  int m_rotate_rows;
+  int blk_rows;
+  int num_blocks;
+  int first_block;
   unsigned int timeout_ms;
   // Grouped GEMM for the experts of a mixture-of-experts layer: one launch covers every local
   // expert. Rows of the activation matrices are expert-contiguous and every expert's segment

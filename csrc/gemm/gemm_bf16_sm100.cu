@@ -67,13 +67,15 @@ struct GemmComm {
   const uint32_t* a_flags;
   int a_slot;
   uint32_t a_epoch;
-  int a_rows_per_block;
   int a_skip_block;       // this rank's own block: already in place, never waited for
-  // GEMM -> reduce-scatter: output row block b goes through DMaps::m[b]
-  int d_rows_per_block;
-  // both: logical m-tile t maps to physical m-tile (t + m_rotate) % num_m, so a rank starts
-  // with its own block (gather) or with its neighbour's (scatter)
-  int m_rotate;
+  // Row geometry shared by both fusions: the M rows are `pieces` of blk_rows rows; piece p belongs
+  // to block p % num_blocks (the rank that wrote it / that receives it) and is the (p / num_blocks)-th
+  // piece of that block. One piece per block is the plain "rank r owns rows [r*m, (r+1)*m)" split;
+  // several pieces per block is a [batch, sequence] tensor whose sequence is split over the ranks.
+  int blk_rows;           // 0 = no collective fusion
+  int num_blocks;
+  int first_block;        // tile order starts with this block (own rows / the neighbour's rows)
+  int scatter;            // GEMM -> reduce-scatter: rows of block b are stored through DMaps::m[b]
   unsigned long long timeout_ns;
   // grouped GEMM (experts of a mixture-of-experts layer), see PicoGemmGroups in gemm.h
   const int* tile_group;  // row-grouped mode: group of every 128-row tile of A / D (-1 = skip)
@@ -96,7 +98,7 @@ struct TileWork {
 
 // Grouped rasterisation: consecutive tile indices (= CTAs running at the same time) cover a
 // compact block of the output so A and B slices are shared through L2.
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int m_rotate = 0) {
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) {
   constexpr int kGroup = 16;
   int tiles_per_group = kGroup * num_n;
   int g = tile / tiles_per_group;
@@ -105,12 +107,23 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
   int r = tile - g * tiles_per_group;
   TileCoord c;
   c.m = first_m + r % gsize;
-  if (m_rotate) {
-    c.m += m_rotate;
-    if (c.m >= num_m) c.m -= num_m;
-  }
   c.n = r / gsize;
   return c;
+}
+
+// Order in which the m-tiles of a collective-fused GEMM are visited: all pieces of block
+// first_block, then those of first_block + 1, ... (wrapping), so the rows that are available
+// first (or wanted first by a peer) are computed first. lm: logical m-tile index.
+__device__ __forceinline__ int block_first_m(int lm, int num_m, const GemmComm& comm) {
+  const int tpp = comm.blk_rows / BM;                       // tiles per piece
+  const int per_block = num_m / comm.num_blocks;            // tiles per block (all its pieces)
+  const int o = lm / per_block;
+  const int rem = lm - o * per_block;
+  const int piece_of_block = rem / tpp;
+  const int j = rem - piece_of_block * tpp;
+  int blk = comm.first_block + o;
+  if (blk >= comm.num_blocks) blk -= comm.num_blocks;
+  return (piece_of_block * comm.num_blocks + blk) * tpp + j;
 }
 
 __device__ __forceinline__ TileWork tile_work(int tile, int num_m, int num_n, int num_kb,
@@ -131,8 +144,8 @@ __device__ __forceinline__ TileWork tile_work(int tile, int num_m, int num_n, in
     w.skip = w.kb1 <= w.kb0;
     return w;
   }
-  TileCoord c = tile_coord(tile, num_m, num_n, comm.m_rotate);
-  w.m = c.m;
+  TileCoord c = tile_coord(tile, num_m, num_n);
+  w.m = comm.blk_rows > 0 ? block_first_m(c.m, num_m, comm) : c.m;
   w.n = c.n;
   if (comm.tile_group != nullptr) {
     w.grp = __ldg(comm.tile_group + c.m);
@@ -205,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // row-grouped mode: this tile's B is group grp's block of the stacked matrix
         const int b_off = comm.tile_group != nullptr ? tw.grp * comm.b_group_rows : 0;
         if (comm.a_flags != nullptr) {
-          const int blk = m0 / comm.a_rows_per_block;
+          const int blk = (m0 / comm.blk_rows) % comm.num_blocks;
           if (blk != comm.a_skip_block && !((ready_blocks >> blk) & 1u)) {
             if (!wait_flag_ge(comm.a_flags + comm.a_slot * PICO_MAX_PEERS + blk,
                               epoch_base(comm.a_flags, comm.a_slot) + comm.a_epoch, comm.timeout_ns, status,
@@ -312,10 +325,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (comm.seg_start != nullptr) m0 += tw.grp * M;   // groups are stacked along the rows of D
       const int n0 = tw.n * BN;
       const CUtensorMap* tmap_d = &dmaps.m[0];
-      if (comm.d_rows_per_block > 0) {
-        const int dest = m0 / comm.d_rows_per_block;
+      if (comm.scatter) {
+        const int piece = m0 / comm.blk_rows;
+        const int dest = piece % comm.num_blocks;
         tmap_d = &dmaps.m[dest];
-        m0 -= dest * comm.d_rows_per_block;
+        m0 = (piece / comm.num_blocks) * comm.blk_rows + (m0 - piece * comm.blk_rows);
       }
       bool ok = mbar_wait(&tmem_full[acc], acc_phase, abort_word, status, 400 + acc);
       // uniform decision for the four epilogue warps (they share named barriers below)
@@ -452,20 +466,28 @@ static int launch(const void* A, const void* B, void* D, int M, int N, int K, in
     rc = pico_host::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, b_rows_total, (uint64_t)ldb * 2,
                                  64, 64, Swizzle::B128);
   if (rc) return rc;
-  const int num_dest = (pc && pc->d_num_dest > 0) ? pc->d_num_dest : 1;
-  const int d_rows = (pc && pc->d_num_dest > 0) ? pc->d_rows_per_block : (red_grouped ? pc->num_groups * M : M);
+  const bool scatter = pc && pc->d_num_dest > 0;
+  const bool gather = pc && pc->a_flags != nullptr;
+  const int num_dest = scatter ? pc->d_num_dest : 1;
   if (num_dest > PICO_MAX_PEERS) {
     pico_host::set_error("gemm: %d destinations exceed the maximum of %d", num_dest, PICO_MAX_PEERS);
     return -2;
   }
-  if (pc && pc->d_num_dest > 0) {
-    if (A_MN != 0 || d_rows % BM != 0 || d_rows * num_dest != M) {
-      pico_host::set_error("gemm->scatter: need K-major A and M (%d) = %d destinations x a multiple of %d rows",
-                           M, num_dest, BM);
+  if (scatter || gather) {
+    const int nb = pc->num_blocks;
+    if (A_MN != 0 || pc->blk_rows <= 0 || pc->blk_rows % BM != 0 || nb < 1 || nb > PICO_MAX_PEERS ||
+        M % (pc->blk_rows * nb) != 0 || (scatter && nb != num_dest) || (scatter && gather) ||
+        pc->first_block < 0 || pc->first_block >= nb) {
+      pico_host::set_error("collective gemm: need K-major A, pieces of a multiple of %d rows, M (%d) = pieces x "
+                           "blocks (%d) x %d rows, and one direction per launch", BM, M, nb, pc->blk_rows);
       return -2;
     }
-    comm.d_rows_per_block = d_rows;
+    comm.blk_rows = pc->blk_rows;
+    comm.num_blocks = nb;
+    comm.first_block = pc->first_block;
+    comm.scatter = scatter ? 1 : 0;
   }
+  const int d_rows = scatter ? M / num_dest : (red_grouped ? pc->num_groups * M : M);
   for (int b = 0; b < num_dest; ++b) {
     void* dptr = (pc && pc->d_num_dest > 0) ? pc->d_ptrs[b] : D;
     if (OUT == OUT_BF16)
@@ -477,19 +499,13 @@ static int launch(const void* A, const void* B, void* D, int M, int N, int K, in
     if (rc) return rc;
   }
   for (int b = num_dest; b < PICO_MAX_PEERS; ++b) dm.m[b] = dm.m[0];
-  if (pc && pc->a_flags != nullptr) {
-    if (A_MN != 0 || pc->a_rows_per_block % BM != 0 || pc->a_rows_per_block <= 0) {
-      pico_host::set_error("gather->gemm: need K-major A and row blocks that are a multiple of %d", BM);
-      return -2;
-    }
+  if (gather) {
     comm.a_flags = pc->a_flags;
     comm.a_slot = pc->a_slot;
     comm.a_epoch = pc->a_epoch;
-    comm.a_rows_per_block = pc->a_rows_per_block;
     comm.a_skip_block = pc->a_skip_block;
   }
   if (pc) {
-    comm.m_rotate = pc->m_rotate_rows / BM;
     comm.timeout_ns = (unsigned long long)pc->timeout_ms * 1000000ull;
     comm.tile_group = pc->tile_group;
     comm.b_group_rows = pc->b_group_rows;

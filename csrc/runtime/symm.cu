@@ -41,7 +41,7 @@ extern "C" int pico_epoch_base_add(uint32_t* local_flags, const PicoEpochDeltas*
       pico_host::set_error("epoch_base_add: slot %d out of range", deltas->slot[i]);
       return -2;
     }
-  pico::epoch_base_add_kernel<<<1, 32, 0, stream>>>(local_flags, *deltas);
+  pico::epoch_base_add_kernel<<<1, PICO_MAX_EPOCH_DELTAS, 0, stream>>>(local_flags, *deltas);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) pico_host::set_error("epoch_base_add: %s", cudaGetErrorString(e));
   return (int)e;

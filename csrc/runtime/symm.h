@@ -23,7 +23,7 @@
 #define PICO_MAX_PEERS 8
 #define PICO_FLAG_SLOTS 256
 #define PICO_FLAG_BYTES ((PICO_FLAG_SLOTS * PICO_MAX_PEERS + PICO_FLAG_SLOTS) * 4)
-#define PICO_MAX_EPOCH_DELTAS 24
+#define PICO_MAX_EPOCH_DELTAS 256
 
 #ifdef __cplusplus
 extern "C" {

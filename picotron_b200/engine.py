@@ -45,11 +45,6 @@ def loss_fn(model, logits, targets, divisor: float = 1.0) -> torch.Tensor:
     """Mean token loss (divided by ``divisor``, the number of micro-batches) from the model output:
     dense logits, or vocabulary-sharded logits when the lm head keeps them sharded
     (``vocab_parallel_ce``). ``backward()`` must be called on the result (or a sum containing it)."""
-    if logits.dim() == 2 and targets.dim() == 2:
-        # fused sequence-parallel lm head: rows are rank-major, bring the targets into that order
-        world = group_size(getattr(model, "tp_group", None))
-        b, s = targets.shape
-        targets = targets.view(b, world, s // world).transpose(0, 1).reshape(-1)
     if getattr(model, "vocab_parallel_ce", False) and group_size(getattr(model, "tp_group", None)) > 1:
         g = model.tp_group
         start = group_rank(g) * logits.shape[-1]
@@ -363,13 +358,16 @@ class TrainEngine:
         from .ops.fused_tp import TPFused
         from .parallel.tensor_parallel import install_fused_tp
         from .runtime.symm import SymmGroup
-        m_local = t["micro_batch_size"] * (t["seq_length"] // m.cp_world_size // m.tp_world_size)
-        if not TPFused.usable(m_local):
+        s_local = t["seq_length"] // m.cp_world_size // m.tp_world_size
+        m_local = t["micro_batch_size"] * s_local
+        if not TPFused.usable(m_local, s_local):
             return
         sg = SymmGroup(m.tp_group, device=self.device)
         self._symm_groups.append(sg)
-        self.fused_tp = TPFused(sg, m_local, self.model_config.hidden_size)
+        self.fused_tp = TPFused(sg, m_local, self.model_config.hidden_size, s_local)
         install_fused_tp(self.model, self.fused_tp)
+        # one micro-batch in flight at a time: gathered inputs can stay in place for the backward pass
+        self.fused_tp.keep_gathered = m.pp_world_size == 1 and os.environ.get("PICO_TP_KEEP_GATHERED", "1") != "0"
         ce_ops.install_peer_exchange(m.tp_group, self.fused_tp.ce_exchange)
 
     def _use_fused_dp(self) -> bool:
@@ -472,6 +470,8 @@ class TrainEngine:
         """Forward + backward of one micro-batch; gradients accumulate; returns its detached loss / ga."""
         timed = self.timer is not None and not (self.device.type == "cuda"
                                                 and torch.cuda.is_current_stream_capturing())
+        if self.fused_tp is not None:
+            self.fused_tp.begin_micro_batch()
         with (self.timer.section("forward") if timed else contextlib.nullcontext()):
             logits = self.dp_model(input_ids=input_ids)
             mb_loss = loss_fn(self.model, logits, target_ids, divisor=ga)
@@ -567,6 +567,8 @@ class TrainEngine:
                 sg.begin_graph()
                 sg.barrier()
             loss.add_(self._micro_batch(inp, tgt, ga))
+            if self.fused_tp is not None:
+                self.fused_tp.join()          # side-stream pushes rejoin the captured stream
             recs = []
             for sg in self._symm_groups:
                 sg.barrier()

@@ -165,14 +165,9 @@ class MLP(nn.Module):
         return swiglu_ops.swiglu(multi_linear([self.gate_proj, self.up_proj], x, cat=True))
 
     def forward(self, x, residual=None):
-        fused = getattr(self.gate_proj, "fused", None)
-        if fused is not None and x.is_cuda and x.dim() == 3 and x.shape[0] * x.shape[1] == fused.m_local \
-                and not getattr(self.gate_proj, "raw", False):
-            # fused sequence parallelism: gate/up output, SwiGLU and the down projection all work on
-            # rank-major rows; the reduce-scatter epilogue adds the residual
-            gu = multi_linear([self.gate_proj, self.up_proj], x, cat=True, rank_major=True)
-            return self.down_proj(swiglu_ops.swiglu(gu), residual=residual, rank_major_in=True,
-                                  shard_bs=(x.shape[0], x.shape[1]))
+        if getattr(self.down_proj, "fused", None) is not None and residual is not None:
+            # fused sequence parallelism: the reduce-scatter epilogue of the down projection adds the residual
+            return self.down_proj(self.hidden(x), residual=residual)
         y = self.down_proj(self.hidden(x))
         return y if residual is None else y + residual
 
@@ -278,16 +273,8 @@ class DecoderLayer(nn.Module):
 
 
 def lm_head(model, x):
-    """final norm + vocabulary projection. On the fused sequence-parallel path the logits stay in
-    rank-major row order (2-D ``[tokens, V/tp]``); ``engine.loss_fn`` reorders the targets to match
-    instead of copying the much larger logits."""
-    x = model.final_norm(x)
-    proj = model.final_proj
-    fused = getattr(proj, "fused", None)
-    if fused is not None and x.is_cuda and x.dim() == 3 and x.shape[0] * x.shape[1] == fused.m_local \
-            and not proj.gather_output:
-        return multi_linear([proj], x, cat=True, rank_major=True)
-    return proj(x)
+    """final norm + vocabulary projection."""
+    return model.final_proj(model.final_norm(x))
 
 
 class Llama(nn.Module):

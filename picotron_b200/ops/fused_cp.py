@@ -70,7 +70,7 @@ class CPFused:
                     rows = rows.contiguous()
                 epoch = self.sg.next_epoch(slot)
                 ext().push_rows(rows, self.gather[c].peer_ptrs(self._region(which, bi)), self.sg.flags.ptrs,
-                                self.world, self.rank, self.s_local, self.kv_cols, slot, epoch)
+                                self.world, self.rank, self.s_local, self.kv_cols, slot, epoch, 0, 0)
                 count_launch()
         return c, slot, epoch
 
@@ -104,7 +104,7 @@ class CPFused:
                     if not src.is_contiguous():
                         src = src.contiguous()
                 ext().scatter_rows(src, self.staging[c].peer_ptrs(self._region(which, bi)), self.sg.flags.ptrs,
-                                   self.world, self.rank, self.rank, self.s_local, self.kv_cols, slot, epoch)
+                                   self.world, self.rank, self.rank, self.s_local, self.kv_cols, slot, epoch, 0)
                 count_launch()
         outs = []
         for which in range(2):

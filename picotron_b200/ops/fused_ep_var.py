@@ -76,7 +76,8 @@ class EPVarFused:
         c, slot, epoch = self._next("count", COUNT_SLOTS)
         e = ext()
         row = counts.contiguous().view(torch.bfloat16).view(1, 2 * self.E)     # raw bytes of the int32 row
-        e.push_rows(row, self.counts_buf[c].ptrs, self.sg.flags.ptrs, self.ep, self.rank, 1, 2 * self.E, slot, epoch)
+        e.push_rows(row, self.counts_buf[c].ptrs, self.sg.flags.ptrs, self.ep, self.rank, 1, 2 * self.E, slot, epoch,
+                    0, 0)
         self.sg.wait(slot, epoch, self.timeout_ms)
         table = self.counts_buf[c].view(torch.int32, (self.ep, self.E))
         dev = counts.device

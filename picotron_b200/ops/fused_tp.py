@@ -11,9 +11,10 @@ an optional residual. No NCCL call is on either path. They replace
 picotron/sequence_parallel/sequence_parallel.py:20-72 (and the chunked P2P overlap of
 overlap.py:40-118).
 
-Rows are kept in *rank-major* order between fused ops: row block r of a gathered tensor is rank
-r's ``[b, s/tp]`` shard flattened. Per-token ops (SwiGLU, the lm head + loss) run in that order
-unchanged; only attention needs ``[b, s, ...]`` and converts with one copy each way.
+Gathered tensors are ordinary ``[b, s, C]`` tensors: the kernels know that a shard is ``b`` pieces
+of ``s/tp`` rows and address piece ``(batch, rank)`` at its place in the full sequence (push, GEMM
+tile order and flag gating, scattering epilogue all work on that piece geometry), so no layout
+conversion copies surround attention or the loss.
 
 Buffers alternate between two copies per kind; because every fused op needs data from all
 ranks before it completes, no rank can be two ops ahead of another, which makes the second
@@ -33,6 +34,8 @@ BM = 128
 GATHER_SLOTS = (0, 1)
 SCATTER_SLOTS = (2, 3)
 CE_SLOTS = (4, 5)
+KEPT_SLOT0 = 16            # flag slots 16 .. 16 + (number of kept gather buffers) - 1
+MAX_KEPT = 224
 
 
 class PeerStatsExchange:
@@ -69,10 +72,14 @@ class PeerStatsExchange:
 
 
 class TPFused:
-    def __init__(self, symm_group, m_local: int, max_cols: int):
+    def __init__(self, symm_group, m_local: int, max_cols: int, s_local: Optional[int] = None):
+        """``m_local`` rows per rank (micro-batch x sequence shard), made of pieces of ``s_local`` rows
+        (the sequence shard of one batch row; default: one piece)."""
         self.sg = symm_group
         self.world, self.rank = symm_group.world, symm_group.rank
         self.m_local = m_local
+        self.s_local = m_local if s_local is None else s_local
+        assert m_local % self.s_local == 0 and self.s_local % BM == 0
         self.m_full = m_local * self.world
         self.max_cols = max_cols
         self.gather = [symm_group.alloc(self.m_full * max_cols * 2) for _ in range(2)]
@@ -81,23 +88,77 @@ class TPFused:
         self.n_scatter = 0
         self.timeout_ms = int(os.environ.get("PICO_COMM_TIMEOUT_MS", "20000"))
         self.ce_exchange = PeerStatsExchange(symm_group, self.m_full, self.timeout_ms)
+        # Pushes run on their own stream so that they overlap the GEMM that consumes the gathered
+        # rows: the GEMM starts on this rank's rows at once and picks the other ranks' row blocks
+        # up as their flags arrive. PICO_TP_COMM_STREAM=0 keeps everything on one stream.
+        self.comm_stream = torch.cuda.Stream(device=symm_group.device) \
+            if os.environ.get("PICO_TP_COMM_STREAM", "1") != "0" else None
+        self._pushing = []        # sources of pushes still in flight on the comm stream
+        # Gathered inputs kept for the backward pass: the i-th column-parallel gather of a micro-batch
+        # lands in its own symmetric buffer, which the weight-gradient GEMM reads later, so the backward
+        # pass gathers nothing again. Needs one micro-batch in flight at a time (no pipeline
+        # parallelism) and ``begin_micro_batch()`` before every forward pass; off by default.
+        self.keep_gathered = False
+        self.kept = []
+        self._kept_idx = 0
 
     @staticmethod
-    def usable(m_local: int) -> bool:
-        return m_local % BM == 0
+    def usable(m_local: int, s_local: Optional[int] = None) -> bool:
+        s_local = m_local if s_local is None else s_local
+        return s_local % BM == 0 and m_local % s_local == 0
+
+    def begin_micro_batch(self):
+        """Start of a forward pass (engine). With kept gather buffers: a peer that already finished its
+        backward pass must not push the next micro-batch's first rows while this rank's last
+        weight-gradient GEMM still reads that buffer, hence a barrier over the group."""
+        self._kept_idx = 0
+        if self.keep_gathered:
+            self.join()
+            self.sg.barrier()
 
     # -- all-gather by pushing ----------------------------------------------------------------
-    def gather_push(self, x2: torch.Tensor):
-        """x2: [m_local, K] contiguous bf16. Returns (gathered view [m_full, K], slot, epoch)."""
+    def gather_push(self, x2: torch.Tensor, keep: bool = False):
+        """x2: [m_local, K] contiguous bf16. Returns (gathered view [m_full, K], slot, epoch). ``keep``:
+        use this micro-batch's next kept buffer (valid until the same call of the next micro-batch)
+        when ``keep_gathered`` is on; the returned view is then safe to hold for the backward pass."""
         m, k = x2.shape
         assert m == self.m_local and k <= self.max_cols
-        b = self.n_gather % 2
-        self.n_gather += 1
-        slot = GATHER_SLOTS[b]
+        if keep and self.keep_gathered:
+            i = self._kept_idx
+            self._kept_idx += 1
+            if i == len(self.kept):
+                assert i < MAX_KEPT, "too many kept gather buffers for the flag table"
+                assert not torch.cuda.is_current_stream_capturing(), \
+                    "kept gather buffers are created by an eager forward pass before any graph capture"
+                self.kept.append(self.sg.alloc(self.m_full * self.max_cols * 2))
+            target, slot = self.kept[i], KEPT_SLOT0 + i
+        else:
+            b = self.n_gather % 2
+            self.n_gather += 1
+            target, slot = self.gather[b], GATHER_SLOTS[b]
         epoch = self.sg.next_epoch(slot)
-        ext().push_rows(x2, self.gather[b].ptrs, self.sg.flags.ptrs, self.world, self.rank, m, k, slot, epoch)
+        view = target.view(torch.bfloat16, (self.m_full, k))
+        sl = self.s_local
+        if self.comm_stream is None:
+            ext().push_rows(x2, target.ptrs, self.sg.flags.ptrs, self.world, self.rank, m, k, slot, epoch, 0, sl)
+        else:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())      # x2 is complete
+            with torch.cuda.stream(self.comm_stream):
+                ext().push_rows(x2, target.ptrs, self.sg.flags.ptrs, self.world, self.rank, m, k, slot, epoch, 1, sl)
+            self._pushing.append(x2)       # keeps the source alive until the main stream joins
+            # this rank's own pieces are filled on the consumer's stream: the GEMM never waits for them
+            ext().push_rows(x2, target.ptrs, self.sg.flags.ptrs, self.world, self.rank, m, k, slot, epoch, 2, sl)
+            count_launch()
         count_launch()
-        return self.gather[b].view(torch.bfloat16, (self.m_full, k)), slot, epoch
+        return view, slot, epoch
+
+    def join(self):
+        """Make the current stream wait for the pushes issued so far (their sources may be released
+        afterwards). Called where a consumer needs the whole gathered buffer anyway, and before the
+        end of a CUDA-graph capture."""
+        if self.comm_stream is not None and self._pushing:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            self._pushing.clear()
 
     def gated_gemm(self, a_buf, weight, slot, epoch, b_mn_major: bool, n_out: int, out=None):
         """out[m_full, n_out] = a_buf @ op(weight), loading A row blocks as their flags arrive."""
@@ -105,18 +166,20 @@ class TPFused:
         if out is None:
             out = torch.empty((m, n_out), device=a_buf.device, dtype=torch.bfloat16)
         ext().gemm_ex(a_buf, weight, out, m, n_out, k, a_buf.stride(0), weight.stride(0), out.stride(0), False,
-                      b_mn_major, 0, 0, self.sg.flags.local_ptr, slot, epoch, self.m_local, self.rank, [], 0,
-                      self.rank * self.m_local, self.timeout_ms)
+                      b_mn_major, 0, 0, self.sg.flags.local_ptr, slot, epoch, self.rank, [], self.s_local,
+                      self.world, self.rank, self.timeout_ms)
         count_launch()
         return out
 
     def wait_gather(self, slot, epoch):
+        self.join()
         self.sg.wait(slot, epoch, self.timeout_ms)
 
     # -- reduce-scatter through the GEMM epilogue ------------------------------------------------
     def scatter_gemm(self, a2, weight, b_mn_major: bool, n_out: int):
-        """Partial product a2[m_full, K] @ op(weight) stored row block r -> rank r's staging slot for
-        this rank; raises this rank's flag afterwards. Returns (buffer index, slot, epoch)."""
+        """Partial product a2[m_full, K] @ op(weight); the rows of rank r's sequence pieces are stored into
+        rank r's staging slot for this rank; raises this rank's flag afterwards. Returns (buffer index,
+        slot, epoch)."""
         m, k = a2.shape
         assert m == self.m_full and n_out <= self.max_cols
         b = self.n_scatter % 2
@@ -125,8 +188,8 @@ class TPFused:
         epoch = self.sg.next_epoch(slot)
         off = self.rank * self.m_local * n_out * 2
         ext().gemm_ex(a2, weight, None, m, n_out, k, a2.stride(0), weight.stride(0), n_out, False, b_mn_major, 0,
-                      0, 0, 0, 0, 0, 0, self.staging[b].peer_ptrs(off), self.m_local,
-                      ((self.rank + 1) % self.world) * self.m_local, self.timeout_ms)
+                      0, 0, 0, 0, 0, self.staging[b].peer_ptrs(off), self.s_local, self.world,
+                      (self.rank + 1) % self.world, self.timeout_ms)
         self.sg.signal(slot, epoch)
         count_launch()
         return b, slot, epoch
@@ -140,34 +203,16 @@ class TPFused:
         return out
 
 
-def to_rank_major(x: torch.Tensor, world: int) -> torch.Tensor:
-    """[b, s, C] -> [world*b*(s/world), C] with row block r = sequence chunk r of every batch row."""
-    b, s, c = x.shape
-    if b == 1:
-        return x.reshape(s, c)
-    return x.view(b, world, s // world, c).transpose(0, 1).reshape(b * s, c)
-
-
-def from_rank_major(x2: torch.Tensor, world: int, b: int) -> torch.Tensor:
-    """Inverse of ``to_rank_major``: [world*b*s_loc, C] -> [b, world*s_loc, C]."""
-    m, c = x2.shape
-    s_loc = m // (world * b)
-    if b == 1:
-        return x2.view(1, m, c)
-    return x2.view(world, b, s_loc, c).transpose(0, 1).reshape(b, world * s_loc, c)
-
-
 class _AGLinearFused(torch.autograd.Function):
-    """y = gather(x) @ cat(weights).T. x: [b, s_loc, K] shard; returns rank-major [m_full, N] or,
-    with ``batch_major``, [b, s, N]."""
+    """y = gather(x) @ cat(weights).T. x: [b, s_loc, K] shard; returns [b, s, N]."""
 
     @staticmethod
-    def forward(ctx, x, tp: TPFused, ws, batch_major, *params):
+    def forward(ctx, x, tp: TPFused, ws, kept, *params):
         b, s_loc, k = x.shape
         x2 = x.reshape(b * s_loc, k)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        buf, slot, epoch = tp.gather_push(x2)
+        buf, slot, epoch = tp.gather_push(x2, keep=kept)
         if ws.fused_weight is not None:
             y = tp.gated_gemm(buf, ws.fused_weight, slot, epoch, False, ws.out_features)
         else:
@@ -176,20 +221,26 @@ class _AGLinearFused(torch.autograd.Function):
             for w in ws.params:
                 tp.gated_gemm(buf, w, slot, epoch, False, w.shape[0], out=y[:, col:col + w.shape[0]])
                 col += w.shape[0]
-        ctx.save_for_backward(x2)
-        ctx.tp, ctx.ws, ctx.batch_major, ctx.shape = tp, ws, batch_major, (b, s_loc, k)
-        return from_rank_major(y, tp.world, b) if batch_major else y
+        # kept: the gathered rows stay in their own symmetric buffer until the backward pass (every
+        # block's flag was awaited by the GEMM above), so neither the shard nor a re-gather is needed
+        ctx.kept = buf if kept else None
+        ctx.save_for_backward(*(() if kept else (x2,)))
+        ctx.tp, ctx.ws, ctx.shape = tp, ws, (b, s_loc, k)
+        return y.view(b, s_loc * tp.world, ws.out_features)
 
     @staticmethod
     def backward(ctx, dy):
-        (x2,) = ctx.saved_tensors
         tp, ws = ctx.tp, ctx.ws
         b, s_loc, k = ctx.shape
-        dy2 = to_rank_major(dy, tp.world) if ctx.batch_major else dy
+        dy2 = dy.reshape(tp.m_full, -1)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        # re-gather the input for the weight gradient first so the pushes overlap the dgrad GEMM
-        buf, slot, epoch = tp.gather_push(x2)
+        if ctx.kept is not None:
+            buf, slot, epoch = ctx.kept, None, None
+        else:
+            # re-gather the input for the weight gradient first so the pushes overlap the dgrad GEMM
+            (x2,) = ctx.saved_tensors
+            buf, slot, epoch = tp.gather_push(x2)
         dx = None
         if ws.fused_weight is not None:
             pending = tp.scatter_gemm(dy2, ws.fused_weight, True, k)
@@ -202,7 +253,8 @@ class _AGLinearFused(torch.autograd.Function):
                 sb, sslot, sepoch = tp.scatter_gemm(dy2[:, col:col + w.shape[0]], w, True, k)
                 dx = tp.scatter_sum(sb, sslot, sepoch, k, addend=dx)
                 col += w.shape[0]
-        tp.wait_gather(slot, epoch)
+        if slot is not None:
+            tp.wait_gather(slot, epoch)
         _, grads = gemm_ops.backward_all(dy2, buf, ws, need_dx=False)
         if pending is not None:
             dx = tp.scatter_sum(*pending, k)
@@ -210,14 +262,15 @@ class _AGLinearFused(torch.autograd.Function):
 
 
 class _LinearRSFused(torch.autograd.Function):
-    """y_shard = reduce_scatter(x @ w.T) (+ addend). x: rank-major [m_full, K_loc] or [b, s, K_loc]."""
+    """y_shard = reduce_scatter(x @ w.T) (+ addend). x: [b, s, K_loc] (or its [b*s, K_loc] view);
+    returns [b, s/tp, N]."""
 
     @staticmethod
-    def forward(ctx, x, w, tp: TPFused, batch_major_in, shard_bs, addend):
-        b, s_loc = shard_bs
-        x2 = to_rank_major(x, tp.world) if batch_major_in else x
+    def forward(ctx, x, w, tp: TPFused, addend):
+        x2 = x.reshape(tp.m_full, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
+        b, s_loc = tp.m_local // tp.s_local, tp.s_local
         n = w.shape[0]
         sb, slot, epoch = tp.scatter_gemm(x2, w, False, n)
         add2 = None
@@ -227,7 +280,7 @@ class _LinearRSFused(torch.autograd.Function):
                 add2 = add2.contiguous()
         y = tp.scatter_sum(sb, slot, epoch, n, addend=add2)
         ctx.save_for_backward(x2, w)
-        ctx.tp, ctx.batch_major_in, ctx.b, ctx.has_addend = tp, batch_major_in, b, addend is not None
+        ctx.tp, ctx.x_shape, ctx.has_addend = tp, x.shape, addend is not None
         return y.view(b, s_loc, n)
 
     @staticmethod
@@ -242,39 +295,38 @@ class _LinearRSFused(torch.autograd.Function):
         dx2 = tp.gated_gemm(buf, w, slot, epoch, True, w.shape[1])
         tp.wait_gather(slot, epoch)
         dw = gemm_ops.wgrad_into(w, buf, x2)
-        dx = from_rank_major(dx2, tp.world, ctx.b) if ctx.batch_major_in else dx2
-        return dx, dw, None, None, None, (dy if ctx.has_addend else None)
+        return dx2.view(ctx.x_shape), dw, None, (dy if ctx.has_addend else None)
 
 
 class _EmbeddingRSFused(torch.autograd.Function):
     """Vocabulary-parallel embedding under sequence parallelism without a collective call: every
     rank looks its vocabulary shard up for the whole sequence (rows of ids it does not own are
-    zero), stores row block o into its slot of rank o's staging buffer and sums the slots it
-    received; backward gathers the output gradient by pushing and scatters it into the table's
-    gradient. ids: [b, s] (full sequence); returns [b, s/tp, H]."""
+    zero), stores the rows of rank o's sequence pieces into its slot of rank o's staging buffer and
+    sums the slots it received; backward gathers the output gradient by pushing and scatters it into
+    the table's gradient. ids: [b, s] (full sequence); returns [b, s/tp, H]."""
 
     @staticmethod
     def forward(ctx, ids, weight, vocab_start, tp: TPFused):
         b, s = ids.shape
         V, H = weight.shape
-        ids_rm = ids.view(b, tp.world, s // tp.world).transpose(0, 1).reshape(-1).contiguous()
+        flat = ids.reshape(-1).contiguous()
         part = torch.empty((tp.m_full, H), device=weight.device, dtype=weight.dtype)
-        ext().embedding_fwd(weight, ids_rm, part, tp.m_full, H, V, vocab_start)
+        ext().embedding_fwd(weight, flat, part, tp.m_full, H, V, vocab_start)
         sb = tp.n_scatter % 2
         tp.n_scatter += 1
         slot = SCATTER_SLOTS[sb]
         epoch = tp.sg.next_epoch(slot)
         ext().scatter_rows(part, tp.staging[sb].ptrs, tp.sg.flags.ptrs, tp.world, tp.rank, tp.world, tp.m_local, H,
-                           slot, epoch)
+                           slot, epoch, tp.s_local)
         count_launch(2)
         y = tp.scatter_sum(sb, slot, epoch, H)
-        ctx.save_for_backward(ids_rm, weight)
-        ctx.tp, ctx.vocab_start, ctx.shape = tp, vocab_start, (b, s // tp.world, H)
+        ctx.save_for_backward(flat, weight)
+        ctx.tp, ctx.vocab_start = tp, vocab_start
         return y.view(b, s // tp.world, H)
 
     @staticmethod
     def backward(ctx, dy):
-        ids_rm, weight = ctx.saved_tensors
+        flat, weight = ctx.saved_tensors
         tp = ctx.tp
         V, H = weight.shape
         dy2 = dy.reshape(-1, H)
@@ -284,7 +336,7 @@ class _EmbeddingRSFused(torch.autograd.Function):
         tp.wait_gather(slot, epoch)
         main_grad = getattr(weight, "main_grad", None)
         acc = main_grad if main_grad is not None else torch.zeros((V, H), device=weight.device, dtype=torch.float32)
-        ext().embedding_bwd(buf, ids_rm, acc, tp.m_full, H, V, ctx.vocab_start)
+        ext().embedding_bwd(buf, flat, acc, tp.m_full, H, V, ctx.vocab_start)
         count_launch()
         if main_grad is not None:
             hook = getattr(weight, "grad_ready_hook", None)
@@ -298,10 +350,11 @@ def embedding_rs(ids, weight, vocab_start: int, tp: TPFused):
     return _EmbeddingRSFused.apply(ids, weight, vocab_start, tp)
 
 
-def ag_linear(x, tp: TPFused, mods, batch_major: bool):
+def ag_linear(x, tp: TPFused, mods):
     ws = gemm_ops.WeightSet.of(mods)
-    return _AGLinearFused.apply(x, tp, ws, batch_major, *ws.params)
+    kept = tp.keep_gathered and torch.is_grad_enabled()      # decided here: grad mode is off inside forward
+    return _AGLinearFused.apply(x, tp, ws, kept, *ws.params)
 
 
-def linear_rs(x, w, tp: TPFused, batch_major_in: bool, shard_bs, addend=None):
-    return _LinearRSFused.apply(x, w, tp, batch_major_in, shard_bs, addend)
+def linear_rs(x, w, tp: TPFused, addend=None):
+    return _LinearRSFused.apply(x, w, tp, addend)

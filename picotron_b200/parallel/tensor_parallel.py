@@ -113,12 +113,10 @@ def _fused_ctx(mod, x):
     return tp
 
 
-def multi_linear(mods: Sequence[nn.Module], x: torch.Tensor, cat: bool = False, rank_major: bool = False):
+def multi_linear(mods: Sequence[nn.Module], x: torch.Tensor, cat: bool = False):
     """Apply several bias-free projections to the same input, sharing the input collective and,
     when the weights are stored back to back, the GEMM. Returns the list of outputs (column
-    slices of one buffer), or that buffer itself ``[..., sum(out_i)]`` with ``cat=True``.
-    ``rank_major`` (fused sequence-parallel path only) keeps the gathered rows in rank-major
-    order as a 2-D ``[tokens, sum(out_i)]`` tensor instead of restoring ``[b, s, ...]``."""
+    slices of one buffer), or that buffer itself ``[..., sum(out_i)]`` with ``cat=True``."""
     first = mods[0]
     splits = [m.weight.shape[0] for m in mods]
     if not isinstance(first, ColumnParallelLinear):
@@ -128,7 +126,7 @@ def multi_linear(mods: Sequence[nn.Module], x: torch.Tensor, cat: bool = False, 
     tp = None if (first.raw or first.tp_world_size == 1) else _fused_ctx(first, x)
     if tp is not None and x.dim() == 3 and x.shape[0] * x.shape[1] == tp.m_local:
         from ..ops import fused_tp
-        y = fused_tp.ag_linear(x, tp, mods, batch_major=not rank_major)
+        y = fused_tp.ag_linear(x, tp, mods)
     elif first.raw or first.tp_world_size == 1:
         y = gemm_ops.multi_linear_cat(x, mods)
     elif first.sequence_parallel:
@@ -194,18 +192,13 @@ class RowParallelLinear(nn.Module):
         with torch.no_grad():
             self.weight.copy_(master[:, lo:lo + self.input_size_per_partition])
 
-    def forward(self, x, addend=None, residual=None, rank_major_in=False, shard_bs=None):
+    def forward(self, x, addend=None, residual=None):
         """``addend`` (parallel block, overlap mode) is a second partial sum folded into the
-        same reduction; ``residual`` is added once to the reduced result. ``rank_major_in`` /
-        ``shard_bs`` describe an input that is still in the rank-major row order of the fused
-        sequence-parallel path (see ``ops.fused_tp``)."""
+        same reduction; ``residual`` is added once to the reduced result."""
         tp = _fused_ctx(self, x)
-        if tp is not None and addend is None and not self.raw:
+        if tp is not None and addend is None and not self.raw and x.numel() // x.shape[-1] == tp.m_full:
             from ..ops import fused_tp
-            if shard_bs is None:
-                shard_bs = (x.shape[0], x.shape[1] // self.tp_world_size)
-            return fused_tp.linear_rs(x, self.weight, tp, not rank_major_in, shard_bs, addend=residual)
-        assert not rank_major_in, "rank-major inputs exist only on the fused path"
+            return fused_tp.linear_rs(x, self.weight, tp, addend=residual)
         if self.raw or self.tp_world_size == 1:
             y = gemm_ops.linear(x, self.weight)
             y = y if addend is None else y + addend

@@ -19,7 +19,7 @@ from .. import ops
 FLAG_SLOTS = 256
 MAX_PEERS = 8
 FLAG_BYTES = (FLAG_SLOTS * MAX_PEERS + FLAG_SLOTS) * 4   # flag words, then one epoch-base word per slot
-MAX_EPOCH_DELTAS = 24
+MAX_EPOCH_DELTAS = 256
 
 
 class SymmBuffer:

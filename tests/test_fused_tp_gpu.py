@@ -69,7 +69,7 @@ def _fused_ops_worker(rank, world):
     dev = torch.device("cuda", rank)
     b, s_loc, K, N = 2, 256, 512, 768
     sg = SymmGroup(None)
-    tp = fused_tp.TPFused(sg, b * s_loc, max(K, N))
+    tp = fused_tp.TPFused(sg, b * s_loc, max(K, N), s_loc)
     torch.manual_seed(0)                               # same full tensors on every rank
     x_full = torch.randn(b, s_loc * world, K, device=dev).to(torch.bfloat16)
     w_col = (torch.randn(N * world, K, device=dev) / K ** 0.5).to(torch.bfloat16)     # column-parallel weight
@@ -82,7 +82,7 @@ def _fused_ops_worker(rank, world):
 
         class M:  # minimal module stand-in for WeightSet.of
             weight = w_loc
-        y = fused_tp.ag_linear(x_sh, tp, [M], batch_major=True)
+        y = fused_tp.ag_linear(x_sh, tp, [M])
         ref = x_full.float() @ w_loc.float().t()
         assert _rel(y, ref) < 1e-2, ("ag_linear fwd", it)
         gy = g_full[:, :, rank * N:(rank + 1) * N].contiguous()
@@ -97,7 +97,7 @@ def _fused_ops_worker(rank, world):
         xin = xin_full[:, :, rank * N:(rank + 1) * N].clone().requires_grad_(True)
         wr = torch.nn.Parameter(w_row[:, rank * N:(rank + 1) * N].clone())
         res = x_full[:, rank * s_loc:(rank + 1) * s_loc].clone().requires_grad_(True)
-        out = fused_tp.linear_rs(xin, wr, tp, True, (b, s_loc), addend=res)
+        out = fused_tp.linear_rs(xin, wr, tp, addend=res)
         ref_full = xin_full.float() @ w_row.float().t() + x_full.float()
         assert _rel(out, ref_full[:, rank * s_loc:(rank + 1) * s_loc]) < 1e-2, ("linear_rs fwd", it)
         go = x_full[:, rank * s_loc:(rank + 1) * s_loc].contiguous()
