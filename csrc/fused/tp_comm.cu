@@ -9,9 +9,12 @@
 namespace pico {
 
 __global__ void push_rows_kernel(const uint4* __restrict__ src, PicoPeerTable dst, PicoPeerTable flags,
-                                 int world, int my_rank, int64_t nvec, int64_t nvec_piece, int slot,
+                                 int world, int my_rank, int num_pieces, int64_t nvec_piece, int slot,
                                  uint32_t epoch, unsigned int* counter, int skip_self) {
-  // piece p of the source (nvec_piece vectors) is piece p * world + my_rank of the destination
+  // piece p of the source (nvec_piece vectors) is piece p * world + my_rank of the destination.
+  // (Reporting the pieces one by one, each behind a grid-wide rendezvous, was measured slower than
+  // one pass over everything with a single flag at the end: 286 vs 271 ms per step at 4 GPUs.)
+  const int64_t nvec = (int64_t)num_pieces * nvec_piece;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
        i += (int64_t)gridDim.x * blockDim.x) {
     const uint4 v = src[i];
@@ -82,8 +85,11 @@ static unsigned int* grid_counter() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
   if (!g_counters[dev]) {
     unsigned int* p = nullptr;
-    if (cudaMalloc(&p, 64 * sizeof(unsigned int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, 64 * sizeof(unsigned int));
+    // words 0..63: one per kernel kind; words 64..319: one per piece of a push; words 320..575: the
+    // same for pushes that leave this rank's own buffer out (they run on a stream of their own and
+    // may overlap an ordinary push)
+    if (cudaMalloc(&p, 576 * sizeof(unsigned int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 576 * sizeof(unsigned int));
     g_counters[dev] = p;
   }
   return g_counters[dev];
@@ -107,19 +113,20 @@ extern "C" int pico_push_rows(const void* src, PicoPeerTable dst, PicoPeerTable 
   if (int rc = check_world("push_rows", world, slot)) return rc;
   const int64_t n = (int64_t)rows * cols;
   if (piece_rows <= 0) piece_rows = rows;
-  if (n % 8 != 0 || rows % piece_rows != 0 || ((int64_t)piece_rows * cols) % 8 != 0) {
-    pico_host::set_error("push_rows: rows*cols and piece_rows*cols must be multiples of 8, rows a multiple of piece_rows");
+  if (n % 8 != 0 || rows % piece_rows != 0 || ((int64_t)piece_rows * cols) % 8 != 0 || rows / piece_rows > 254) {
+    pico_host::set_error("push_rows: rows*cols and piece_rows*cols must be multiples of 8, rows a multiple of "
+                         "piece_rows, at most 254 pieces");
     return -2;
   }
   unsigned int* counter = grid_counter();
   if (!counter) return -1;
-  const int64_t nvec = n / 8;
-  int grid = (int)((nvec + 255) / 256);
+  const int64_t nvec_piece = (int64_t)piece_rows * cols / 8;
+  int grid = (int)((n / 8 + 255) / 256);
   const int cap = pico_host::num_sms() * 4;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
-  push_rows_kernel<<<grid, 256, 0, stream>>>((const uint4*)src, dst, flags, world, my_rank, nvec,
-                                             (int64_t)piece_rows * cols / 8, slot, epoch, counter, skip_self);
+  push_rows_kernel<<<grid, 256, 0, stream>>>((const uint4*)src, dst, flags, world, my_rank, rows / piece_rows,
+                                             nvec_piece, slot, epoch, counter + (skip_self == 1 ? 320 : 64), skip_self);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) pico_host::set_error("push_rows: %s", cudaGetErrorString(e));
   return (int)e;

@@ -210,7 +210,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      uint32_t ready_blocks = 0;  // row blocks of A known to have arrived
+      uint64_t ready_pieces = 0;  // per block (8 bits each): pieces of A known to have arrived
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const TileWork tw = tile_work(tile, num_m, num_n, num_kb, comm);
         if (tw.skip) continue;
@@ -218,15 +218,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // row-grouped mode: this tile's B is group grp's block of the stacked matrix
         const int b_off = comm.tile_group != nullptr ? tw.grp * comm.b_group_rows : 0;
         if (comm.a_flags != nullptr) {
-          const int blk = (m0 / comm.blk_rows) % comm.num_blocks;
-          if (blk != comm.a_skip_block && !((ready_blocks >> blk) & 1u)) {
+          const int piece = m0 / comm.blk_rows;
+          const int blk = piece % comm.num_blocks;
+          // the writer reports its pieces in order: piece k of a block is there once progress > k
+          const uint32_t need = min(piece / comm.num_blocks + 1, 254);
+          if (blk != comm.a_skip_block && ((ready_pieces >> (8 * blk)) & 0xFFu) < need) {
             if (!wait_flag_ge(comm.a_flags + comm.a_slot * PICO_MAX_PEERS + blk,
-                              epoch_base(comm.a_flags, comm.a_slot) + comm.a_epoch, comm.timeout_ns, status,
+                              flag_value(comm.a_flags, comm.a_slot, comm.a_epoch, need), comm.timeout_ns, status,
                               500 + blk)) {
               *abort_word = 1;
               break;
             }
-            ready_blocks |= 1u << blk;
+            ready_pieces = (ready_pieces & ~(0xFFull << (8 * blk))) | ((uint64_t)need << (8 * blk));
             // the rows were written by another GPU; order the flag observation before the
             // bulk-copy engine's reads of them
             asm volatile("fence.proxy.async;" ::: "memory");

@@ -28,6 +28,16 @@ __device__ __forceinline__ uint32_t epoch_base(const void* local_flags, int slot
   return __ldcg(reinterpret_cast<const uint32_t*>(local_flags) + PICO_FLAG_SLOTS * PICO_MAX_PEERS + slot);
 }
 
+// A flag word holds (absolute epoch << 8) | progress. Progress kFlagDone means the operation of that
+// epoch is complete; 1 .. 254 mean that many parts of it are (the all-gather pushes report piece by
+// piece so that their consumer can start on the first pieces). Waits compare with a wrap-safe ">=",
+// so a waiter for part k is also released by any later part, by kFlagDone and by later epochs.
+constexpr uint32_t kFlagDone = 0xFFu;
+__device__ __forceinline__ uint32_t flag_value(const void* local_flags, int slot, uint32_t rel_epoch,
+                                               uint32_t progress) {
+  return ((epoch_base(local_flags, slot) + rel_epoch) << 8) | progress;
+}
+
 // Spin until *p >= epoch or `timeout_ns` passes. On timeout records error 2 and returns false.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t epoch, uint64_t timeout_ns,
                                              int* status, int site) {
@@ -55,8 +65,8 @@ __device__ __forceinline__ bool wait_slot_all(const uint32_t* local_flags, int s
   if (threadIdx.x == 0) pico_wait_ok = 1;
   __syncthreads();
   if ((int)threadIdx.x < world) {
-    const uint32_t epoch = epoch_base(local_flags, slot) + rel_epoch;
-    if (!wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + threadIdx.x, epoch, timeout_ns, status,
+    const uint32_t want = flag_value(local_flags, slot, rel_epoch, kFlagDone);
+    if (!wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + threadIdx.x, want, timeout_ns, status,
                       site + threadIdx.x))
       pico_wait_ok = 0;
   }
@@ -64,11 +74,11 @@ __device__ __forceinline__ bool wait_slot_all(const uint32_t* local_flags, int s
   return pico_wait_ok != 0;
 }
 
-// Grid-wide completion: the last CTA to finish raises flag [slot][my_rank] = base + rel_epoch on
+// Grid-wide completion: the last CTA to arrive raises flag [slot][my_rank] to (epoch, progress) on
 // every rank of `flags`. `counter` is a device word that returns to zero after each use.
 __device__ __forceinline__ void raise_flags_when_grid_done(unsigned int* counter, PicoPeerTable flags,
                                                            int world, int my_rank, int slot,
-                                                           uint32_t rel_epoch) {
+                                                           uint32_t rel_epoch, uint32_t progress = kFlagDone) {
   __threadfence_system();
   __syncthreads();
   __shared__ bool pico_last_cta;
@@ -81,7 +91,7 @@ __device__ __forceinline__ void raise_flags_when_grid_done(unsigned int* counter
   if (pico_last_cta && (int)threadIdx.x < world) {
     __threadfence_system();
     st_release_sys(flag_word(flags.ptr[threadIdx.x], slot, my_rank),
-                   epoch_base(flags.ptr[my_rank], slot) + rel_epoch);
+                   flag_value(flags.ptr[my_rank], slot, rel_epoch, progress));
   }
 }
 

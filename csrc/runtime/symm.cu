@@ -13,15 +13,15 @@ __global__ void signal_peers_kernel(PicoPeerTable flags, int world, int my_rank,
   __threadfence_system();
   const int t = threadIdx.x;
   if (t < world)
-    st_release_sys(flag_word(flags.ptr[t], slot, my_rank), epoch_base(flags.ptr[my_rank], slot) + epoch);
+    st_release_sys(flag_word(flags.ptr[t], slot, my_rank), flag_value(flags.ptr[my_rank], slot, epoch, kFlagDone));
 }
 
 __global__ void wait_flags_kernel(const uint32_t* local_flags, int world, int slot, uint32_t epoch,
                                   uint64_t timeout_ns, int* status) {
   const int t = threadIdx.x;
   if (t < world)
-    wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + t, epoch_base(local_flags, slot) + epoch, timeout_ns,
-                 status, 900 + t);
+    wait_flag_ge(local_flags + slot * PICO_MAX_PEERS + t, flag_value(local_flags, slot, epoch, kFlagDone),
+                 timeout_ns, status, 900 + t);
 }
 
 __global__ void epoch_base_add_kernel(uint32_t* local_flags, PicoEpochDeltas d) {
