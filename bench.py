@@ -7,6 +7,8 @@ GPUs of one node.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
     python bench.py --impl reference ...     # the unmodified reference package from baseline/_ref
+    ... bench.py --config moe|cp|pp [--variant V] [--layers L]   # the other benchmark configurations
+                                                                 # (benchmarks/config_specs.py), both arms
 
 Layouts (all with sequence parallelism, vocabulary-parallel cross entropy and ZeRO-1 where the
 axis exists): 1 GPU = no parallelism, 2 = TP2, 4 = TP4, 8 = DP2 x TP4.
@@ -249,7 +251,7 @@ def run_reference(args):
         os.environ["FLASH_ATTEN"] = "1"
         os.environ["DEVICE"] = "cuda"
         os.environ["DTYPE"] = "bfloat16"
-        sys.path.insert(0, ref_root)
+        import_reference(ref_root)
         import torch.nn.functional as F
         import picotron.process_group_manager as rpgm
         from picotron.model import Llama as RefLlama
@@ -345,15 +347,141 @@ def run_reference(args):
                   flush=True)
 
 
+# ------------------------------------------------------------ the other configurations, both arms
+def config_line(args, spec, world, ms_total, e2e_ms_total, arm, clocks, launches, impl, final_loss):
+    from benchmarks.config_specs import flops_per_token as fpt_of
+    from picotron_b200.utils import measured_peak_flops
+    tokens = arm["tokens_per_step"]
+    ms_per_step = ms_total / args.steps
+    value = tokens / (ms_per_step / 1e3)
+    fpt = fpt_of(spec["model"], spec["seq"])
+    return {
+        "metric": f"training throughput, {spec['name']} configuration (tokens/s, whole job)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic seeded uniform tokens, random-init N(0,0.02) weights", "impl": impl,
+        "mfu_percent_h100_constant": round(value / world * fpt / H100_PEAK * 100.0, 2),
+        "mfu_percent_b200_measured_peak": round(value / world * fpt / measured_peak_flops() * 100.0, 2),
+        "config": {"model": spec["model_label"], "layers": spec["model"]["num_hidden_layers"],
+                   "global_batch_tokens": tokens, "seq_len": spec["seq"], "micro_batch": spec["mbs"],
+                   "grad_accum": spec["grad_acc"], "optimizer": "AdamW lr 3e-4", "variant": spec["variant"],
+                   "parallelism": arm.get("parallelism", spec["label"]),
+                   "l2": "per-step working set exceeds the 126 MB L2; no explicit flush"},
+        "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
+                   "reasons": clocks.get("reasons", [])},
+        "e2e": {"value": round(tokens / (e2e_ms_total / args.steps / 1e3), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": arm["h2d_bytes_per_step"], "d2h_bytes_per_step": arm["d2h_bytes_per_step"]},
+        "gpu_launches": launches, "final_loss": final_loss,
+    }
+
+
+def build_ours_arm(spec, device):
+    """This framework's arm of a configuration: ``TrainEngine`` on the spec's engine config."""
+    from picotron_b200.engine import TrainEngine
+    engine = TrainEngine(spec["engine_cfg"], device=device)
+    dl = engine.data_loader
+    g = torch.Generator().manual_seed(99 + dl.dp_rank)
+    vocab = engine.model_config.vocab_size
+    shape = (dl.micro_batch_size, dl.seq_length_per_gpu)
+    resident = [(torch.randint(0, vocab, shape, generator=g).to(device), torch.randint(0, vocab, shape, generator=g).to(device))
+                for _ in range(dl.grad_acc_steps)]
+
+    def e2e_step():
+        return engine.average_loss(engine.train_step())
+
+    return dict(device_step=lambda: engine.train_step(device_batches=resident), e2e_step=e2e_step,
+                tokens_per_step=engine.tokens_per_step,
+                h2d_bytes_per_step=dl.grad_acc_steps * 2 * shape[0] * shape[1] * 8, d2h_bytes_per_step=4,
+                parallelism=spec["label"], close=engine.close)
+
+
+def run_config(args):
+    from benchmarks.config_specs import make_spec
+    reference = args.impl == "reference"
+    ref_root = os.path.join(REPO, "baseline", "_ref")
+    if reference and not os.path.isdir(os.path.join(ref_root, "picotron")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/picotron is not installed"}))
+        return
+    try:
+        rank, local_rank, world = setup_distributed(args.gpus)
+        device = torch.device("cuda", local_rank)
+        spec = make_spec(args.config, world, args.variant, args.layers, args.seq)
+        if reference:
+            import_reference(ref_root)
+            from baseline import reference_arms
+            arm = {"moe": reference_arms.build_moe, "cp": reference_arms.build_cp,
+                   "pp": reference_arms.build_pp}[args.config](spec, device, world)
+        else:
+            arm = build_ours_arm(spec, device)
+        ops = None
+        if not reference:
+            from picotron_b200 import ops
+        for _ in range(args.warmup):
+            arm["device_step"]()
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        l0 = 0 if reference else ops.launches()
+        ms = timed(arm["device_step"], args.steps, device)
+        launches = 0 if reference else ops.launches() - l0
+        clocks = sampler.stop() if sampler else {}
+        last = {}
+
+        def e2e():
+            last["loss"] = arm["e2e_step"]()
+
+        for _ in range(max(1, args.warmup // 2)):
+            e2e()
+        e2e_ms = timed(e2e, args.steps, device)
+        if not reference:
+            ops.check_status("bench")
+        # under pipeline parallelism only the last stage knows the loss: report the largest value seen
+        lt = torch.tensor([float(last.get("loss") or 0.0)], device=device)
+        dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+        last["loss"] = float(lt.item())
+        if rank == 0:
+            print(json.dumps(config_line(args, spec, world, ms, e2e_ms, arm, clocks, launches,
+                                         "reference" if reference else "picotron_b200", last.get("loss"))), flush=True)
+        if "close" in arm:
+            arm["close"]()
+        dist.destroy_process_group()
+    except Exception as exc:
+        if not reference:
+            raise
+        if int(os.environ.get("RANK", "0")) == 0:   # the reference could not run on this stack: say why, exit 0
+            print(json.dumps({"impl": "reference", "config": args.config,
+                              "unavailable": f"{type(exc).__name__}: {str(exc).splitlines()[0][:300] if str(exc) else ''}"}),
+                  flush=True)
+
+
+def import_reference(ref_root: str) -> None:
+    """Put the installed reference first on the import path and make sure ``picotron`` resolves to it
+    (this repository also ships a ``picotron`` package: aliases of its own modules)."""
+    for name in [n for n in sys.modules if n == "picotron" or n.startswith("picotron.")]:
+        del sys.modules[name]
+    if REPO in sys.path:
+        sys.path.remove(REPO)
+    sys.path.insert(0, ref_root)
+    import picotron
+    assert os.path.abspath(picotron.__file__).startswith(os.path.abspath(ref_root)), picotron.__file__
+    sys.path.append(REPO)       # behind the reference: for baseline.reference_arms and the result line only
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="smollm", choices=["smollm", "moe", "cp", "pp"],
+                    help="smollm = the headline configuration; the others are described in benchmarks/config_specs.py")
+    ap.add_argument("--variant", default=None, help="moe: capacity|dropless, cp: ring|ulysses, pp: interleaved|zb|1f1b|afab")
+    ap.add_argument("--layers", type=int, default=0, help="non-headline configurations only: reduced depth for quick checks")
+    ap.add_argument("--seq", type=int, default=0, help="non-headline configurations only: sequence length override")
     args = ap.parse_args()
-    assert args.gpus in LAYOUTS, f"--gpus must be one of {sorted(LAYOUTS)}"
     args.warmup = max(3, args.warmup)   # never time a cold run
+    if args.config != "smollm":
+        run_config(args)
+        return
+    assert args.gpus in LAYOUTS, f"--gpus must be one of {sorted(LAYOUTS)}"
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -24,72 +24,28 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from benchmarks.config_specs import flops_per_token, make_spec  # noqa: E402
 from picotron_b200 import ops  # noqa: E402
 from picotron_b200.engine import TrainEngine  # noqa: E402
 
 
 def build_cfg(args, world):
-    if args.config == "pp":
-        tp = 2 if world >= 4 else 1
-        pp = 2 if world >= 2 else 1
-        dp = world // (tp * pp)
-        layers = args.layers or 32
-        return {
-            "distributed": dict(tp_size=tp, pp_size=pp, dp_size=dp, pp_engine=args.pp_engine, num_virtual_stages=2,
-                                sequence_parallel=tp > 1, vocab_parallel_ce=tp > 1, zero_stage=1 if dp > 1 else 0),
-            "model": dict(name="meta-llama/Llama-2-7b-hf", num_hidden_layers=layers, init_std=0.02),
-            "training": dict(seed=1, learning_rate=3e-4, seq_length=args.seq or 4096, micro_batch_size=1,
-                             gradient_accumulation_steps=16, num_samples=1 << 14),
-            "dataset": dict(name="synthetic"),
-        }, f"tp{tp}xpp{pp}xdp{dp} {args.pp_engine}"
+    """(engine config, label) of a configuration; the definitions live in ``config_specs``."""
+    variant = {"pp": args.pp_engine, "cp": args.cp_attention,
+               "moe": "capacity" if args.capacity > 0 else "dropless"}[args.config]
+    spec = make_spec(args.config, world, variant, args.layers, args.seq)
+    cfg = spec["engine_cfg"]
     if args.config == "moe":
-        layers = args.layers or 16
-        return {
-            "distributed": dict(ep_size=world, ep_as_dp=world > 1),
-            "model": dict(name="moe-ep8-bench", num_hidden_layers=layers, init_std=0.02, num_experts=64,
-                          num_experts_per_tok=6, num_shared_experts=0, shared_expert_intermediate_size=2048,
-                          ep_capacity_factor=args.capacity, ep_capacity_dropless=args.dropless, ep_fp8_dispatch=True,
-                          ep_num_tiles=4, router_aux_loss_coef=1e-3, router_bias_update_rate=1e-3,
-                          ep_backend=args.ep_backend),
-            "training": dict(seed=1, learning_rate=3e-4, seq_length=args.seq or 4096, micro_batch_size=2,
-                             gradient_accumulation_steps=1, num_samples=1 << 14),
-            "dataset": dict(name="synthetic"),
-        }, (f"ep{world} capacity{args.capacity} {'dropless' if args.dropless else 'drop'} fp8-dispatch"
-            if args.capacity > 0 else
-            (f"ep{world} dropless, peer-memory exchange with device-side layout" if args.ep_backend == "fused"
-             else f"ep{world} tiled-4 variable-size exchange fp8-dispatch"))
-    if args.config == "cp":
-        layers = args.layers or 16
-        seq = args.seq or 16384 * world
-        return {
-            "distributed": dict(cp_size=world, cp_attention=args.cp_attention),
-            "model": dict(name="long-context-bench", num_hidden_layers=layers, init_std=0.02,
-                          max_position_embeddings=seq),
-            "training": dict(seed=1, learning_rate=3e-4, seq_length=seq, micro_batch_size=1,
-                             gradient_accumulation_steps=1, num_samples=256),
-            "dataset": dict(name="synthetic"),
-        }, f"cp{world} {args.cp_attention}"
-    raise SystemExit(f"unknown config {args.config}")
+        cfg["model"]["ep_capacity_dropless"] = bool(args.dropless)
+        if args.capacity <= 0:
+            cfg["model"]["ep_backend"] = args.ep_backend
+        else:
+            cfg["model"]["ep_capacity_factor"] = args.capacity
+    return cfg, spec["label"]
 
 
-def active_params(mc) -> float:
-    """Parameters that take part in one token's forward pass (routed experts count top-k times)."""
-    h, L, v = mc.hidden_size, mc.num_hidden_layers, mc.vocab_size
-    hd = h // mc.num_attention_heads
-    attn = 2 * h * h + 2 * h * mc.num_key_value_heads * hd
-    ffn = 3 * h * mc.intermediate_size
-    experts = getattr(mc, "num_experts", 1) or 1
-    if experts > 1:
-        shared = getattr(mc, "shared_expert_intermediate_size", None) or \
-            mc.intermediate_size * (getattr(mc, "num_shared_experts", 0) or 0)
-        ffn = mc.num_experts_per_tok * 3 * h * mc.intermediate_size + 3 * h * shared + h * experts
-    return L * (attn + ffn) + v * h
-
-
-def mfu_percent(mc, seq_len: int, tokens_per_s_per_gpu: float, peak_flops: float) -> float:
-    """The reference's formula (picotron/utils.py:51-62) on the active parameters."""
-    flops_per_token = 6 * active_params(mc) + 12 * mc.num_hidden_layers * mc.hidden_size * seq_len
-    return 100.0 * tokens_per_s_per_gpu * flops_per_token / peak_flops
+def mfu_percent(mc, seq_len: int, tokens_per_s_per_gpu: float, peak_flops: float, model: dict) -> float:
+    return 100.0 * tokens_per_s_per_gpu * flops_per_token(model, seq_len) / peak_flops
 
 
 def main():
@@ -141,15 +97,19 @@ def main():
         step_ms = ms.item() / args.steps
         from picotron_b200.runtime.timing import measured_peaks
         tps = eng.tokens_per_step / step_ms * 1e3
+        variant = {"pp": args.pp_engine, "cp": args.cp_attention,
+                   "moe": "capacity" if args.capacity > 0 else "dropless"}[args.config]
+        model = make_spec(args.config, world, variant, args.layers, args.seq)["model"]
         mfu_b200 = mfu_percent(eng.model_config, cfg["training"]["seq_length"], tps / world,
-                               measured_peaks()["bf16_tflops"] * 1e12)
-        mfu_h100 = mfu_percent(eng.model_config, cfg["training"]["seq_length"], tps / world, 989.5e12)
+                               measured_peaks()["bf16_tflops"] * 1e12, model)
+        mfu_h100 = mfu_percent(eng.model_config, cfg["training"]["seq_length"], tps / world, 989.5e12, model)
         print(json.dumps({"mfu_percent_b200_measured_peak": round(mfu_b200, 2),
                           "mfu_percent_h100_constant": round(mfu_h100, 2),"config": args.config, "layout": label, "n_gpus": world, "layers": cfg["model"]["num_hidden_layers"],
                           "seq_len": cfg["training"]["seq_length"], "tokens_per_step": eng.tokens_per_step,
                           "ms_per_step": round(step_ms, 2), "tokens_per_s": round(eng.tokens_per_step / step_ms * 1e3, 1),
                           "loss": round(lossv, 4), "peak_mem_gib": round(mem.item(), 1),
                           "gpu_launches": ops.launches() - l0, "steps": args.steps, "warmup": args.warmup}), flush=True)
+    eng.close()
     dist.destroy_process_group()
 
 
