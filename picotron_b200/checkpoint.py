@@ -22,9 +22,11 @@ Added on top, all ignorable by a reader of the reference format:
 
 ``init_model_with_dematerialized_weights`` / ``init_model_with_materialized_weights`` give the
 meta-device construction path of the reference (checkpoint.py:17-121): build without memory,
-then materialise and initialise; when a directory of Hugging Face safetensors is given, the
-shapes are validated against it before the parameters are (re-)initialised, as the reference
-does (it reads the files but always trains from random init, checkpoint.py:114-119).
+then materialise and initialise. ``InitializationManager`` locates this rank's tensors in a
+directory of Hugging Face safetensors (single file or sharded), cuts out its tensor-parallel
+slice and can load it; by default the values are only checked and the model is initialised
+randomly, as the reference does (it reads the files but always trains from random init,
+checkpoint.py:114-119).
 """
 from __future__ import annotations
 
@@ -49,44 +51,166 @@ def init_model_with_dematerialized_weights(include_buffers: bool = False):
 
 
 def init_model_with_materialized_weights(model: nn.Module, model_config=None, save_dir: Optional[str] = None,
-                                         device="cpu"):
-    """Allocate real storage for a meta-constructed model and run its initialisers."""
-    if save_dir is not None and os.path.isdir(save_dir):
-        _validate_against_safetensors(model, save_dir)
+                                         device="cpu", load_pretrained: bool = False):
+    """Allocate real storage for a meta-constructed model and initialise it.
+
+    With a directory of Hugging Face safetensors (``save_dir``) this rank's tensors are located in
+    the (single-file or sharded) checkpoint, checked against the local parameter shapes and — with
+    ``load_pretrained`` — copied in, each rank reading only its own tensor-parallel slice. The
+    default keeps the reference's behaviour, which reads the files and then trains from random
+    initialisation anyway (checkpoint.py:114-119)."""
+    manager = InitializationManager(model, model_config)
+    tensors = {}
+    if save_dir is not None and os.path.isdir(save_dir) and manager.has_safetensors(save_dir):
+        tensors = manager.read_local_tensors(save_dir, load_values=load_pretrained)
     model.to_empty(device=device)
-    with torch.no_grad():
-        # leaves own the initialisers; containers (Attention, MLP, MoELayer, ...) only delegate
-        for mod in model.modules():
-            if hasattr(mod, "reset_parameters") and next(mod.children(), None) is None:
-                mod.reset_parameters()
-        for _, buf in model.named_buffers():
-            buf.zero_()
+    manager.init_model_parameters()
+    if load_pretrained:
+        manager.copy_into_model(tensors)
     assert_no_meta_tensors(model)
     return model
 
 
-def _validate_against_safetensors(model, save_dir):
-    try:
+class InitializationManager:
+    """Maps this rank's parameters to the tensors of a Hugging Face Llama checkpoint and loads them
+    (picotron/checkpoint.py:124-267 — ``get_layer_names_in_sft_format``, ``adjust_tensor_size``,
+    ``convert_safetensors_to_hf_name`` — re-done on top of the model's own parameter names: a
+    pipeline stage holds its layers under their global indices and tensor-parallel layers hold
+    their shard, so the wanted names and slices follow from ``named_parameters()`` and the local
+    shapes instead of from a separate description of the layout)."""
+
+    _RENAMES = (("decoder_layers.", "model.layers."), ("attention.", "self_attn."), ("out_proj", "o_proj"))
+    _TOP_LEVEL = {"embedding.weight": "model.embed_tokens.weight", "final_norm.weight": "model.norm.weight",
+                  "final_proj.weight": "lm_head.weight"}
+
+    def __init__(self, model: nn.Module, model_config=None, tp_rank: Optional[int] = None,
+                 tp_world_size: Optional[int] = None):
+        self.model, self.model_config = model, model_config
+        if tp_rank is None or tp_world_size is None:
+            m = pgm.process_group_manager
+            tp_rank = m.tp_rank if m is not None else 0
+            tp_world_size = m.tp_world_size if m is not None else 1
+        self.tp_rank, self.tp_world_size = tp_rank, tp_world_size
+
+    # ---------------------------------------------------------------------------------- names
+    def hf_name(self, param_name: str) -> Optional[str]:
+        """Checkpoint name of one of this model's parameters, or None when the dense checkpoint has
+        no such tensor (routed experts, router, shared expert, latent projections)."""
+        if param_name in self._TOP_LEVEL:
+            return self._TOP_LEVEL[param_name]
+        if not param_name.startswith("decoder_layers."):
+            return None
+        moe = getattr(self.model_config, "num_experts", 1) and getattr(self.model_config, "num_experts", 1) > 1
+        if ".mlp." in param_name and moe:
+            return None
+        name = param_name
+        for old, new in self._RENAMES:
+            name = name.replace(old, new)
+        return name
+
+    def get_layer_names_in_sft_format(self):
+        """Checkpoint tensor names this rank needs (its pipeline stage's layers; its MoE layers skip
+        the dense feed-forward weights)."""
+        return [n for n in (self.hf_name(k) for k, _ in self.model.named_parameters()) if n is not None]
+
+    @staticmethod
+    def convert_safetensors_to_hf_name(sft_name: str) -> str:
+        """Checkpoint tensor name -> this package's parameter name."""
+        for ours, theirs in InitializationManager._TOP_LEVEL.items():
+            if sft_name == theirs:
+                return ours
+        name = sft_name
+        for ours, theirs in reversed(InitializationManager._RENAMES):
+            name = name.replace(theirs, ours)
+        return name
+
+    # ---------------------------------------------------------------------------------- files
+    @staticmethod
+    def has_safetensors(save_dir: str) -> bool:
+        return any(f.endswith(".safetensors") for f in os.listdir(save_dir))
+
+    @staticmethod
+    def _locate(save_dir: str):
+        """{checkpoint tensor name: file} from the shard index, or by listing the files' keys."""
         from safetensors import safe_open
-    except ImportError:
-        return
-    files = [f for f in os.listdir(save_dir) if f.endswith(".safetensors")]
-    shapes = {}
-    for f in files:
-        with safe_open(os.path.join(save_dir, f), framework="pt") as fh:
-            for k in fh.keys():
-                shapes[k] = tuple(fh.get_slice(k).get_shape())
-    hf_names = {"embedding.weight": "model.embed_tokens.weight", "final_norm.weight": "model.norm.weight",
-                "final_proj.weight": "lm_head.weight"}
-    for name, p in model.named_parameters():
-        hf = hf_names.get(name)
-        if hf is None and name.startswith("decoder_layers."):
-            hf = ("model.layers." + name[len("decoder_layers."):]).replace("attention.", "self_attn.") \
-                .replace("out_proj", "o_proj")
-        if hf in shapes and len(shapes[hf]) == p.dim():
-            full = shapes[hf]
-            ok = all(a == b or a % b == 0 for a, b in zip(full, p.shape))
-            assert ok, f"{name}: local shape {tuple(p.shape)} does not tile checkpoint shape {full}"
+        index_path = os.path.join(save_dir, "model.safetensors.index.json")
+        if os.path.exists(index_path):
+            with open(index_path) as fh:
+                return {k: os.path.join(save_dir, v) for k, v in json.load(fh)["weight_map"].items()}
+        where = {}
+        for f in sorted(os.listdir(save_dir)):
+            if f.endswith(".safetensors"):
+                with safe_open(os.path.join(save_dir, f), framework="pt") as fh:
+                    for k in fh.keys():
+                        where[k] = os.path.join(save_dir, f)
+        return where
+
+    def adjust_tensor_size(self, full_shape, local_shape, name: str = ""):
+        """Index expression (a tuple of slices) that cuts this rank's shard out of a checkpoint tensor
+        of ``full_shape``: the dimension in which the local parameter is ``tp`` times smaller is
+        split by rank; a dimension that is merely larger in the checkpoint (the config asked for
+        fewer heads or layers' worth of rows) is truncated. Raises if the local shape cannot be
+        obtained that way."""
+        assert len(full_shape) == len(local_shape), f"{name}: rank mismatch {full_shape} vs {local_shape}"
+        out = []
+        for full, local in zip(full_shape, local_shape):
+            if full == local:
+                out.append(slice(0, local))
+            elif full == local * self.tp_world_size:
+                out.append(slice(self.tp_rank * local, (self.tp_rank + 1) * local))
+            elif full > local:
+                out.append(slice(0, local))
+            else:
+                raise ValueError(f"{name}: checkpoint shape {tuple(full_shape)} cannot provide local shape "
+                                 f"{tuple(local_shape)} (tp={self.tp_world_size})")
+        return tuple(out)
+
+    def read_local_tensors(self, save_dir: str, load_values: bool = True):
+        """{parameter name: tensor or None}: every local parameter that has a checkpoint tensor is
+        checked against it and, with ``load_values``, this rank's slice of it is read (only the slice
+        is read from disk). Parameters without a counterpart (MoE weights, an lm head absent because
+        the checkpoint ties it to the embedding) are left out."""
+        from safetensors import safe_open
+        where = self._locate(save_dir)
+        out, handles = {}, {}
+        try:
+            for pname, p in self.model.named_parameters():
+                hf = self.hf_name(pname)
+                if hf is None or hf not in where:
+                    continue
+                path = where[hf]
+                if path not in handles:
+                    handles[path] = safe_open(path, framework="pt", device="cpu")
+                sl = handles[path].get_slice(hf)
+                index = self.adjust_tensor_size(tuple(sl.get_shape()), tuple(p.shape), pname)
+                out[pname] = sl[index] if load_values else None
+        finally:
+            for h in handles.values():
+                if hasattr(h, "__exit__"):
+                    h.__exit__(None, None, None)
+        return out
+
+    # ---------------------------------------------------------------------------------- init
+    def init_model_parameters(self):
+        """Run the initialisers: leaves own them; containers (Attention, MLP, MoELayer, ...) delegate."""
+        with torch.no_grad():
+            for mod in self.model.modules():
+                if hasattr(mod, "reset_parameters") and next(mod.children(), None) is None:
+                    mod.reset_parameters()
+            for _, buf in self.model.named_buffers():
+                buf.zero_()
+
+    def copy_into_model(self, tensors) -> int:
+        """Copy the loaded slices into the parameters (in place: they may be views of a flat buffer).
+        Returns the number of parameters filled."""
+        n = 0
+        params = dict(self.model.named_parameters())
+        with torch.no_grad():
+            for name, t in tensors.items():
+                if t is not None:
+                    params[name].copy_(t.to(params[name].dtype))
+                    n += 1
+        return n
 
 
 class CheckpointManager:

@@ -35,6 +35,10 @@ def _worker(rank, world, port, fn, errors):
             dist.destroy_process_group()
 
 
+#: world sizes every multi-GPU test runs at (those the machine has; the rest are skipped)
+WORLDS = [2, 4, 8]
+
+
 def run_gpu_ranks(fn, world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -117,8 +121,9 @@ def _fused_ops_worker(rank, world):
     ops.check_status("fused tp")
 
 
-def test_fused_tp_ops_2gpu():
-    run_gpu_ranks(_fused_ops_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_tp_ops(world):
+    run_gpu_ranks(_fused_ops_worker, world)
 
 
 def _timeout_worker(rank, world):
@@ -141,8 +146,22 @@ def _timeout_worker(rank, world):
     assert t[0].item() == sum(range(1, world + 1))
 
 
-def test_bounded_wait_reports_timeout_2gpu():
-    run_gpu_ranks(_timeout_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_bounded_wait_reports_timeout(world):
+    run_gpu_ranks(_timeout_worker, world)
+
+
+def _tp_engine_cfg(tp, dp, zero_stage=0):
+    """Small Llama whose heads, KV heads and sequence divide by every tested TP size (head_dim 64, a
+    sequence shard of 128 rows per rank)."""
+    return {"distributed": dict(tp_size=tp, dp_size=dp, sequence_parallel=True, vocab_parallel_ce=True,
+                                zero_stage=zero_stage),
+            "model": dict(name="tiny-llama-test", init_std=0.02, dtype="bfloat16", num_hidden_layers=2,
+                          hidden_size=1024, intermediate_size=2048, num_attention_heads=16, num_key_value_heads=8,
+                          max_position_embeddings=128 * tp),
+            "training": dict(seed=0, learning_rate=1e-3, seq_length=128 * tp, micro_batch_size=2,
+                             gradient_accumulation_steps=2, num_samples=512),
+            "dataset": dict(name="synthetic")}
 
 
 def _engine_worker(rank, world):
@@ -153,12 +172,7 @@ def _engine_worker(rank, world):
     losses = {}
     for fused in ("1", "0"):
         os.environ["PICO_FUSED_TP"] = fused
-        cfg = {"distributed": dict(tp_size=world, dp_size=1, sequence_parallel=True, vocab_parallel_ce=True),
-               "model": dict(name="tiny-llama-test", init_std=0.02, dtype="bfloat16", num_hidden_layers=2,
-                             hidden_size=512, intermediate_size=1024, num_attention_heads=8, num_key_value_heads=4),
-               "training": dict(seed=0, learning_rate=1e-3, seq_length=256, micro_batch_size=2,
-                                gradient_accumulation_steps=2, num_samples=512),
-               "dataset": dict(name="synthetic")}
+        cfg = _tp_engine_cfg(world, 1)
         eng = TrainEngine(cfg, device=torch.device("cuda", rank))
         assert (eng.fused_tp is not None) == (fused == "1")
         losses[fused] = [eng.train_step().item() for _ in range(3)]
@@ -176,8 +190,42 @@ def _engine_worker(rank, world):
     assert eager == losses["1"], (eager, losses["1"])
 
 
-def test_engine_fused_tp_matches_nccl_path_2gpu():
-    run_gpu_ranks(_engine_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_engine_fused_tp_matches_nccl_path(world):
+    run_gpu_ranks(_engine_worker, world)
+
+
+def _engine_dp_tp_worker(rank, world):
+    """DP2 x TP(world/2) with sequence parallelism, vocabulary-parallel loss and ZeRO-1 — the layout of
+    the 8-GPU headline run: every fused path on (peer-memory TP kernels, graph replay, one-launch
+    ZeRO-1 optimizer) against the same layout on NCCL collectives; losses over three steps, the
+    parameters afterwards, and identical replicas."""
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.engine import TrainEngine
+    out = {}
+    for fused in ("1", "0"):
+        os.environ["PICO_FUSED_TP"] = os.environ["PICO_FUSED_DP"] = fused
+        pgm.process_group_manager = None
+        eng = TrainEngine(_tp_engine_cfg(world // 2, 2, zero_stage=1), device=torch.device("cuda", rank))
+        assert (eng.fused_tp is not None) == (fused == "1") and (eng.dp_symm is not None) == (fused == "1")
+        losses = [eng.average_loss(eng.train_step()) for _ in range(3)]
+        ops.check_status("dp x tp engine fused=" + fused)
+        params = eng.store.flat_params.float().clone()
+        other = params.clone()
+        dist.broadcast(other, src=dist.get_global_rank(eng.pgm.dp_group, 0), group=eng.pgm.dp_group)
+        assert torch.equal(other, params), "data-parallel replicas diverged"
+        out[fused] = (losses, params)
+        eng.close()
+    for a, b in zip(out["1"][0], out["0"][0]):
+        assert abs(a - b) < 3e-2, (out["1"][0], out["0"][0])
+    rel = (out["1"][1] - out["0"][1]).norm() / out["0"][1].norm()
+    assert rel < 1e-2, rel
+    os.environ["PICO_FUSED_TP"] = os.environ["PICO_FUSED_DP"] = "1"
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_engine_dp2_tp_zero1_matches_nccl_path(world):
+    run_gpu_ranks(_engine_dp_tp_worker, world)
 
 
 def _dp_engine_worker(rank, world):
@@ -210,8 +258,9 @@ def _dp_engine_worker(rank, world):
     assert rel < 1e-2, rel
 
 
-def test_engine_fused_zero1_matches_nccl_path_2gpu():
-    run_gpu_ranks(_dp_engine_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_engine_fused_zero1_matches_nccl_path(world):
+    run_gpu_ranks(_dp_engine_worker, world)
 
 
 def _ep_worker(rank, world):
@@ -255,8 +304,9 @@ def _ep_worker(rank, world):
                 assert rel < 3e-2, (n, fp8, dropless, rel)
 
 
-def test_fused_ep_capacity_moe_2gpu():
-    run_gpu_ranks(_ep_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_ep_capacity_moe(world):
+    run_gpu_ranks(_ep_worker, world)
 
 
 def _cp_worker(rank, world):
@@ -269,7 +319,7 @@ def _cp_worker(rank, world):
     pgm.setup_process_group_manager(tp_size=1, cp_size=world, pp_size=1, dp_size=1)
     dev = torch.device("cuda", rank)
     torch.manual_seed(0)
-    b, s, H, Hkv, d = 1, 512 * world, 8, 4, 64
+    b, s, H, Hkv, d = 1, 512 * world, 16, 8, 64      # Ulysses splits both head counts over the ranks
     q = torch.randn(b, s, H, d, device=dev, dtype=torch.bfloat16)
     k = torch.randn(b, s, Hkv, d, device=dev, dtype=torch.bfloat16)
     v = torch.randn(b, s, Hkv, d, device=dev, dtype=torch.bfloat16)
@@ -288,8 +338,9 @@ def _cp_worker(rank, world):
             assert _rel(got, want[:, sl]) < 3e-2, fn.__name__
 
 
-def test_context_parallel_attention_2gpu():
-    run_gpu_ranks(_cp_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_context_parallel_attention(world):
+    run_gpu_ranks(_cp_worker, world)
 
 
 def _fused_cp_worker(rank, world):
@@ -332,8 +383,9 @@ def _fused_cp_worker(rank, world):
         cpar.install_fused_cp(None)
 
 
-def test_fused_context_parallel_attention_2gpu():
-    run_gpu_ranks(_fused_cp_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_context_parallel_attention(world):
+    run_gpu_ranks(_fused_cp_worker, world)
 
 
 def _fused_ulysses_worker(rank, world):
@@ -347,7 +399,7 @@ def _fused_ulysses_worker(rank, world):
     pgm.setup_process_group_manager(tp_size=1, cp_size=world, pp_size=1, dp_size=1)
     group = pgm.get_pgm().cp_group
     dev = torch.device("cuda", rank)
-    b, s_loc, H, Hkv, d = 2, 256, 8, 2 * world, 64
+    b, s_loc, H, Hkv, d = 2, 256, 4 * world, 2 * world, 64
     s = s_loc * world
     u = UlyssesFused(SymmGroup(group, device=dev), b, s_loc, H * d)
     uly.install_fused_ulysses(u)
@@ -375,8 +427,9 @@ def _fused_ulysses_worker(rank, world):
         uly.install_fused_ulysses(None)
 
 
-def test_fused_ulysses_attention_2gpu():
-    run_gpu_ranks(_fused_ulysses_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_ulysses_attention(world):
+    run_gpu_ranks(_fused_ulysses_worker, world)
 
 
 def _ep_var_worker(rank, world):
@@ -398,8 +451,10 @@ def _ep_var_worker(rank, world):
     torch.manual_seed(3)
     layer = MoELayer(cfg).to(dev).to(torch.bfloat16)
     T = 512
-    epv_bf16 = EPVarFused(sg, layer.num_local_experts, 512, T * 2, slack=2.0)
-    epv_fp8 = EPVarFused(sg, layer.num_local_experts, 512, T * 2, slack=2.0, fp8_dispatch=True)
+    # the router is skewed on purpose: with few experts per rank one rank can receive most rows
+    slack = 2.0 if world == 2 else float(world)
+    epv_bf16 = EPVarFused(sg, layer.num_local_experts, 512, T * 2, slack=slack)
+    epv_fp8 = EPVarFused(sg, layer.num_local_experts, 512, T * 2, slack=slack, fp8_dispatch=True)
     assert epv_fp8.fp8
     for rnd in range(4):
         epv = epv_fp8 if rnd == 3 else epv_bf16      # last round: FP8 block-scaled forward dispatch
@@ -430,5 +485,6 @@ def _ep_var_worker(rank, world):
     layer.fused_ep_var = None
 
 
-def test_fused_dropless_ep_2gpu():
-    run_gpu_ranks(_ep_var_worker, 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_dropless_ep(world):
+    run_gpu_ranks(_ep_var_worker, world)
