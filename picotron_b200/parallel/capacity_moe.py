@@ -23,10 +23,17 @@ def compute_capacity(num_tokens: int, top_k: int, num_experts: int, factor: floa
     return max(1, int(factor * num_tokens * top_k / num_experts + 0.999))
 
 
+def expert_counts(expert_idx: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Rows per expert (int64). ``scatter_add`` instead of ``bincount``: the latter reads the maximum
+    back to the host on CUDA, which stalls the stream and cannot be captured in a CUDA graph."""
+    return torch.zeros(num_experts, dtype=torch.int64, device=expert_idx.device).scatter_add_(
+        0, expert_idx, torch.ones_like(expert_idx, dtype=torch.int64))
+
+
 def slot_assignment(expert_idx: torch.Tensor, num_experts: int) -> torch.Tensor:
     """slot[i] = number of earlier rows routed to the same expert as row i."""
     order = torch.argsort(expert_idx, stable=True)
-    counts = torch.bincount(expert_idx, minlength=num_experts)
+    counts = expert_counts(expert_idx, num_experts)
     starts = torch.cumsum(counts, 0) - counts
     sorted_expert = expert_idx[order]
     pos = torch.arange(order.numel(), device=expert_idx.device) - starts[sorted_expert]
@@ -45,15 +52,18 @@ def _capacity_moe_fused(layer, epf, tokens, expert_idx, weights, token_idx, num_
     y = torch.zeros((num_tokens, d), device=tokens.device, dtype=torch.float32)
     rows = torch.arange(R, device=tokens.device, dtype=torch.int32)
     for r in range(rounds):
+        # no boolean-mask indexing or nonzero(): those read sizes back to the host. Rows outside this
+        # round are routed to a spare table entry (index E*C) on the way out and weighted by zero on
+        # the way back, so every tensor keeps a static shape.
         in_round = (slot >= r * C) & (slot < (r + 1) * C)
-        idx = expert_idx * C + (slot - r * C)
-        row_of_slot = torch.full((E * C,), -1, device=tokens.device, dtype=torch.int32)
-        row_of_slot[idx[in_round]] = rows[in_round]
-        x = fused_ep.dispatch(tokens, row_of_slot, layer.top_k, epf, bool(layer.ep_fp8_dispatch))   # [L, ep*C, d]
+        idx = torch.where(in_round, expert_idx * C + (slot - r * C), torch.full_like(slot, E * C))
+        row_of_slot = torch.full((E * C + 1,), -1, device=tokens.device, dtype=torch.int32)
+        row_of_slot.scatter_(0, idx, rows)
+        x = fused_ep.dispatch(tokens, row_of_slot[:E * C], layer.top_k, epf, bool(layer.ep_fp8_dispatch))  # [L, ep*C, d]
         out = layer.experts_uniform(x)
         back = fused_ep.combine(out, epf)                                                           # [E*C, d]
-        sel = torch.nonzero(in_round).squeeze(1)
-        y = y.index_add(0, token_idx[sel], back[idx[sel]].float() * weights[sel].float().unsqueeze(-1))
+        contrib = back[idx.clamp(max=E * C - 1)].float() * weights.float().unsqueeze(-1)
+        y = y.index_add(0, token_idx, torch.where(in_round.unsqueeze(-1), contrib, torch.zeros_like(contrib)))
     dropped = (slot >= rounds * C).float().mean()
     return y.to(tokens.dtype), dropped
 
@@ -66,7 +76,7 @@ def capacity_moe(layer, routed, expert_idx, weights, token_idx, num_tokens: int,
     slot = slot_assignment(expert_idx, E)
     rounds = 1
     if dropless:
-        max_count = torch.bincount(expert_idx, minlength=E).max()
+        max_count = expert_counts(expert_idx, E).max()
         need = torch.clamp((max_count + C - 1) // C, min=1, max=max_rounds).to(torch.int64)
         if ep > 1:
             dist.all_reduce(need, op=dist.ReduceOp.MAX, group=layer.ep_group)

@@ -266,7 +266,8 @@ class MoELayer(nn.Module):
         from ..ops import fused_ep_var as fv
         epv = self.fused_ep_var
         order, inv = _argsort_inv(expert_idx)
-        counts = torch.bincount(expert_idx, minlength=self.num_experts).to(torch.int32)
+        from .capacity_moe import expert_counts
+        counts = expert_counts(expert_idx, self.num_experts).to(torch.int32)
         plan = epv.plan(counts)
         recv = fv.var_dispatch(routed[order], plan, epv)
         y_pad = self._experts_on_layout(recv, plan.layout, rows_in_use=plan.seg_start[self.num_local_experts:])
@@ -291,7 +292,7 @@ class MoELayer(nn.Module):
         topk_idx, topk_w = self._route(tokens)
         shared = self._shared_start(tokens)
         latent = self.down_proj_latent(tokens) if self.latent else tokens
-        token_idx = torch.arange(T, device=tokens.device).repeat_interleave(self.top_k)
+        token_idx = torch.arange(T, device=tokens.device).repeat_interleave(self.top_k, output_size=T * self.top_k)
         routed = latent[token_idx]                       # [T*k, d] token-major
         expert_idx = topk_idx.reshape(-1)
         weights = topk_w.reshape(-1)

@@ -289,3 +289,45 @@ def test_dropless_layout_reference_is_consistent_across_ranks():
             assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
         used = seg_start[L] // 128
         assert all(t >= 0 for t in tiles[:used]) and all(t == -1 for t in tiles[used:])
+
+
+def test_fused_capacity_routing_matches_plain_path(monkeypatch):
+    """The bookkeeping around the peer-memory exchange kernels of the capacity path (slot table
+    without boolean-mask indexing, masked weighted sum) against the plain path, with the two exchange
+    kernels emulated by their definition on one rank: outputs, dropped fraction and gradients."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.ops import fused_ep
+    from picotron_b200.parallel import capacity_moe as cm
+    from picotron_b200.parallel.expert_parallel import MoELayer
+
+    pgm.setup_process_group_manager(tp_size=1, cp_size=1, pp_size=1, dp_size=1, ep_size=1)
+    for dropless in (False, True):
+        cfg = moe_config(ep_capacity_factor=0.5, ep_capacity_dropless=dropless, num_shared_experts=0)
+        torch.manual_seed(4)
+        layer = MoELayer(cfg)
+        T, k, E, d = 24, cfg.num_experts_per_tok, cfg.num_experts, cfg.hidden_size
+        C = cm.compute_capacity(T, k, E, cfg.ep_capacity_factor)
+        tokens = torch.randn(T, d, requires_grad=True)
+        expert_idx = torch.randint(0, E, (T * k,))
+        weights = torch.rand(T * k, requires_grad=True)
+        token_idx = torch.arange(T).repeat_interleave(k)
+        slot = cm.slot_assignment(expert_idx, E)
+        rounds = int(((cm.expert_counts(expert_idx, E).max() + C - 1) // C).item()) if dropless else 1
+
+        def fake_dispatch(tok, row_of_slot, top_k, epf, quant):       # [E*C] rows -> [L, C, d] on one rank
+            valid = (row_of_slot >= 0).unsqueeze(-1)
+            src = tok[(row_of_slot.clamp_min(0) // top_k).long()]
+            return torch.where(valid, src, torch.zeros_like(src)).view(E, C, d)
+
+        monkeypatch.setattr(fused_ep, "dispatch", fake_dispatch)
+        monkeypatch.setattr(fused_ep, "combine", lambda out, epf: out.reshape(E * C, d))
+        epf = types.SimpleNamespace(C=C, d=d)
+        y1, drop1 = cm._capacity_moe_fused(layer, epf, tokens, expert_idx, weights, token_idx, T, slot, rounds)
+        g1 = torch.autograd.grad(y1.square().sum(), [tokens, weights])
+        y2, drop2 = cm.capacity_moe(layer, tokens[token_idx], expert_idx, weights, token_idx, T, C, dropless,
+                                    cfg.ep_max_rounds)
+        g2 = torch.autograd.grad(y2.square().sum(), [tokens, weights])
+        assert torch.allclose(y1, y2, atol=1e-5), (y1 - y2).abs().max()
+        assert abs(float(drop1) - float(drop2)) < 1e-6
+        for a, b in zip(g1, g2):
+            assert torch.allclose(a, b, atol=1e-4), (a - b).abs().max()
