@@ -92,3 +92,34 @@ def test_reference_import_paths_are_served():
         assert ours.process_group_manager is marker
     finally:
         ours.process_group_manager = old
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_protocol_model_finds_no_race_in_the_fused_tp_protocol(world):
+    """Random interleavings of ranks and streams over the operation list of the fused tensor-parallel
+    path: two alternating copies of each buffer, pushes on a communication stream, with and without
+    kept gather buffers (which need the barrier that opens a micro-batch)."""
+    from picotron_b200.runtime.protocol_model import build_program, simulate
+    for keep in (False, True):
+        prog = build_program(layers=3, micro_batches=3, keep_gathered=keep, barrier=keep)
+        for seed in range(25):
+            assert simulate(world, prog, seed) == [], (keep, seed)
+    # pushes on the main stream (PICO_TP_COMM_STREAM=0) are the same protocol with less freedom
+    prog = build_program(layers=2, micro_batches=2, keep_gathered=False, barrier=False, comm_stream=False)
+    for seed in range(10):
+        assert simulate(world, prog, seed) == []
+
+
+def test_protocol_model_detects_the_races_the_design_rules_out():
+    """The model has teeth: drop a rule and some schedule shows the race it prevents."""
+    from picotron_b200.runtime.protocol_model import build_program, simulate
+
+    def races(**kw):
+        prog = build_program(layers=2, micro_batches=3, **kw)
+        return any(simulate(3, prog, seed) for seed in range(60))
+
+    assert races(keep_gathered=True, barrier=False), \
+        "kept gather buffers without the barrier at the start of a micro-batch must race"
+    assert races(keep_gathered=False, barrier=False, double_buffer=False), \
+        "a single copy of the gather / staging buffers must race"
+    assert not races(keep_gathered=True, barrier=True)
