@@ -518,11 +518,21 @@ static int launch(const void* q, const void* k, const void* v, void* out, float*
 }
 
 }  // namespace pp
-
-int launch_fwd_pingpong(const void* q, const void* k, const void* v, void* out, float* lse,
-                        const PicoAttnParams* p, cudaStream_t stream) {
-  if (p->head_dim == 64) return pp::launch<64>(q, k, v, out, lse, p, stream);
-  return pp::launch<128>(q, k, v, out, lse, p, stream);
-}
-
 }  // namespace pico
+
+extern "C" int pico_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                                  const PicoAttnParams* p, cudaStream_t stream) {
+  if (p->batch <= 0 || p->seq_q <= 0 || p->heads <= 0) return 0;
+  if (p->heads % p->kv_heads != 0) {
+    pico_host::set_error("attention: heads (%d) must be a multiple of kv_heads (%d)", p->heads, p->kv_heads);
+    return -2;
+  }
+  if ((p->o_row_stride % 8) != 0 || (p->o_batch_stride % 8) != 0 || (reinterpret_cast<uintptr_t>(out) & 15)) {
+    pico_host::set_error("attention: output must be 16-byte aligned with strides that are multiples of 8");
+    return -2;
+  }
+  if (p->head_dim == 64) return pico::pp::launch<64>(q, k, v, out, lse, p, stream);
+  if (p->head_dim == 128) return pico::pp::launch<128>(q, k, v, out, lse, p, stream);
+  pico_host::set_error("attention: head_dim %d not supported (64 or 128)", p->head_dim);
+  return -2;
+}
