@@ -161,6 +161,83 @@ void accumulate_bf16_into_f32(const at::Tensor& src, at::Tensor& dst, int64_t n)
         "accumulate");
 }
 
+void moe_route(const at::Tensor& logits, const c10::optional<at::Tensor>& bias, at::Tensor& probs, at::Tensor& idx,
+               at::Tensor& w, at::Tensor& counts, int64_t k, bool renorm) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == at::kBFloat16 && logits.stride(1) == 1, "moe_route: bf16 [T, E] logits");
+  const int64_t T = logits.size(0), E = logits.size(1);
+  TORCH_CHECK(probs.scalar_type() == at::kFloat && probs.is_contiguous() && probs.numel() == T * E &&
+                  idx.scalar_type() == at::kInt && idx.is_contiguous() && idx.numel() == T * k &&
+                  w.scalar_type() == at::kFloat && w.is_contiguous() && w.numel() == T * k &&
+                  counts.scalar_type() == at::kInt && counts.numel() == E &&
+                  (!bias.has_value() || !bias->defined() || (bias->scalar_type() == at::kFloat && bias->numel() == E)),
+              "moe_route: output / bias tensors of the wrong type or size");
+  check(pico_moe_route(logits.data_ptr(), logits.stride(0), (const float*)cptr(bias), (float*)probs.data_ptr(),
+                       idx.data_ptr<int>(), (float*)w.data_ptr(), counts.data_ptr<int>(), (int)T, (int)E, (int)k,
+                       renorm ? 1 : 0, stream_of(logits)),
+        "moe_route");
+}
+
+void moe_route_bwd(const at::Tensor& probs, const at::Tensor& idx, const at::Tensor& w, const at::Tensor& dw,
+                   const c10::optional<at::Tensor>& dprobs, at::Tensor& dlogits, int64_t k, bool renorm) {
+  c10::cuda::CUDAGuard guard(probs.device());
+  const int64_t T = probs.size(0), E = probs.size(1);
+  TORCH_CHECK(probs.is_contiguous() && probs.scalar_type() == at::kFloat && dw.scalar_type() == at::kFloat &&
+                  dw.is_contiguous() && dw.numel() == T * k && dlogits.scalar_type() == at::kFloat &&
+                  dlogits.is_contiguous() && dlogits.numel() == T * E && idx.scalar_type() == at::kInt &&
+                  w.scalar_type() == at::kFloat &&
+                  (!dprobs.has_value() || !dprobs->defined() ||
+                   (dprobs->scalar_type() == at::kFloat && dprobs->is_contiguous() && dprobs->numel() == T * E)),
+              "moe_route_bwd: fp32 contiguous tensors of matching sizes");
+  check(pico_moe_route_bwd((const float*)probs.data_ptr(), idx.data_ptr<int>(), (const float*)w.data_ptr(),
+                           (const float*)dw.data_ptr(), (const float*)cptr(dprobs), (float*)dlogits.data_ptr(), (int)T,
+                           (int)E, (int)k, renorm ? 1 : 0, stream_of(probs)),
+        "moe_route_bwd");
+}
+
+void moe_slots(const at::Tensor& idx, int64_t E, int64_t C, at::Tensor& pos, const c10::optional<at::Tensor>& row_of_slot) {
+  c10::cuda::CUDAGuard guard(idx.device());
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_contiguous() && pos.scalar_type() == at::kInt &&
+                  pos.is_contiguous() && pos.numel() == idx.numel() &&
+                  (!row_of_slot.has_value() || !row_of_slot->defined() ||
+                   (row_of_slot->scalar_type() == at::kInt && row_of_slot->is_contiguous() && row_of_slot->numel() >= E * C)),
+              "moe_slots: int32 contiguous tensors");
+  check(pico_moe_slots(idx.data_ptr<int>(), (int)idx.numel(), (int)E, (int)C, pos.data_ptr<int>(),
+                       row_of_slot.has_value() && row_of_slot->defined() ? row_of_slot->data_ptr<int>() : nullptr,
+                       stream_of(idx)),
+        "moe_slots");
+}
+
+void moe_combine(const at::Tensor& out, const at::Tensor& idx, const at::Tensor& pos, const at::Tensor& w, at::Tensor& y,
+                 int64_t k, int64_t C) {
+  c10::cuda::CUDAGuard guard(out.device());
+  const int64_t T = y.size(0), d = y.size(1);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.size(-1) == d &&
+                  y.scalar_type() == at::kBFloat16 && y.is_contiguous() && idx.scalar_type() == at::kInt &&
+                  pos.scalar_type() == at::kInt && w.scalar_type() == at::kFloat && idx.numel() == T * k &&
+                  pos.numel() == T * k && w.numel() == T * k && idx.is_contiguous() && pos.is_contiguous() &&
+                  w.is_contiguous(),
+              "moe_combine: tensors of the wrong type or size");
+  check(pico_moe_combine(out.data_ptr(), idx.data_ptr<int>(), pos.data_ptr<int>(), (const float*)w.data_ptr(),
+                         y.data_ptr(), (int)T, (int)k, (int)C, (int)d, stream_of(out)),
+        "moe_combine");
+}
+
+void moe_combine_bwd(const at::Tensor& dy, const at::Tensor& out, const at::Tensor& row_of_slot, const at::Tensor& w,
+                     at::Tensor& dout, at::Tensor& dw, int64_t k) {
+  c10::cuda::CUDAGuard guard(out.device());
+  const int64_t slots = out.numel() / out.size(-1), d = out.size(-1);
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.size(-1) == d &&
+                  out.scalar_type() == at::kBFloat16 && out.is_contiguous() && dout.scalar_type() == at::kBFloat16 &&
+                  dout.is_contiguous() && dout.numel() == out.numel() && row_of_slot.scalar_type() == at::kInt &&
+                  row_of_slot.is_contiguous() && row_of_slot.numel() >= slots && w.scalar_type() == at::kFloat &&
+                  dw.scalar_type() == at::kFloat && w.is_contiguous() && dw.is_contiguous() && dw.numel() == w.numel(),
+              "moe_combine_bwd: tensors of the wrong type or size");
+  check(pico_moe_combine_bwd(dy.data_ptr(), out.data_ptr(), row_of_slot.data_ptr<int>(), (const float*)w.data_ptr(),
+                             dout.data_ptr(), (float*)dw.data_ptr(), slots, (int)k, (int)d, stream_of(out)),
+        "moe_combine_bwd");
+}
+
 void scale_unless_one(at::Tensor& x, const at::Tensor& scale) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && scale.scalar_type() == at::kFloat &&
@@ -585,6 +662,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("accumulate_bf16_into_f32", &accumulate_bf16_into_f32);
   m.def("fill_u32", &fill_u32);
   m.def("scale_unless_one", &scale_unless_one);
+  m.def("moe_route", &moe_route);
+  m.def("moe_route_bwd", &moe_route_bwd);
+  m.def("moe_slots", &moe_slots);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine_bwd", &moe_combine_bwd);
   m.def("status_fetch", &status_fetch);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);

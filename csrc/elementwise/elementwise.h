@@ -80,6 +80,28 @@ int pico_embedding_fwd(const void* W, const int64_t* ids, void* out, int rows, i
 int pico_embedding_bwd(const void* dout, const int64_t* ids, float* dW, int rows, int H, int Vlocal,
                        int vocab_start, cudaStream_t stream);
 
+// ---- mixture-of-experts routing (moe_route.cu) -----------------------------------------------
+// Router: logits bf16 [T, E] (row stride ldl, E <= 256) -> probs fp32 [T, E] (softmax), the k experts
+// with the largest probs (+ bias[e] when bias != NULL; ties to the lower index) in idx int32 [T, k],
+// their un-biased probabilities in w fp32 [T, k] (divided by their sum when renorm != 0 and k > 1),
+// and counts[e] += rows routed to e (int32 [E], zeroed by the caller). k <= 8.
+int pico_moe_route(const void* logits, int64_t ldl, const float* bias, float* probs, int32_t* idx, float* w,
+                   int32_t* counts, int T, int E, int k, int renorm, cudaStream_t stream);
+// dlogits fp32 [T, E] from dw fp32 [T, k] and, optionally, a dense gradient dprobs fp32 [T, E].
+int pico_moe_route_bwd(const float* probs, const int32_t* idx, const float* w, const float* dw,
+                       const float* dprobs, float* dlogits, int T, int E, int k, int renorm, cudaStream_t stream);
+// pos[r] = number of earlier routed rows with the same expert (idx int32 [R], row order); when
+// row_of_slot != NULL (int32 [E * C], -1 on entry) row_of_slot[e * C + pos] = r for pos < C.
+int pico_moe_slots(const int32_t* idx, int R, int E, int C, int32_t* pos, int32_t* row_of_slot,
+                   cudaStream_t stream);
+// y[t] = sum_j [pos[t,j] < C] w[t,j] * out[idx[t,j] * C + pos[t,j]] (out bf16 [E*C, d], y bf16 [T, d]).
+int pico_moe_combine(const void* out, const int32_t* idx, const int32_t* pos, const float* w, void* y, int T,
+                     int k, int C, int d, cudaStream_t stream);
+// dout[s] = w[row] * dy[row / k] and dw[row] = <dy[row / k], out[s]> with row = row_of_slot[s]
+// (dout[s] = 0 for empty slots; dw fp32 [T*k] zeroed by the caller).
+int pico_moe_combine_bwd(const void* dy, const void* out, const int32_t* row_of_slot, const float* w, void* dout,
+                         float* dw, int64_t slots, int k, int d, cudaStream_t stream);
+
 // ---- misc ---------------------------------------------------------------------------------
 // dst_f32 += src_bf16 (n elements); used to fold bf16 gradients into fp32 accumulators.
 int pico_accumulate_bf16_into_f32(const void* src, float* dst, int64_t n, cudaStream_t stream);

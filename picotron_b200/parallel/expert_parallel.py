@@ -140,14 +140,19 @@ class MoELayer(nn.Module):
         self._balance(probs, topk_idx)
         return topk_idx, topk_w.to(tokens.dtype)
 
-    def _balance(self, probs, topk_idx):
+    def _balance(self, probs, topk_idx, counts=None):
+        """Auxiliary balancing loss and loss-free bias update from this forward pass's routing;
+        ``counts`` (rows per expert) may come from the routing kernel."""
         self.aux_loss = None
         if not (self.training and (self.router_aux_loss_coef > 0 or self.use_loss_free)):
             return
         T = probs.shape[0]
-        counts = torch.zeros(self.num_experts, device=probs.device, dtype=probs.dtype)
-        counts.scatter_add_(0, topk_idx.reshape(-1), torch.ones(topk_idx.numel(), device=probs.device,
-                                                                dtype=probs.dtype))
+        if counts is None:
+            counts = torch.zeros(self.num_experts, device=probs.device, dtype=probs.dtype)
+            counts.scatter_add_(0, topk_idx.reshape(-1), torch.ones(topk_idx.numel(), device=probs.device,
+                                                                    dtype=probs.dtype))
+        else:
+            counts = counts.to(probs.dtype)
         if self.router_aux_loss_coef > 0:
             f = counts * (self.num_experts / (self.top_k * T))
             self.aux_loss = self.router_aux_loss_coef * (f * probs.mean(dim=0)).sum()
@@ -284,11 +289,48 @@ class MoELayer(nn.Module):
         back = epc.all_to_all(y[plan.regroup_inv], plan.in_splits, plan.out_splits, self.ep_group)
         return back[plan.inv_order]
 
+    def _device_routed_ok(self, tokens) -> bool:
+        """Capacity-limited dispatch through the peer-memory kernels with routing, slot assignment and
+        the weighted combine on the device (``ops.moe_route``): bf16 CUDA tokens, one round (rows over
+        capacity are dropped), a fused exchange context of matching capacity."""
+        epf = self.fused_ep
+        if epf is None or not tokens.is_cuda or tokens.dtype != torch.bfloat16 or self.ep_capacity_factor <= 0 \
+                or self.ep_capacity_dropless or self.ep_world_size == 1 or self.num_experts > 256 or self.top_k > 8:
+            return False
+        if os.environ.get("PICO_MOE_DEVICE_ROUTING", "1") == "0":
+            return False
+        from .capacity_moe import compute_capacity
+        return epf.C == compute_capacity(tokens.shape[0], self.top_k, self.num_experts, self.ep_capacity_factor) \
+            and epf.d == self.expert_dim
+
+    def _forward_device_routed(self, tokens):
+        """router GEMM -> route kernel -> slot kernel -> dispatch (peer memory, fp8 optional) -> grouped
+        experts -> combine exchange -> weighted-sum kernel: no eager sort / gather / index_add, nothing
+        read on the host."""
+        from ..ops import fused_ep
+        from ..ops import moe_route as mr
+        epf, T, k, E = self.fused_ep, tokens.shape[0], self.top_k, self.num_experts
+        logits = self.gate(tokens)
+        bias = self.expert_bias if self.use_loss_free else None
+        probs, idx, w, counts = mr.route(logits, bias, k, self.norm_topk_prob)
+        self._balance(probs, idx, counts)
+        shared = self._shared_start(tokens)
+        latent = self.down_proj_latent(tokens) if self.latent else tokens
+        pos, table = mr.slots(idx, E, epf.C)
+        x = fused_ep.dispatch(latent, table, k, epf, bool(self.ep_fp8_dispatch))      # [L, ep*C, d]
+        out = self.experts_uniform(x)
+        back = fused_ep.combine(out, epf)                                             # [E*C, d]
+        y = mr.combine(back, idx, pos.view(T, k), w, table, epf.C)
+        self.last_dropped_fraction = (pos >= epf.C).float().mean()
+        return self._finalize(y, shared)
+
     # ------------------------------------------------------------------------------ forward
     def forward(self, x):
         shape = x.shape
         tokens = x.reshape(-1, self.hidden_size)
         T = tokens.shape[0]
+        if self._device_routed_ok(tokens):
+            return self._forward_device_routed(tokens).view(shape)
         topk_idx, topk_w = self._route(tokens)
         shared = self._shared_start(tokens)
         latent = self.down_proj_latent(tokens) if self.latent else tokens
