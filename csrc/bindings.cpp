@@ -238,6 +238,25 @@ void moe_combine_bwd(const at::Tensor& dy, const at::Tensor& out, const at::Tens
         "moe_combine_bwd");
 }
 
+void attn_merge(const at::Tensor& out_a, const at::Tensor& lse_a, const at::Tensor& out_b, const at::Tensor& lse_b,
+                at::Tensor& out, at::Tensor& lse) {
+  c10::cuda::CUDAGuard guard(out_b.device());
+  TORCH_CHECK(out_a.dim() == 4 && out_a.sizes() == out_b.sizes() && out.sizes() == out_b.sizes() &&
+                  out_a.is_contiguous() && out_b.is_contiguous() && out.is_contiguous() &&
+                  out_b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kFloat &&
+                  (out_a.scalar_type() == at::kFloat || out_a.scalar_type() == at::kBFloat16),
+              "attn_merge: contiguous [b, s, h, d] tensors (a: fp32 or bf16, b: bf16, result fp32)");
+  TORCH_CHECK(lse_a.scalar_type() == at::kFloat && lse_b.scalar_type() == at::kFloat && lse.scalar_type() == at::kFloat &&
+                  lse_a.is_contiguous() && lse_b.is_contiguous() && lse.is_contiguous() &&
+                  lse_a.numel() == out.size(0) * out.size(1) * out.size(2) && lse_b.numel() == lse_a.numel() &&
+                  lse.numel() == lse_a.numel(),
+              "attn_merge: fp32 contiguous [b, h, s] log-sum-exp tensors");
+  check(pico_attn_merge(out_a.data_ptr(), out_a.scalar_type() == at::kFloat ? 1 : 0, (const float*)lse_a.data_ptr(),
+                        out_b.data_ptr(), (const float*)lse_b.data_ptr(), (float*)out.data_ptr(), (float*)lse.data_ptr(),
+                        (int)out.size(0), (int)out.size(1), (int)out.size(2), (int)out.size(3), stream_of(out_b)),
+        "attn_merge");
+}
+
 void scale_unless_one(at::Tensor& x, const at::Tensor& scale) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && scale.scalar_type() == at::kFloat &&
@@ -662,6 +681,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("accumulate_bf16_into_f32", &accumulate_bf16_into_f32);
   m.def("fill_u32", &fill_u32);
   m.def("scale_unless_one", &scale_unless_one);
+  m.def("attn_merge", &attn_merge);
   m.def("moe_route", &moe_route);
   m.def("moe_route_bwd", &moe_route_bwd);
   m.def("moe_slots", &moe_slots);

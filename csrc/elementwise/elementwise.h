@@ -102,6 +102,13 @@ int pico_moe_combine(const void* out, const int32_t* idx, const int32_t* pos, co
 int pico_moe_combine_bwd(const void* dy, const void* out, const int32_t* row_of_slot, const float* w, void* dout,
                          float* dw, int64_t slots, int k, int d, cudaStream_t stream);
 
+// ---- merge of two partial attention results (disjoint key sets) ------------------------------
+// out = out_a * exp(lse_a - lse) + out_b * exp(lse_b - lse), lse = log(exp(lse_a) + exp(lse_b)).
+// out_a fp32 (a_is_f32) or bf16, out_b bf16, all [B, S, H, D] contiguous; out fp32 (may be out_a);
+// lse tensors fp32 [B, H, S] (lse may be lse_a).
+int pico_attn_merge(const void* out_a, int a_is_f32, const float* lse_a, const void* out_b, const float* lse_b,
+                    float* out, float* lse, int B, int S, int H, int D, cudaStream_t stream);
+
 // ---- misc ---------------------------------------------------------------------------------
 // dst_f32 += src_bf16 (n elements); used to fold bf16 gradients into fp32 accumulators.
 int pico_accumulate_bf16_into_f32(const void* src, float* dst, int64_t n, cudaStream_t stream);

@@ -247,6 +247,58 @@ __global__ void fill_kernel(uint32_t* __restrict__ dst, uint32_t value, int64_t 
 
 using namespace pico;
 
+// Exact merge of two partial attention results over disjoint key sets (online softmax):
+// lse' = log(exp(lse_a) + exp(lse_b)); out' = out_a * exp(lse_a - lse') + out_b * exp(lse_b - lse').
+// out_a: fp32 or bf16 [b, s, H, d]; out_b: bf16; result fp32 (may alias out_a when that is fp32).
+// lse: fp32 [b, H, s]. One warp per (b, s, h) row. A row that has seen no key on either side
+// (both lse = -inf) stays zero with lse = -inf.
+template <typename TA>
+__global__ void attn_merge_kernel(const TA* __restrict__ out_a, const float* __restrict__ lse_a,
+                                  const __nv_bfloat16* __restrict__ out_b, const float* __restrict__ lse_b,
+                                  float* __restrict__ out, float* __restrict__ lse, int B, int S, int H, int D) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t rows = (int64_t)B * S * H;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    const int h = (int)(r % H);
+    const int64_t bs = r / H;
+    const int s = (int)(bs % S);
+    const int b = (int)(bs / S);
+    const int64_t li = ((int64_t)b * H + h) * S + s;
+    const float la = lse_a[li], lb = lse_b[li];
+    const float mx = fmaxf(la, lb);
+    float wa = 0.f, wb = 0.f, ln = -INFINITY;
+    if (mx > -INFINITY) {
+      const float ea = __expf(la - mx), eb = __expf(lb - mx);
+      ln = mx + __logf(ea + eb);
+      wa = ea / (ea + eb);
+      wb = eb / (ea + eb);
+    }
+    for (int c = lane; c < D; c += 32) {
+      const float a = (float)out_a[r * D + c];
+      const float bb = __bfloat162float(out_b[r * D + c]);
+      out[r * D + c] = a * wa + bb * wb;
+    }
+    if (lane == 0) lse[li] = ln;
+  }
+}
+
+extern "C" int pico_attn_merge(const void* out_a, int a_is_f32, const float* lse_a, const void* out_b,
+                               const float* lse_b, float* out, float* lse, int B, int S, int H, int D,
+                               cudaStream_t stream) {
+  const int64_t rows = (int64_t)B * S * H;
+  if (rows <= 0) return 0;
+  const int grid = grid_for(rows * 32, 256);
+  if (a_is_f32)
+    attn_merge_kernel<float><<<grid, 256, 0, stream>>>((const float*)out_a, lse_a, (const __nv_bfloat16*)out_b,
+                                                       lse_b, out, lse, B, S, H, D);
+  else
+    attn_merge_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out_a, lse_a,
+                                                               (const __nv_bfloat16*)out_b, lse_b, out, lse, B, S, H, D);
+  return finish("attn_merge");
+}
+
 // x *= *scale unless *scale == 1 (the usual case costs one scalar load per thread and no traffic)
 __global__ void scale_unless_one_kernel(uint4* __restrict__ x, int64_t nvec, const float* __restrict__ scale) {
   const float sc = *scale;

@@ -68,6 +68,17 @@ def merge_attention_blocks(out, lse, blk_out, blk_lse):
     """
     if out is None:
         return blk_out.float(), blk_lse
+    if blk_out.is_cuda and blk_out.dtype == torch.bfloat16 and out.dtype in (torch.float32, torch.bfloat16) \
+            and out.is_contiguous() and blk_out.is_contiguous() and lse.is_contiguous() and blk_lse.is_contiguous() \
+            and not reference_ops_forced_() and not torch.is_grad_enabled():
+        # one kernel instead of six eager ones (the ring forward runs under no_grad: its autograd
+        # function owns the backward); fp32 accumulators are updated in place
+        from . import count_launch, ext
+        merged = out if out.dtype == torch.float32 else torch.empty(out.shape, device=out.device, dtype=torch.float32)
+        new_lse = torch.empty_like(lse)
+        ext().attn_merge(out, lse, blk_out, blk_lse, merged, new_lse)
+        count_launch()
+        return merged, new_lse
     new_lse = torch.logaddexp(lse, blk_lse)
     safe = torch.where(torch.isinf(new_lse), torch.zeros_like(new_lse), new_lse)
     w_old = torch.exp(lse - safe).transpose(1, 2).unsqueeze(-1)      # [b, s, H, 1]

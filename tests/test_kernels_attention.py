@@ -116,3 +116,32 @@ def test_attention_backward_block_offsets():
         dq, dk, dv = A.flash_attention_backward(go, q, kb, vb, out, lse, True, None, q_pos0=s, k_pos0=blk * s)
         rq, rk, rv = A.attention_block_backward(go, q, kb, vb, out, lse, True, None, q_offset=s, k_offset=blk * s)
         assert _rel(dq, rq) < 2e-2 and _rel(dk, rk) < 2e-2 and _rel(dv, rv) < 2e-2
+
+
+@pytest.mark.parametrize("acc_dtype", [torch.float32, torch.bfloat16])
+def test_merge_kernel_matches_eager_merge(acc_dtype):
+    """Online-softmax merge of two partial results: the kernel against the eager formula, including
+    rows that have seen no key on one side or on both (lse = -inf)."""
+    from picotron_b200 import ops
+    from picotron_b200.ops import attention as A
+    torch.manual_seed(0)
+    b, s, H, d = 2, 300, 6, 64
+    out_a = torch.randn(b, s, H, d, device="cuda").to(acc_dtype)
+    out_b = torch.randn(b, s, H, d, device="cuda").to(torch.bfloat16)
+    lse_a = torch.randn(b, H, s, device="cuda") * 3
+    lse_b = torch.randn(b, H, s, device="cuda") * 3
+    lse_a[0, 0, :10] = float("-inf")
+    lse_b[0, 1, :10] = float("-inf")
+    lse_a[1, 2, 5:9] = float("-inf")
+    lse_b[1, 2, 5:9] = float("-inf")
+    with torch.enable_grad():       # the eager formula is what runs when gradients are recorded
+        want_out, want_lse = A.merge_attention_blocks(out_a.clone().requires_grad_(True), lse_a, out_b, lse_b)
+    with torch.no_grad():
+        got_out, got_lse = A.merge_attention_blocks(out_a.clone(), lse_a.clone(), out_b, lse_b)
+    ops.check_status("attn merge")
+    assert got_out.dtype == torch.float32
+    assert torch.equal(torch.isinf(got_lse), torch.isinf(want_lse))
+    fin = ~torch.isinf(want_lse)
+    assert torch.allclose(got_lse[fin], want_lse[fin], atol=1e-5, rtol=1e-5)
+    assert torch.allclose(got_out, want_out.detach(), atol=2e-3, rtol=1e-3)
+    assert got_out[1, 5:9, 2].abs().max().item() == 0.0        # no key on either side: stays zero
