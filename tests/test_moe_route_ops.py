@@ -63,8 +63,13 @@ def test_route_kernel_matches_reference(E, k, renorm, use_bias):
     from picotron_b200.ops import moe_route as mr
     torch.manual_seed(E + k)
     T = 777
-    logits = (torch.randn(T, E, device="cuda") * 2.0).to(torch.bfloat16).requires_grad_(True)
-    bias = (torch.randn(E, device="cuda") * 0.05) if use_bias else None
+    # every row is a random permutation of E distinct values that bf16 represents exactly: no ties, so the
+    # selection is unambiguous (which of two equal scores wins is not part of the contract)
+    step = 1.0 / 32 if E > 64 else 1.0 / 8
+    perm = torch.rand(T, E, device="cuda").argsort(dim=-1).float()
+    logits = ((perm - E / 2) * step).to(torch.bfloat16).requires_grad_(True)
+    assert torch.equal(logits.detach().float(), (perm - E / 2) * step)
+    bias = (torch.randn(E, device="cuda") * 0.001) if use_bias else None
     probs, idx, w, counts = mr.route(logits, bias, k, renorm)
     ref_logits = logits.detach().float().requires_grad_(True)
     rp, ri, rw, rc = mr.route_ref(ref_logits, bias, k, renorm)
