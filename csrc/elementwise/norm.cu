@@ -53,7 +53,7 @@ extern "C" int pico_rmsnorm_fwd(const void* x, const void* residual, const void*
   return (int)e;
 }
 
-extern "C" int pico_rmsnorm_bwd_num_partials(void) { return pico_host::num_sms() * 2; }
+extern "C" int pico_rmsnorm_bwd_num_partials(void) { return pico_host::num_sms() * 4; }
 
 extern "C" int pico_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd,
                                 const void* dres, void* dh, float* dw_partial, float* dw_f32,
@@ -65,6 +65,22 @@ extern "C" int pico_rmsnorm_bwd(const void* dy, const void* h, const void* w, co
     return -2;
   }
   const int grid = pico_rmsnorm_bwd_num_partials();
+  if (H == 2048 || H == 4096) {
+    const __nv_bfloat16* a = (const __nv_bfloat16*)dy;
+    const __nv_bfloat16* b = (const __nv_bfloat16*)h;
+    const __nv_bfloat16* c = (const __nv_bfloat16*)w;
+    const __nv_bfloat16* d = (const __nv_bfloat16*)dres;
+    __nv_bfloat16* o = (__nv_bfloat16*)dh;
+    if (H == 2048)
+      pico::rmsnorm_bwd_rows_kernel<1, 4><<<grid, pico::kNormThreads, 0, stream>>>(a, b, c, rstd, d, o, dw_partial, rows, H);
+    else
+      pico::rmsnorm_bwd_rows_kernel<2, 2><<<grid, pico::kNormThreads, 0, stream>>>(a, b, c, rstd, d, o, dw_partial, rows, H);
+    pico::colsum_kernel<<<(H + 31) / 32, 256, 0, stream>>>(dw_partial, grid, H, dw_f32,
+                                                             (__nv_bfloat16*)dw_bf16, accumulate);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) pico_host::set_error("rmsnorm_bwd: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
   if (H % 256 == 0 && H <= 2048) {
     const __nv_bfloat16* a = (const __nv_bfloat16*)dy;
     const __nv_bfloat16* b = (const __nv_bfloat16*)h;
