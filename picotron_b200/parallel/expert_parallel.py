@@ -131,6 +131,14 @@ class MoELayer(nn.Module):
     # ------------------------------------------------------------------------------ routing
     def _route(self, tokens):
         logits = self.gate(tokens)
+        if logits.is_cuda and logits.dtype == torch.bfloat16 and self.num_experts <= 256 and self.top_k <= 8 \
+                and os.environ.get("PICO_MOE_DEVICE_ROUTING", "1") != "0":
+            # one kernel for softmax + bias + top-k + renormalisation + counts (ops/moe_route.py)
+            from ..ops import moe_route as mr
+            probs, idx, w, counts = mr.route(logits, self.expert_bias if self.use_loss_free else None, self.top_k,
+                                             self.norm_topk_prob)
+            self._balance(probs, idx, counts)
+            return idx.long(), w.to(tokens.dtype)
         probs = F.softmax(logits, dim=-1, dtype=torch.float32)
         scores = probs + self.expert_bias.to(probs.dtype) if self.use_loss_free else probs
         topk_idx = torch.topk(scores, self.top_k, dim=-1).indices
