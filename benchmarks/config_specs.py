@@ -10,7 +10,9 @@
         ``dropless`` (variable-size exchange; tiled over 4 token tiles where the arm has tiles)
   cp    long-context Llama: 16 layers, hidden 2048, 32 query / 8 KV heads, FFN 5632, vocab 32000,
         RoPE theta 5e5, 16384 tokens per GPU (131072 on 8), micro-batch 1, CP = number of GPUs.
-        variants: ``ring``, ``ulysses``
+        variants: ``ring``, ``ulysses``, ``ring_zigzag`` (this framework only: ring attention on
+        zigzag shards, every rank holding one early and one late chunk; the reference has contiguous
+        shards only, its arm then runs plain ``ring``)
   pp    Llama-2-7B shape: 32 layers, hidden 4096, 32 heads, FFN 11008, vocab 32000, seq 4096,
         micro-batch 1, 16 micro-batches; 8 GPUs = TP2 x PP2 x DP2, 4 = TP2 x PP2, 2 = PP2.
         variants: ``interleaved`` (2 virtual stages), ``zb``, ``1f1b``, ``afab``
@@ -27,7 +29,7 @@ PP_MODEL = dict(hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
                 num_key_value_heads=32, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0)
 
 DEFAULT_VARIANT = {"moe": "capacity", "cp": "ulysses", "pp": "interleaved"}
-VARIANTS = {"moe": ("capacity", "dropless"), "cp": ("ring", "ulysses"), "pp": ("interleaved", "zb", "1f1b", "afab")}
+VARIANTS = {"moe": ("capacity", "dropless"), "cp": ("ring", "ulysses", "ring_zigzag"), "pp": ("interleaved", "zb", "1f1b", "afab")}
 
 
 def make_spec(name: str, world: int, variant: str = None, layers: int = 0, seq: int = 0) -> dict:
@@ -60,13 +62,15 @@ def make_spec(name: str, world: int, variant: str = None, layers: int = 0, seq: 
         if layers:
             m["num_hidden_layers"] = layers
         s = seq or 16384 * world
-        cfg = {"distributed": dict(cp_size=world, cp_attention=variant),
+        zigzag = variant == "ring_zigzag"
+        variant_attn = "ring" if zigzag else variant
+        cfg = {"distributed": dict(cp_size=world, cp_attention=variant_attn, cp_zigzag=zigzag),
                "model": dict(name="long-context-bench", init_std=0.02, max_position_embeddings=s,
                              num_hidden_layers=m["num_hidden_layers"]),
                "training": dict(seed=1, learning_rate=3e-4, seq_length=s, micro_batch_size=1,
                                 gradient_accumulation_steps=1, num_samples=256),
                "dataset": dict(name="synthetic")}
-        return dict(name=name, variant=variant, model=m, seq=s, mbs=1, grad_acc=1, lr=3e-4, cp_attention=variant,
+        return dict(name=name, variant=variant, model=m, seq=s, mbs=1, grad_acc=1, lr=3e-4, cp_attention=variant_attn,
                     engine_cfg=cfg, label=f"cp{world} {variant}",
                     model_label="long-context Llama (16L h2048 32q/8kv heads ffn5632 v32000, rope theta 5e5)")
     if name == "pp":

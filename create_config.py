@@ -30,7 +30,7 @@ def create_single_config(args) -> str:
              pp_engine=args.pp_engine, num_virtual_stages=args.num_virtual_stages, use_cpu=args.use_cpu,
              backend="gloo" if args.use_cpu else "nccl", sequence_parallel=args.sequence_parallel,
              vocab_parallel_ce=args.vocab_parallel_ce, async_tp=args.async_tp, overlap_comm=args.overlap_comm,
-             zero_stage=args.zero_stage, dp_engine=args.dp_engine, cp_attention=args.cp_attention,
+             zero_stage=args.zero_stage, dp_engine=args.dp_engine, cp_attention=args.cp_attention, cp_zigzag=args.cp_zigzag,
              ep_as_dp=args.ep_as_dp)
     m["name"] = args.model_name
     shape = MODEL_SHAPES.get(args.model_name, {})
@@ -109,6 +109,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--zero_stage", type=int, default=0, choices=[0, 1, 2, 3])
     p.add_argument("--dp_engine", type=str, default="bucket", choices=["bucket", "naive", "zero", "fused"])
     p.add_argument("--cp_attention", type=str, default="ring", choices=["ring", "ulysses"])
+    p.add_argument("--cp_zigzag", action="store_true",
+                   help="ring attention: give every rank one early and one late chunk of the sequence (balanced causal work)")
     p.add_argument("--ep_as_dp", action="store_true")
     p.add_argument("--parallel_block", action="store_true")
     p.add_argument("--init_std", type=float, default=None)

@@ -47,7 +47,7 @@ DEFAULTS: Dict[str, Dict[str, Any]] = {
     "distributed": dict(tp_size=1, cp_size=1, ep_size=1, pp_size=1, dp_size=1, pp_engine="1f1b",
                         num_virtual_stages=2, backend="nccl", use_cpu=False, sequence_parallel=False,
                         vocab_parallel_ce=False, async_tp=False, overlap_comm=False, zero_stage=0,
-                        dp_engine="bucket", cp_attention="ring", ep_as_dp=False),
+                        dp_engine="bucket", cp_attention="ring", cp_zigzag=False, ep_as_dp=False),
     "model": dict(name="HuggingFaceTB/SmolLM-360M-Instruct", num_hidden_layers=None, num_attention_heads=None,
                   num_key_value_heads=None, num_experts=1, num_experts_per_tok=2, num_shared_experts=0,
                   norm_topk_prob=True, dtype="bfloat16", use_flash_attention=True, use_fused_adam=True,

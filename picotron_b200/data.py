@@ -50,13 +50,16 @@ class MicroBatchDataLoader:
                  grad_acc_steps: int = 1, device: str = "cpu", subset_name: Optional[str] = None,
                  split: str = "train", num_samples: Optional[int] = None, pin_memory: bool = True,
                  vocab_size: Optional[int] = None, seed: int = 0, dp_world_size: Optional[int] = None,
-                 dp_rank: Optional[int] = None, cp_world_size: Optional[int] = None, cp_rank: Optional[int] = None):
+                 dp_rank: Optional[int] = None, cp_world_size: Optional[int] = None, cp_rank: Optional[int] = None,
+                 cp_zigzag: bool = False):
         m = pgm.get_pgm()
         self.dp_world_size = dp_world_size if dp_world_size is not None else m.dp_world_size
         self.dp_rank = dp_rank if dp_rank is not None else m.dp_rank
         self.cp_world_size = cp_world_size if cp_world_size is not None else m.cp_world_size
         self.cp_rank = cp_rank if cp_rank is not None else m.cp_rank
         self.micro_batch_size = micro_batch_size
+        #: zigzag context parallelism: this rank's tokens are chunks r and 2*cp-1-r of the sequence
+        self.cp_zigzag = bool(cp_zigzag) and self.cp_world_size > 1
         self.seq_length = seq_length
         self.grad_acc_steps = grad_acc_steps
         self.global_batch_size = micro_batch_size * grad_acc_steps * self.dp_world_size
@@ -97,11 +100,19 @@ class MicroBatchDataLoader:
 
     def collate(self, rows: torch.Tensor):
         """rows: [mbs, seq+1] -> this CP rank's slice of inputs / targets / positions."""
-        lo = self.cp_rank * self.seq_length_per_gpu
-        hi = lo + self.seq_length_per_gpu
-        input_ids = rows[:, lo:hi].contiguous()
-        target_ids = rows[:, lo + 1:hi + 1].contiguous()
-        position_ids = torch.arange(lo, hi, dtype=torch.long).unsqueeze(0).expand(rows.shape[0], -1).contiguous()
+        if self.cp_zigzag:
+            h = self.seq_length_per_gpu // 2
+            starts = (self.cp_rank * h, (2 * self.cp_world_size - 1 - self.cp_rank) * h)
+            input_ids = torch.cat([rows[:, s0:s0 + h] for s0 in starts], dim=1).contiguous()
+            target_ids = torch.cat([rows[:, s0 + 1:s0 + h + 1] for s0 in starts], dim=1).contiguous()
+            position_ids = torch.cat([torch.arange(s0, s0 + h, dtype=torch.long) for s0 in starts]) \
+                .unsqueeze(0).expand(rows.shape[0], -1).contiguous()
+        else:
+            lo = self.cp_rank * self.seq_length_per_gpu
+            hi = lo + self.seq_length_per_gpu
+            input_ids = rows[:, lo:hi].contiguous()
+            target_ids = rows[:, lo + 1:hi + 1].contiguous()
+            position_ids = torch.arange(lo, hi, dtype=torch.long).unsqueeze(0).expand(rows.shape[0], -1).contiguous()
         if self.pin_memory:
             input_ids, target_ids, position_ids = (t.pin_memory() for t in (input_ids, target_ids, position_ids))
         return {"input_ids": input_ids, "target_ids": target_ids, "position_ids": position_ids,

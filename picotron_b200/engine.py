@@ -190,7 +190,8 @@ class TrainEngine:
             subset_name=cfg["dataset"].get("subset_name"), split=cfg["dataset"].get("split", "train"),
             num_proc=cfg["dataset"].get("num_proc", 1),
             dp_world_size=m.dp_world_size * (m.ep_world_size if d["ep_as_dp"] else 1),
-            dp_rank=m.dp_rank * (m.ep_world_size if d["ep_as_dp"] else 1) + (m.ep_rank if d["ep_as_dp"] else 0))
+            dp_rank=m.dp_rank * (m.ep_world_size if d["ep_as_dp"] else 1) + (m.ep_rank if d["ep_as_dp"] else 0),
+            cp_zigzag=bool(d.get("cp_zigzag", False)) and d["cp_attention"] == "ring")
         self.tokens_per_step = self.data_loader.global_batch_size * t["seq_length"]
         self._build_model()
         self._build_optimizer()
@@ -222,7 +223,8 @@ class TrainEngine:
             model = wrap_pipeline(model, self.model_config, d["pp_engine"], d["num_virtual_stages"])
         if m.cp_world_size > 1:
             from .parallel.context_parallel import apply_context_parallel
-            apply_context_parallel(model, attention=d["cp_attention"], seq_length=self.cfg["training"]["seq_length"])
+            apply_context_parallel(model, attention=d["cp_attention"], seq_length=self.cfg["training"]["seq_length"],
+                                   zigzag=bool(d.get("cp_zigzag", False)) and d["cp_attention"] == "ring")
         # (re-)initialise in canonical module order from the configured seed: tensor-parallel
         # layers draw the full master weight and keep their slice, so a TP run starts from
         # exactly the weights of the single-device run (reference: checkpoint.py:114-119)

@@ -179,6 +179,9 @@ class RotaryTables:
     def __init__(self, max_positions: int, head_dim: int, theta: float):
         self.max_positions, self.head_dim, self.theta = max_positions, head_dim, theta
         self.pos_offset = 0
+        #: zigzag context parallelism: the local tokens are several pieces of the sequence, given as
+        #: (local start, length, global position of the first token); None = one piece at pos_offset
+        self.pos_pieces = None
         self._cache = {}
 
     def tables(self, device, dtype):
@@ -193,7 +196,10 @@ class RotaryTables:
 
     def apply(self, x):
         cos, sin, half = self.tables(x.device, x.dtype)
-        return rope_ops.apply_rope(x, cos, sin, self.pos_offset, tables=half)
+        if self.pos_pieces is None:
+            return rope_ops.apply_rope(x, cos, sin, self.pos_offset, tables=half)
+        return torch.cat([rope_ops.apply_rope(x[:, lo:lo + n], cos, sin, pos, tables=half)
+                          for lo, n, pos in self.pos_pieces], dim=1)
 
 
 class DecoderLayer(nn.Module):

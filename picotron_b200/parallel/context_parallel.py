@@ -28,16 +28,29 @@ from .cp_communications import ContextCommunicate
 from .dist_utils import group_rank, group_size
 
 
+def shard_pieces(rank: int, n: int, s_loc: int, zigzag: bool):
+    """How rank ``rank`` of ``n`` holds its ``s_loc`` tokens: a list of (local start, length, global
+    position of the first token). Contiguous sharding is one piece at ``rank * s_loc``. Zigzag sharding
+    cuts the sequence into ``2n`` chunks and gives rank r chunks r and 2n-1-r, which balances causal
+    attention: every rank owns one early (cheap) and one late (expensive) chunk."""
+    if not zigzag:
+        return [(0, s_loc, rank * s_loc)]
+    assert s_loc % 2 == 0, "zigzag sharding needs an even number of tokens per rank"
+    h = s_loc // 2
+    return [(0, h, rank * h), (h, h, (2 * n - 1 - rank) * h)]
+
+
 class _RingAttention(torch.autograd.Function):
-    """q: [b, s_loc, H, d]; k, v: [b, s_loc, Hkv, d] (this rank's shard)."""
+    """q: [b, s_loc, H, d]; k, v: [b, s_loc, Hkv, d] (this rank's shard, contiguous or zigzag pieces)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, sm_scale, causal, group):
+    def forward(ctx, q, k, v, sm_scale, causal, group, zigzag):
         n, rank = group_size(group), group_rank(group)
         s_loc = q.shape[1]
         comm = ContextCommunicate("fwd", group=group, send_rank=_ring_peer(group, +1),
                                   recv_rank=_ring_peer(group, -1))
-        out, lse = None, None
+        q_pieces = shard_pieces(rank, n, s_loc, zigzag)
+        acc = [(None, None) for _ in q_pieces]           # (out, lse) per query piece
         cur_k, cur_v = k.contiguous(), v.contiguous()
         use_kernel = attn_ops.kernel_supports(q, k) and not attn_ops.reference_ops_forced_()
         for step in range(n):
@@ -46,27 +59,32 @@ class _RingAttention(torch.autograd.Function):
                 next_v = comm.send_recv(cur_v)
                 comm.commit()
             src = (rank - step) % n          # owner of the block in hand
-            if not causal or src <= rank:
-                if use_kernel:
-                    # tcgen05 flash attention on this key block; global positions give the mask
-                    blk_out, blk_lse = attn_ops.flash_attention_forward(q, cur_k, cur_v, causal, sm_scale,
-                                                                        q_pos0=rank * s_loc, k_pos0=src * s_loc)
-                else:
-                    blk_out, blk_lse = attn_ops.attention_block(q, cur_k, cur_v, causal and src == rank, sm_scale,
-                                                                q_offset=0, k_offset=0)
-                out, lse = attn_ops.merge_attention_blocks(out, lse, blk_out, blk_lse)
+            for qi, (q0, qlen, qpos) in enumerate(q_pieces):
+                for k0, klen, kpos in shard_pieces(src, n, s_loc, zigzag):
+                    if causal and kpos > qpos + qlen - 1:
+                        continue             # every key of this piece lies in the future of every query
+                    qq, kk, vv = q[:, q0:q0 + qlen], cur_k[:, k0:k0 + klen], cur_v[:, k0:k0 + klen]
+                    if use_kernel:
+                        # tcgen05 flash attention on this key piece; global positions give the mask
+                        blk_out, blk_lse = attn_ops.flash_attention_forward(qq, kk, vv, causal, sm_scale,
+                                                                            q_pos0=qpos, k_pos0=kpos)
+                    else:
+                        blk_out, blk_lse = attn_ops.attention_block(qq, kk, vv, causal, sm_scale,
+                                                                    q_offset=qpos, k_offset=kpos)
+                    acc[qi] = attn_ops.merge_attention_blocks(acc[qi][0], acc[qi][1], blk_out, blk_lse)
             if step + 1 < n:
                 comm.wait()
                 cur_k, cur_v = next_k, next_v
-        out = out.to(q.dtype)
+        out = torch.cat([o for o, _ in acc], dim=1).to(q.dtype) if len(acc) > 1 else acc[0][0].to(q.dtype)
+        lse = torch.cat([l for _, l in acc], dim=2) if len(acc) > 1 else acc[0][1]
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.sm_scale, ctx.causal, ctx.group, ctx.use_kernel = sm_scale, causal, group, use_kernel
+        ctx.sm_scale, ctx.causal, ctx.group, ctx.use_kernel, ctx.zigzag = sm_scale, causal, group, use_kernel, zigzag
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
-        group, causal = ctx.group, ctx.causal
+        group, causal, zigzag = ctx.group, ctx.causal, ctx.zigzag
         n, rank = group_size(group), group_rank(group)
         kv_comm = ContextCommunicate("bwd-kv", group=group, send_rank=_ring_peer(group, +1),
                                      recv_rank=_ring_peer(group, -1))
@@ -77,25 +95,29 @@ class _RingAttention(torch.autograd.Function):
         cur_k, cur_v = k.contiguous(), v.contiguous()
         s_loc = q.shape[1]
         dout = dout.contiguous()
+        q_pieces = shard_pieces(rank, n, s_loc, zigzag)
         for step in range(n):
             if step + 1 < n:
                 next_k = kv_comm.send_recv(cur_k)
                 next_v = kv_comm.send_recv(cur_v)
                 kv_comm.commit()
             src = (rank - step) % n
-            if not causal or src <= rank:
-                if ctx.use_kernel:
-                    bdq, bdk, bdv = attn_ops.flash_attention_backward(dout, q, cur_k, cur_v, out, lse, causal,
-                                                                      ctx.sm_scale, q_pos0=rank * s_loc,
-                                                                      k_pos0=src * s_loc)
-                    bdk, bdv = bdk.float(), bdv.float()
-                else:
-                    bdq, bdk, bdv = attn_ops.attention_block_backward(dout, q, cur_k, cur_v, out, lse,
-                                                                      causal and src == rank, ctx.sm_scale)
-                dq += bdq
-            else:
-                bdk = torch.zeros(cur_k.shape, device=q.device, dtype=torch.float32)
-                bdv = torch.zeros(cur_v.shape, device=q.device, dtype=torch.float32)
+            bdk = torch.zeros(cur_k.shape, device=q.device, dtype=torch.float32)
+            bdv = torch.zeros(cur_v.shape, device=q.device, dtype=torch.float32)
+            for q0, qlen, qpos in q_pieces:
+                for k0, klen, kpos in shard_pieces(src, n, s_loc, zigzag):
+                    if causal and kpos > qpos + qlen - 1:
+                        continue
+                    qs, ks = slice(q0, q0 + qlen), slice(k0, k0 + klen)
+                    args = (dout[:, qs], q[:, qs], cur_k[:, ks], cur_v[:, ks], out[:, qs], lse[:, :, qs].contiguous(),
+                            causal, ctx.sm_scale)
+                    if ctx.use_kernel:
+                        pdq, pdk, pdv = attn_ops.flash_attention_backward(*args, q_pos0=qpos, k_pos0=kpos)
+                    else:
+                        pdq, pdk, pdv = attn_ops.attention_block_backward(*args, q_offset=qpos, k_offset=kpos)
+                    dq[:, qs] += pdq
+                    bdk[:, ks] += pdk
+                    bdv[:, ks] += pdv
             if step > 0:
                 grad_comm.wait()          # accumulators of the block now in hand have arrived
                 dk_acc, dv_acc = recv_dk + bdk, recv_dv + bdv
@@ -110,7 +132,7 @@ class _RingAttention(torch.autograd.Function):
                 kv_comm.wait()
                 cur_k, cur_v = next_k, next_v
         grad_comm.wait()
-        return dq.to(q.dtype), recv_dk.to(k.dtype), recv_dv.to(v.dtype), None, None, None
+        return dq.to(q.dtype), recv_dk.to(k.dtype), recv_dv.to(v.dtype), None, None, None, None
 
 
 def _ring_peer(group, delta: int) -> int:
@@ -130,16 +152,18 @@ def install_fused_cp(cp) -> None:
     _FUSED_CP = cp
 
 
-def ring_attention_bshd(q, k, v, causal: bool = True, sm_scale=None, group=None):
+def ring_attention_bshd(q, k, v, causal: bool = True, sm_scale=None, group=None, zigzag: bool = False):
+    """``zigzag``: the local tokens are chunks r and 2n-1-r of the sequence (see ``shard_pieces``)
+    instead of one contiguous slice."""
     group = group if group is not None else pgm.get_pgm().cp_group
     if group_size(group) == 1:
         return attn_ops.attention(q, k, v, causal, sm_scale)
     cp = _FUSED_CP
-    if cp is not None and causal and cp.sg.group is group and cp.matches(k) and attn_ops.kernel_supports(q, k) \
-            and not attn_ops.reference_ops_forced_():
+    if cp is not None and causal and not zigzag and cp.sg.group is group and cp.matches(k) \
+            and attn_ops.kernel_supports(q, k) and not attn_ops.reference_ops_forced_():
         from ..ops.fused_cp import gathered_causal_attention
         return gathered_causal_attention(q, k, v, sm_scale, cp)
-    return _RingAttention.apply(q, k, v, sm_scale, causal, group)
+    return _RingAttention.apply(q, k, v, sm_scale, causal, group, zigzag)
 
 
 def ring_attention(q, k, v, sm_scale, is_causal, group=None):
@@ -159,12 +183,17 @@ def update_rope_for_context_parallel(cos, sin, cp_rank=None, cp_world_size=None)
     return cos[cp_rank * per:(cp_rank + 1) * per], sin[cp_rank * per:(cp_rank + 1) * per]
 
 
-def apply_context_parallel(model, attention: str = "ring", group=None, seq_length: int = None):
+def apply_context_parallel(model, attention: str = "ring", group=None, seq_length: int = None,
+                           zigzag: bool = False):
     """Install ring or Ulysses attention on every layer and offset RoPE positions to this rank's
     slice of the sequence: rank r holds positions ``[r * s_local, (r + 1) * s_local)`` with
     ``s_local = seq_length / cp``. ``seq_length`` is the training sequence length; it defaults to
     the model's ``max_position_embeddings`` (the reference slices its tables by that,
-    context_parallel.py:326-334), which is only right when the two are equal. Returns the model."""
+    context_parallel.py:326-334), which is only right when the two are equal. ``zigzag`` (ring
+    attention only; the data loader must slice the same way, ``MicroBatchDataLoader(cp_zigzag=True)``)
+    gives rank r chunks r and 2n-1-r of the sequence instead, so that causal attention costs every
+    rank the same (with contiguous shards rank r computes r+1 blocks and the last rank paces the ring,
+    as the reference's README notes, context_parallel/README.md:146-148). Returns the model."""
     m = pgm.get_pgm()
     group = group if group is not None else m.cp_group
     n, rank = group_size(group), group_rank(group)
@@ -177,14 +206,16 @@ def apply_context_parallel(model, attention: str = "ring", group=None, seq_lengt
             return ulysses_attention_bshd(q, k, v, causal, sm_scale, group)
     else:
         def core(q, k, v, causal, sm_scale=None):
-            return ring_attention_bshd(q, k, v, causal, sm_scale, group)
+            return ring_attention_bshd(q, k, v, causal, sm_scale, group, zigzag=zigzag)
     for layer in model.decoder_layers_iter():
         layer.attention.core = core
     s_total = model.rope.max_positions if seq_length is None else int(seq_length)
     assert s_total <= model.rope.max_positions, \
         f"sequence length {s_total} exceeds max_position_embeddings {model.rope.max_positions}"
     assert s_total % n == 0, "sequence length must be divisible by the context-parallel size"
+    assert not (zigzag and attention == "ulysses"), "zigzag sharding applies to ring attention only"
     model.rope.pos_offset = rank * (s_total // n)
+    model.rope.pos_pieces = shard_pieces(rank, n, s_total // n, True) if zigzag else None
     model.cp_group = group
     model.cp_attention = attention
     return model

@@ -85,3 +85,62 @@ def _model_worker(rank, world, kind):
 @pytest.mark.parametrize("kind", ["ring", "ulysses"])
 def test_cp2_model(kind):
     run_distributed(_model_worker, 2, kind)
+
+
+def _zigzag_attn_worker(rank, world, kv_heads):
+    """Ring attention on zigzag shards (rank r holds chunks r and 2n-1-r) against full attention."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.ops import attention as A
+    from picotron_b200.parallel.context_parallel import ring_attention_bshd, shard_pieces
+
+    pgm.setup_process_group_manager(tp_size=1, cp_size=world, pp_size=1, dp_size=1)
+    torch.manual_seed(6)
+    b, s, H, d = 2, 8 * world, 4, 16
+    q = torch.randn(b, s, H, d)
+    k = torch.randn(b, s, kv_heads, d)
+    v = torch.randn(b, s, kv_heads, d)
+    go = torch.randn(b, s, H, d)
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ref = A.attention_ref(qr, kr, vr, True)
+    ref.backward(go)
+    pieces = shard_pieces(rank, world, s // world, True)
+    assert [p[2] for p in pieces] == [rank * 4, (2 * world - 1 - rank) * 4]
+
+    def mine(t):
+        return torch.cat([t[:, pos:pos + n] for _, n, pos in pieces], dim=1)
+
+    ql, kl, vl = (mine(t).clone().requires_grad_(True) for t in (q, k, v))
+    out = ring_attention_bshd(ql, kl, vl, True, zigzag=True)
+    out.backward(mine(go))
+    assert (out - mine(ref)).abs().max().item() < 2e-4
+    for got, want in ((ql.grad, qr.grad), (kl.grad, kr.grad), (vl.grad, vr.grad)):
+        assert (got - mine(want)).abs().max().item() < 2e-4
+
+
+@pytest.mark.parametrize("world,kv_heads", [(2, 2), (4, 4), (4, 1)])
+def test_zigzag_ring_attention(world, kv_heads):
+    run_distributed(_zigzag_attn_worker, world, kv_heads)
+
+
+def _zigzag_engine_worker(rank, world, out_path):
+    """The trainer with cp_zigzag (loader slicing, rotary positions, ring attention) reproduces the
+    losses of the contiguous layout: same tokens, same model, only the assignment to ranks differs."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.engine import TrainEngine
+    losses = {}
+    for zz in (False, True):
+        pgm.process_group_manager = None
+        cfg = {"distributed": dict(cp_size=world, cp_attention="ring", cp_zigzag=zz, use_cpu=True),
+               "model": dict(name="tiny-llama-test", init_std=0.02, dtype="float32", num_hidden_layers=2),
+               "training": dict(seed=0, learning_rate=1e-3, seq_length=64, micro_batch_size=2,
+                                gradient_accumulation_steps=1, num_samples=256),
+               "dataset": dict(name="synthetic")}
+        eng = TrainEngine(cfg, device=torch.device("cpu"))
+        assert eng.data_loader.cp_zigzag == zz
+        losses[zz] = [eng.average_loss(eng.train_step()) for _ in range(3)]
+    for a, b in zip(losses[True], losses[False]):
+        assert abs(a - b) < 2e-4, losses
+
+
+def test_zigzag_trainer_matches_contiguous_layout(tmp_path):
+    run_distributed(_zigzag_engine_worker, 2, str(tmp_path / "x"))
