@@ -8,7 +8,11 @@ pp_size, dp_size, pp_engine, num_virtual_stages, backend, use_cpu), ``model``, `
 reference only exposes as library code: ``distributed.{sequence_parallel, vocab_parallel_ce,
 async_tp, overlap_comm, zero_stage, dp_engine, cp_attention, ep_as_dp}``,
 ``model.{parallel_block, hidden_size, intermediate_size, vocab_size, rope_theta, rms_norm_eps,
-max_position_embeddings, init_std}`` and ``dataset.name = "synthetic"``.
+max_position_embeddings, init_std}``, ``dataset.name = "synthetic"`` and
+``training.{cuda_graph, flat_params}`` (``flat_params``: bf16 parameters and fp32 gradients in two flat
+device buffers, the fast path on a GPU; ``null`` = on unless ``zero_stage`` >= 2, whose gradient and
+parameter sharding lives on the per-parameter path of ``parallel/zero.py``; ``true`` keeps the flat
+buffers, where stages 2 and 3 shard the optimizer state only).
 """
 from __future__ import annotations
 
@@ -57,7 +61,7 @@ DEFAULTS: Dict[str, Dict[str, Any]] = {
                   shared_expert_intermediate_size=None),
     "training": dict(seed=42, learning_rate=3e-4, total_train_steps=200, seq_length=1024, micro_batch_size=32,
                      gradient_accumulation_steps=1, num_samples=400000, max_tokens=None, weight_decay=0.01,
-                     cuda_graph=True),
+                     cuda_graph=True, flat_params=None),
     "dataset": dict(name="roneneldan/TinyStories", subset_name=None, num_workers=0, num_proc=4, split="train"),
     "checkpoint": dict(save_dir="ckpt", save_frequency=300, load_path=""),
     "logging": dict(use_wandb=False, project_name="picotron", run_name=None, metrics_jsonl=None,

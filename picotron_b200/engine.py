@@ -233,7 +233,7 @@ class TrainEngine:
             model.reset_parameters()
         model.to(self.dtype).to(self.device)
         self.model = model
-        self.flat = self.device.type == "cuda" and self.dtype == torch.bfloat16
+        self.flat = self.device.type == "cuda" and self.dtype == torch.bfloat16 and self._flat_wanted()
         self._symm_groups = []         # symmetric-memory groups whose kernels run inside a micro-batch
         self._mb_graph = None
         self.dp_symm = None
@@ -263,6 +263,20 @@ class TrainEngine:
         self.fused_tp = None
         self._maybe_install_fused_tp()
         self._maybe_install_fused_cp()
+
+    def _flat_wanted(self) -> bool:
+        """``training.flat_params``. The flat buffers keep every gradient and parameter whole on every
+        rank (the optimizer kernel shards the state and the update), so ZeRO stages 2 and 3, whose
+        point is to hold only a shard of them, default to the per-parameter path of
+        ``parallel/zero.py`` (picotron/data_parallel/zero.py:102-176)."""
+        want = self.cfg["training"].get("flat_params")
+        stage = self.cfg["distributed"]["zero_stage"]
+        if want is None:
+            return stage < 2
+        if want and stage >= 2 and self.pgm.global_rank == 0:
+            print(f"zero_stage={stage} on flat parameters: the optimizer state is sharded, gradients and "
+                  "parameters stay whole on every rank (set training.flat_params=false for sharded ones)", flush=True)
+        return bool(want)
 
     def _maybe_install_fused_cp(self):
         """Context parallelism through NVLink peer memory on the flat bf16 path: ring attention gathers

@@ -269,6 +269,9 @@ class DecoderLayer(nn.Module):
         from ..parallel import sequence_parallel as sp
         n = self.input_layernorm(x)
         if getattr(self, "fused_ptb", False):
+            tp = self._ptb_peer_ctx(n)
+            if tp is not None:
+                return self._forward_parallel_peer(x, n, rope, tp)
             if self.ptb_overlap:
                 mlp_partial = self.mlp(n)  # un-reduced [b, s, h] partial sum (down_proj is raw)
                 return x + self.attention(n, rope, out_addend=mlp_partial)
@@ -276,6 +279,36 @@ class DecoderLayer(nn.Module):
             partial = self.attention(ng, rope) + self.mlp(ng)
             return x + sp.ReduceScatterToSequenceParallelRegion.apply(partial, self.tp_group)
         return x + self.attention(n, rope) + self.mlp(n)
+
+    def _ptb_peer_ctx(self, n):
+        """The peer-memory tensor-parallel context when the whole block can run on it: projections in
+        their no-collective form, local attention on the flash kernels, the micro-batch shape the
+        symmetric buffers were sized for."""
+        attn = self.attention
+        if self.ptb_overlap or not attn.q_proj.raw:
+            return None
+        tp = getattr(attn.q_proj, "fused", None)
+        if tp is None or not n.is_cuda or n.dtype != torch.bfloat16 or n.dim() != 3 \
+                or n.shape[0] * n.shape[1] != tp.m_local:
+            return None
+        if attn.core is not _local_attention or attn.head_dim not in (64, 128) or attn_ops.reference_ops_forced_():
+            return None
+        return tp
+
+    def _forward_parallel_peer(self, x, n, rope, tp):
+        """Parallel block on the fused tensor-parallel kernels: one pushed gather feeds the q/k/v and
+        the gate/up GEMMs as its row blocks arrive; the out- and down-projection partial sums leave
+        through the GEMMs' scatter epilogues and are summed, with the residual, on the owner of the
+        rows. No collective call (picotron/model.py:319-329 runs them on NCCL)."""
+        from ..ops import fused_tp
+        attn, mlp = self.attention, self.mlp
+        qkv, gate_up = fused_tp.ag_linear_sets(n, tp, [[attn.q_proj, attn.k_proj, attn.v_proj],
+                                                       [mlp.gate_proj, mlp.up_proj]])
+        _, _, half = rope.tables(x.device, x.dtype)
+        a = attn_ops.rope_attention_fused(qkv, attn.num_local_heads, attn.num_local_kv_heads, attn.head_dim,
+                                          half[0], half[1], rope.pos_offset)
+        act = swiglu_ops.swiglu(gate_up)
+        return fused_tp.dual_linear_rs(a, attn.out_proj.weight, act, mlp.down_proj.weight, tp, addend=x)
 
 
 def lm_head(model, x):

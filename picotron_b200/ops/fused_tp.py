@@ -261,6 +261,109 @@ class _AGLinearFused(torch.autograd.Function):
         return (dx.view(b, s_loc, k), None, None, None, *grads)
 
 
+def _units(ws):
+    """GEMM operands of a weight set: the fused view when its parameters are stored back to back, else
+    every parameter by itself."""
+    return [ws.fused_weight] if ws.fused_weight is not None else list(ws.params)
+
+
+class _AGLinearSetsFused(torch.autograd.Function):
+    """One gather feeding several weight sets: y_i = gather(x) @ cat(weights of set i).T. The parallel
+    transformer block reads the same normed rows for q/k/v and for gate/up
+    (picotron/model.py:319-329). x: [b, s_loc, K] shard; returns one [b, s, N_i] tensor per set."""
+
+    @staticmethod
+    def forward(ctx, x, tp: TPFused, sets, kept, *params):
+        b, s_loc, k = x.shape
+        x2 = x.reshape(b * s_loc, k)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        buf, slot, epoch = tp.gather_push(x2, keep=kept)
+        outs = []
+        for ws in sets:
+            y = torch.empty((tp.m_full, ws.out_features), device=x.device, dtype=x.dtype)
+            col = 0
+            for w in _units(ws):
+                tp.gated_gemm(buf, w, slot, epoch, False, w.shape[0], out=y[:, col:col + w.shape[0]])
+                col += w.shape[0]
+            outs.append(y.view(b, s_loc * tp.world, ws.out_features))
+        ctx.kept = buf if kept else None
+        ctx.save_for_backward(*(() if kept else (x2,)))
+        ctx.tp, ctx.sets, ctx.shape = tp, sets, (b, s_loc, k)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        tp, sets = ctx.tp, ctx.sets
+        b, s_loc, k = ctx.shape
+        if ctx.kept is not None:
+            buf, slot, epoch = ctx.kept, None, None
+        else:
+            (x2,) = ctx.saved_tensors
+            buf, slot, epoch = tp.gather_push(x2)
+        dy2s = []
+        dx = None
+        for ws, dy in zip(sets, dys):
+            dy2 = dy.reshape(tp.m_full, -1)
+            if not dy2.is_contiguous():
+                dy2 = dy2.contiguous()
+            dy2s.append(dy2)
+            # each partial product is reduced before the next one reuses the two staging buffers
+            col = 0
+            for w in _units(ws):
+                sb, sslot, sepoch = tp.scatter_gemm(dy2[:, col:col + w.shape[0]], w, True, k)
+                dx = tp.scatter_sum(sb, sslot, sepoch, k, addend=dx)
+                col += w.shape[0]
+        if slot is not None:
+            tp.wait_gather(slot, epoch)
+        grads = []
+        for ws, dy2 in zip(sets, dy2s):
+            grads += gemm_ops.backward_all(dy2, buf, ws, need_dx=False)[1]
+        return (dx.view(b, s_loc, k), None, None, None, *grads)
+
+
+class _DualLinearRSFused(torch.autograd.Function):
+    """y_shard = reduce_scatter(xa @ wa.T) + reduce_scatter(xb @ wb.T) (+ addend): the output side of the
+    parallel transformer block, whose attention and feed-forward partial sums land on the same rows.
+    Two scatter epilogues and two slot sums forward; backward gathers dy once for both branches."""
+
+    @staticmethod
+    def forward(ctx, xa, wa, xb, wb, tp: TPFused, addend):
+        b, s_loc = tp.m_local // tp.s_local, tp.s_local
+        n = wa.shape[0]
+        xs = []
+        for x in (xa, xb):
+            x2 = x.reshape(tp.m_full, x.shape[-1])
+            xs.append(x2 if x2.is_contiguous() else x2.contiguous())
+        y = None
+        if addend is not None:
+            y = addend.reshape(b * s_loc, n)
+            if not y.is_contiguous():
+                y = y.contiguous()
+        for x2, w in zip(xs, (wa, wb)):
+            sb, slot, epoch = tp.scatter_gemm(x2, w, False, n)
+            y = tp.scatter_sum(sb, slot, epoch, n, addend=y)
+        ctx.save_for_backward(xs[0], wa, xs[1], wb)
+        ctx.tp, ctx.shapes, ctx.has_addend = tp, (xa.shape, xb.shape), addend is not None
+        return y.view(b, s_loc, n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xa2, wa, xb2, wb = ctx.saved_tensors
+        tp = ctx.tp
+        dy2 = dy.reshape(-1, wa.shape[0])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        buf, slot, epoch = tp.gather_push(dy2)
+        dxa = tp.gated_gemm(buf, wa, slot, epoch, True, wa.shape[1])
+        dxb = tp.gated_gemm(buf, wb, slot, epoch, True, wb.shape[1])
+        tp.wait_gather(slot, epoch)
+        dwa = gemm_ops.wgrad_into(wa, buf, xa2)
+        dwb = gemm_ops.wgrad_into(wb, buf, xb2)
+        return (dxa.view(ctx.shapes[0]), dwa, dxb.view(ctx.shapes[1]), dwb, None,
+                (dy if ctx.has_addend else None))
+
+
 class _LinearRSFused(torch.autograd.Function):
     """y_shard = reduce_scatter(x @ w.T) (+ addend). x: [b, s, K_loc] (or its [b*s, K_loc] view);
     returns [b, s/tp, N]."""
@@ -356,5 +459,16 @@ def ag_linear(x, tp: TPFused, mods):
     return _AGLinearFused.apply(x, tp, ws, kept, *ws.params)
 
 
+def ag_linear_sets(x, tp: TPFused, mod_sets):
+    """Several groups of projections on one gathered input; returns one output per group."""
+    sets = [gemm_ops.WeightSet.of(mods) for mods in mod_sets]
+    kept = tp.keep_gathered and torch.is_grad_enabled()
+    return _AGLinearSetsFused.apply(x, tp, sets, kept, *[p for ws in sets for p in ws.params])
+
+
 def linear_rs(x, w, tp: TPFused, addend=None):
     return _LinearRSFused.apply(x, w, tp, addend)
+
+
+def dual_linear_rs(xa, wa, xb, wb, tp: TPFused, addend=None):
+    return _DualLinearRSFused.apply(xa, wa, xb, wb, tp, addend)

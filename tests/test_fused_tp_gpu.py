@@ -151,14 +151,14 @@ def test_bounded_wait_reports_timeout(world):
     run_gpu_ranks(_timeout_worker, world)
 
 
-def _tp_engine_cfg(tp, dp, zero_stage=0):
+def _tp_engine_cfg(tp, dp, zero_stage=0, parallel_block=False):
     """Small Llama whose heads, KV heads and sequence divide by every tested TP size (head_dim 64, a
     sequence shard of 128 rows per rank)."""
     return {"distributed": dict(tp_size=tp, dp_size=dp, sequence_parallel=True, vocab_parallel_ce=True,
                                 zero_stage=zero_stage),
             "model": dict(name="tiny-llama-test", init_std=0.02, dtype="bfloat16", num_hidden_layers=2,
                           hidden_size=1024, intermediate_size=2048, num_attention_heads=16, num_key_value_heads=8,
-                          max_position_embeddings=128 * tp),
+                          max_position_embeddings=128 * tp, parallel_block=parallel_block),
             "training": dict(seed=0, learning_rate=1e-3, seq_length=128 * tp, micro_batch_size=2,
                              gradient_accumulation_steps=2, num_samples=512),
             "dataset": dict(name="synthetic")}
@@ -193,6 +193,46 @@ def _engine_worker(rank, world):
 @pytest.mark.parametrize("world", WORLDS)
 def test_engine_fused_tp_matches_nccl_path(world):
     run_gpu_ranks(_engine_worker, world)
+
+
+def _engine_ptb_worker(rank, world):
+    """Parallel transformer block under TP + sequence parallelism: the peer-memory form (one pushed
+    gather for q/k/v and gate/up, two scatter epilogues summed with the residual) against the same
+    block on NCCL all-gather / reduce-scatter; losses over three steps and the parameters afterwards."""
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.engine import TrainEngine
+    from picotron_b200.ops import fused_tp
+    calls = [0]
+    plain = fused_tp.dual_linear_rs
+
+    def counted(*a, **k):
+        calls[0] += 1
+        return plain(*a, **k)
+
+    fused_tp.dual_linear_rs = counted
+    out = {}
+    for fused in ("1", "0"):
+        os.environ["PICO_FUSED_TP"] = fused
+        pgm.process_group_manager = None
+        eng = TrainEngine(_tp_engine_cfg(world, 1, parallel_block=True), device=torch.device("cuda", rank))
+        before = calls[0]
+        losses = [eng.train_step().item() for _ in range(3)]
+        ops.check_status("parallel block fused=" + fused)
+        assert (calls[0] > before) == (fused == "1"), "the peer-memory block did not run" if fused == "1" else \
+            "the NCCL arm took the peer-memory block"
+        out[fused] = (losses, eng.store.flat_params.float().clone())
+        eng.close()
+    fused_tp.dual_linear_rs = plain
+    os.environ["PICO_FUSED_TP"] = "1"
+    for a, b in zip(out["1"][0], out["0"][0]):
+        assert abs(a - b) < 3e-2, (out["1"][0], out["0"][0])
+    rel = (out["1"][1] - out["0"][1]).norm() / out["0"][1].norm()
+    assert rel < 1e-2, rel
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_engine_parallel_block_on_peer_memory_matches_nccl_path(world):
+    run_gpu_ranks(_engine_ptb_worker, world)
 
 
 def _engine_dp_tp_worker(rank, world):
@@ -261,6 +301,38 @@ def _dp_engine_worker(rank, world):
 @pytest.mark.parametrize("world", WORLDS)
 def test_engine_fused_zero1_matches_nccl_path(world):
     run_gpu_ranks(_dp_engine_worker, world)
+
+
+def _zero_stages_worker(rank, world):
+    """ZeRO stages 2 and 3 on GPUs run on the per-parameter path (gradients dropped on non-owners,
+    stage 3 also the parameters' storage); three steps of each against ZeRO-1 on the flat buffers."""
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.engine import TrainEngine
+    losses = {}
+    for stage in (1, 2, 3):
+        pgm.process_group_manager = None
+        cfg = {"distributed": dict(tp_size=1, dp_size=world, zero_stage=stage),
+               "model": dict(name="tiny-llama-test", init_std=0.02, dtype="bfloat16", num_hidden_layers=2,
+                             hidden_size=512, intermediate_size=1024, num_attention_heads=8, num_key_value_heads=4),
+               "training": dict(seed=0, learning_rate=1e-3, seq_length=256, micro_batch_size=2,
+                                gradient_accumulation_steps=2, num_samples=512),
+               "dataset": dict(name="synthetic")}
+        eng = TrainEngine(cfg, device=torch.device("cuda", rank))
+        assert eng.flat == (stage == 1)
+        losses[stage] = [eng.average_loss(eng.train_step()) for _ in range(3)]
+        ops.check_status(f"zero stage {stage}")
+        if stage == 3:
+            held = sum(p.untyped_storage().size() for p in eng.model.parameters())
+            whole = sum(p.numel() * p.element_size() for p in eng.model.parameters())
+            assert held < 0.75 * whole, (held, whole)          # the other rank's parameters are not resident
+        eng.close()
+    for stage in (2, 3):
+        for a, b in zip(losses[stage], losses[1]):
+            assert abs(a - b) < 5e-2, losses
+
+
+def test_engine_zero_stages_2_and_3_shard_on_gpu():
+    run_gpu_ranks(_zero_stages_worker, 2)
 
 
 def _ep_worker(rank, world):
