@@ -342,7 +342,13 @@ class TrainEngine:
             self._symm_groups.append(sg)
             # rows one rank may receive, as a multiple of the balanced load: an untrained router is
             # skewed (single experts at 3-5x, groups of 8 experts at up to ~1.7x the mean were measured)
-            slack = float(os.environ.get("PICO_EP_VAR_SLACK", getattr(mc, "ep_var_slack", 3.0) or 3.0))
+            # ``ep_var_slack`` 0 = the worst case (every row of every rank routed to one rank: ep_size times
+            # the balanced load), with which the overflow cannot happen; the buffers then take
+            # 2 x ep_size x tokens x top_k x dim x 2 bytes (1.6 GB at 8192 tokens, top-6, dim 2048, EP 8)
+            slack = os.environ.get("PICO_EP_VAR_SLACK", getattr(mc, "ep_var_slack", 3.0))
+            slack = 3.0 if slack is None else float(slack)
+            if slack <= 0:
+                slack = float(m.ep_world_size)
             self.fused_ep = EPVarFused(sg, layers[0].num_local_experts, layers[0].expert_dim,
                                        tokens * mc.num_experts_per_tok, slack=min(slack, float(m.ep_world_size)),
                                        fp8_dispatch=bool(getattr(mc, "ep_fp8_dispatch", False)))

@@ -77,7 +77,7 @@ def check_status(what: str = "") -> None:
     if words[0] != 0:
         names = {1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "bounds check failed"}
         hints = {3100: " — the receive buffer of the dropless MoE exchange cannot hold the rows routed to one rank: "
-                       "raise model.ep_var_slack (or PICO_EP_VAR_SLACK)"}
+                       "raise model.ep_var_slack (or PICO_EP_VAR_SLACK); 0 sizes it for the worst case"}
         raise RuntimeError(
             f"kernel error {words[0]} ({names.get(words[0], 'unknown')}) block={words[1]} "
             f"site={words[2]} extra={words[3]} {what}{hints.get(words[2], '')}")
