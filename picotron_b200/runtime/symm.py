@@ -22,6 +22,29 @@ FLAG_BYTES = (FLAG_SLOTS * MAX_PEERS + FLAG_SLOTS) * 4   # flag words, then one 
 MAX_EPOCH_DELTAS = 256
 
 
+class _Jitter:
+    """Race-detection aid. ``PICO_RACE_JITTER=<seed>`` delays the launching stream by a random time
+    (0 to ``PICO_RACE_JITTER_US``, default 200 microseconds, drawn separately on every rank) before each
+    operation that takes a flag epoch, i.e. before every kernel that communicates. The delays move the
+    ranks against each other without changing what is computed: a run with jitter must give the same
+    bits as a run without, and any difference points at an ordering that the flags do not enforce.
+    Delays are real launches, so the mode is meant for eager runs (``training.cuda_graph: false``)."""
+
+    def __init__(self):
+        import os
+        import random
+        seed = os.environ.get("PICO_RACE_JITTER", "")
+        self.rng = None
+        if seed not in ("", "0"):
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            self.rng = random.Random(int(seed) * 1009 + rank)
+            self.max_cycles = int(float(os.environ.get("PICO_RACE_JITTER_US", "200")) * 1900)
+
+    def __call__(self):
+        if self.rng is not None and torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+            torch.cuda._sleep(self.rng.randrange(self.max_cycles))
+
+
 class SymmBuffer:
     def __init__(self, nbytes: int, local_ptr: int, ptrs: List[int], device_index: int):
         self.nbytes, self.local_ptr, self.ptrs = nbytes, local_ptr, ptrs
@@ -70,6 +93,7 @@ class SymmGroup:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self._buffers: List[SymmBuffer] = []
         self.flags = self.alloc(FLAG_BYTES)
+        self._jitter = _Jitter()
         self._epochs = [0] * FLAG_SLOTS          # absolute epoch last used per slot
         self._base = [0] * FLAG_SLOTS            # host mirror of the device's epoch-base words
         self._recording = None                   # slot -> epochs used, while a graph is being captured
@@ -114,6 +138,7 @@ class SymmGroup:
     def next_epoch(self, slot: int) -> int:
         """The next epoch of ``slot`` as kernels take it: relative to the slot's device-side base
         word (zero until a CUDA graph over this group has been replayed)."""
+        self._jitter()
         self._epochs[slot] += 1
         if self._recording is not None:
             self._recording[slot] = self._recording.get(slot, 0) + 1

@@ -190,6 +190,33 @@ def _engine_worker(rank, world):
     assert eager == losses["1"], (eager, losses["1"])
 
 
+def _jitter_worker(rank, world):
+    """Race check by double run: random per-rank delays before every communicating kernel must not
+    change a single bit of three optimizer steps (eager launches, so the delays differ per step)."""
+    from picotron_b200 import ops, process_group_manager as pgm
+    from picotron_b200.engine import TrainEngine
+    runs = {}
+    for seed in ("", "7", "8"):
+        os.environ["PICO_RACE_JITTER"] = seed
+        pgm.process_group_manager = None
+        cfg = _tp_engine_cfg(world, 1)
+        cfg["training"]["cuda_graph"] = False
+        eng = TrainEngine(cfg, device=torch.device("cuda", rank))
+        losses = [eng.train_step().item() for _ in range(3)]
+        ops.check_status("jitter seed=" + seed)
+        runs[seed] = (losses, eng.store.flat_params.clone())
+        eng.close()
+    os.environ["PICO_RACE_JITTER"] = ""
+    for seed in ("7", "8"):
+        assert runs[seed][0] == runs[""][0], (seed, runs[seed][0], runs[""][0])
+        assert torch.equal(runs[seed][1], runs[""][1]), f"parameters differ under launch delays (seed {seed})"
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_engine_bits_survive_random_launch_delays(world):
+    run_gpu_ranks(_jitter_worker, world)
+
+
 @pytest.mark.parametrize("world", WORLDS)
 def test_engine_fused_tp_matches_nccl_path(world):
     run_gpu_ranks(_engine_worker, world)
