@@ -45,10 +45,26 @@ class _Jitter:
             torch.cuda._sleep(self.rng.randrange(self.max_cycles))
 
 
+GUARD_BYTES = 256        # canary zone on either side of a buffer (keeps the 256-byte alignment)
+GUARD_PATTERN = 0xA5
+
+
 class SymmBuffer:
-    def __init__(self, nbytes: int, local_ptr: int, ptrs: List[int], device_index: int):
-        self.nbytes, self.local_ptr, self.ptrs = nbytes, local_ptr, ptrs
+    def __init__(self, nbytes: int, local_ptr: int, ptrs: List[int], device_index: int, guard: int = 0):
+        """``guard`` > 0: the allocation is ``guard`` bytes larger on both sides than the ``nbytes`` the
+        users see; ``local_ptr`` / ``ptrs`` point past the leading zone."""
+        self.nbytes, self.local_ptr, self.ptrs, self.guard = nbytes, local_ptr, ptrs, guard
         self.local = ops.ext().tensor_from_ptr(local_ptr, nbytes, device_index)
+        self.guards = None
+        if guard:
+            e = ops.ext()
+            self.guards = (e.tensor_from_ptr(local_ptr - guard, guard, device_index),
+                           e.tensor_from_ptr(local_ptr + nbytes, guard, device_index))
+            for g in self.guards:
+                g.fill_(GUARD_PATTERN)
+
+    def guards_intact(self) -> bool:
+        return self.guards is None or all(bool((g == GUARD_PATTERN).all()) for g in self.guards)
 
     def view(self, dtype: torch.dtype, shape, offset_bytes: int = 0) -> torch.Tensor:
         n = 1
@@ -84,6 +100,16 @@ class GraphEpochs:
             g._base[s] += n
 
 
+_LIVE_GROUPS = None      # weak set of the process's open groups (for ``check_all_canaries``)
+
+
+def check_all_canaries() -> None:
+    """``check_canaries`` on every open group of this process (tests call it after their last kernel)."""
+    for g in list(_LIVE_GROUPS or ()):
+        if not g._closed:
+            g.check_canaries()
+
+
 class SymmGroup:
     def __init__(self, group=None, device=None):
         self.group = group
@@ -92,19 +118,27 @@ class SymmGroup:
         assert self.world <= MAX_PEERS, f"at most {MAX_PEERS} GPUs per symmetric group"
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self._buffers: List[SymmBuffer] = []
+        import os
+        self._guard = GUARD_BYTES if os.environ.get("PICO_SYMM_CANARY", "0") == "1" else 0
         self.flags = self.alloc(FLAG_BYTES)
         self._jitter = _Jitter()
         self._epochs = [0] * FLAG_SLOTS          # absolute epoch last used per slot
         self._base = [0] * FLAG_SLOTS            # host mirror of the device's epoch-base words
         self._recording = None                   # slot -> epochs used, while a graph is being captured
         self._closed = False
+        global _LIVE_GROUPS
+        if _LIVE_GROUPS is None:
+            import weakref
+            _LIVE_GROUPS = weakref.WeakSet()
+        _LIVE_GROUPS.add(self)
 
     def alloc(self, nbytes: int) -> SymmBuffer:
         """Collective over the group: every rank must call it with the same size."""
         e = ops.ext()
         nbytes = (nbytes + 255) // 256 * 256
+        g = self._guard
         with torch.cuda.device(self.device):
-            ptr, handle = e.symm_alloc(nbytes)
+            ptr, handle = e.symm_alloc(nbytes + 2 * g)
             if self.world == 1:
                 ptrs = [ptr]
             else:
@@ -112,9 +146,22 @@ class SymmGroup:
                 dist.all_gather_object(handles, bytes(handle), group=self.group)
                 ptrs = [ptr if r == self.rank else e.symm_open(handles[r]) for r in range(self.world)]
                 dist.barrier(group=self.group)
-        buf = SymmBuffer(nbytes, ptr, ptrs, self.device.index)
+        buf = SymmBuffer(nbytes, ptr + g, [p + g for p in ptrs], self.device.index, guard=g)
         self._buffers.append(buf)
         return buf
+
+    def check_canaries(self) -> None:
+        """With ``PICO_SYMM_CANARY=1`` every symmetric buffer sits between two 256-byte zones of a fixed
+        pattern; a kernel of any rank that stores past either end of a buffer of this rank changes them.
+        Synchronises and raises when a zone was touched. No-op without the switch."""
+        if not self._guard:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            bad = [i for i, buf in enumerate(self._buffers) if not buf.guards_intact()]
+        if bad:
+            raise RuntimeError(f"symmetric buffers {bad} of rank {self.rank}: guard words overwritten "
+                               f"(sizes {[self._buffers[i].nbytes for i in bad]})")
 
     def close(self) -> None:
         """Unmap the peers' buffers and free this rank's. Collective in effect: every rank must stop
@@ -125,14 +172,20 @@ class SymmGroup:
         e = ops.ext()
         with torch.cuda.device(self.device):
             torch.cuda.synchronize()
+            if self.world > 1 and dist.is_initialized() and self._guard:
+                dist.barrier(group=self.group)       # every rank's kernels are done before zones are read
+            damaged = [i for i, buf in enumerate(self._buffers) if not buf.guards_intact()]
             for buf in self._buffers:
                 for r, p in enumerate(buf.ptrs):
                     if r != self.rank and p != buf.local_ptr:
-                        e.symm_close(p)
+                        e.symm_close(p - buf.guard)
             if self.world > 1 and dist.is_initialized():
                 dist.barrier(group=self.group)       # nobody frees memory a peer still has mapped
             for buf in self._buffers:
-                e.symm_free(buf.local_ptr)
+                e.symm_free(buf.local_ptr - buf.guard)
+        if damaged:
+            self._buffers.clear()
+            raise RuntimeError(f"symmetric buffers {damaged} of rank {self.rank}: guard words overwritten")
         self._buffers.clear()
 
     def next_epoch(self, slot: int) -> int:

@@ -21,13 +21,17 @@ def _free_port():
 
 def _worker(rank, world, port, fn, errors):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0", PICO_SYMM_CANARY="1")
     try:
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
         fn(rank, world)
         torch.cuda.synchronize()
         dist.barrier()
+        # every symmetric buffer of these tests sits between guard zones: no kernel of any rank may have
+        # stored past an end of a buffer of this rank
+        from picotron_b200.runtime.symm import check_all_canaries
+        check_all_canaries()
     except Exception:
         errors.put((rank, traceback.format_exc()))
     finally:
