@@ -66,6 +66,21 @@ def main():
     m1, m2 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
     qk = torch.randn(4, M // 4, 32, 64, device=dev, dtype=bf)
     cos = torch.randn(M // 4, 32, device=dev)
+    emb_w = torch.randn(V, H, device=dev, dtype=bf)
+    ids = torch.randint(0, V, (M,), device=dev)
+    emb_out = torch.empty(M, H, device=dev, dtype=bf)
+    emb_dw = torch.zeros(V, H, device=dev)
+    E, K = 64, 6
+    r_logits = torch.randn(4 * M, E, device=dev, dtype=bf)
+    r_probs = torch.empty(4 * M, E, device=dev)
+    r_idx = torch.empty(4 * M, K, device=dev, dtype=torch.int32)
+    r_w = torch.empty(4 * M, K, device=dev)
+    r_counts = torch.zeros(E, device=dev, dtype=torch.int32)
+    mb, ms, mh, md = 1, M, 32, 64
+    oa = torch.randn(mb, ms, mh, md, device=dev)
+    ob = torch.randn(mb, ms, mh, md, device=dev, dtype=bf)
+    la, lb = torch.randn(mb, mh, ms, device=dev), torch.randn(mb, mh, ms, device=dev)
+    lnew = torch.empty_like(la)
     cases = [
         ("rmsnorm_fwd(+residual)", lambda: e.rmsnorm_fwd(x, res, w, y, h, rstd, M, H, 1e-5), M * H * 2 * 4),
         ("rmsnorm_bwd", lambda: e.rmsnorm_bwd(x, h, w, rstd, res, dh, part, dw, None, True, M, H), M * H * 2 * 4),
@@ -76,6 +91,12 @@ def main():
         ("ce_loss_grad(in place)", lambda: e.ce_loss_grad(logits, V, tgt, stats, loss, logits, V, 1.0, M, V, 0), M * V * 2 * 2),
         ("adamw(bf16 p, fp32 g/m/v)", lambda: e.adamw(p, None, g, m1, m2, n, 1e-4, 0.9, 0.95, 1e-8, 0.01, 0.1, 0.1, 1.0, True),
          n * (2 * 2 + 4 * 6)),
+        ("embedding_fwd", lambda: e.embedding_fwd(emb_w, ids, emb_out, M, H, V, 0), M * H * 2 * 2),
+        ("embedding_bwd(fp32 acc)", lambda: e.embedding_bwd(x, ids, emb_dw, M, H, V, 0), M * H * (2 + 4 * 2)),
+        ("moe_route(E=64,k=6)", lambda: e.moe_route(r_logits, None, r_probs, r_idx, r_w, r_counts, K, True),
+         4 * M * (E * 2 + E * 4 + K * 8)),
+        ("attn_merge(fp32 acc += bf16 block)", lambda: e.attn_merge(oa, la, ob, lb, oa, lnew),
+         mb * ms * mh * md * (4 + 2 + 4)),
     ]
     for name, fn, nbytes in cases:
         t = time_fn(fn, args.iters, flush)

@@ -576,7 +576,8 @@ extern "C" int pico_gemm_bf16_ex(const void* A, const void* B, void* D, int M, i
   if (N <= 64)
     return pico::dispatch_bn<64>(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_mode,
                                  max_ctas, comm, stream);
-  if (N <= 128 || ((N + 127) / 128) * ((M + 127) / 128) <= 148)
+  // ... and so do problems with no more 128 x 128 tiles than the device has SMs (one wave either way).
+  if (N <= 128 || ((N + 127) / 128) * ((M + 127) / 128) <= pico_host::num_sms())
     return pico::dispatch_bn<128>(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major,
                                   out_mode, max_ctas, comm, stream);
   return pico::dispatch_bn<256>(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_mode,

@@ -22,6 +22,7 @@ from . import count_launch, ext
 
 EXPERT_SLOTS = (20, 21)   # flags of exchanges that land in the expert-major slab
 SOURCE_SLOTS = (22, 23)   # flags of exchanges that land in the source-major slab
+LOAD_SLOTS = (24, 25)     # flags of the per-expert load tables
 
 
 class EPFused:
@@ -36,6 +37,8 @@ class EPFused:
         self.source_slab = [symm_group.alloc(rows * dim * 2) for _ in range(2)]
         self.n_expert = 0
         self.n_source = 0
+        self.n_load = 0
+        self.load_tables = {}            # number of experts -> two [ep, E] int32 tables in symmetric memory
         self.timeout_ms = int(os.environ.get("PICO_COMM_TIMEOUT_MS", "20000"))
 
     def _next(self, kind: str):
@@ -48,6 +51,32 @@ class EPFused:
             self.n_source += 1
             slot = SOURCE_SLOTS[b]
         return b, slot, self.sg.next_epoch(slot)
+
+    def sum_over_ranks(self, counts: torch.Tensor) -> torch.Tensor:
+        """counts: [E] int32 on the device. Returns their sum over the expert-parallel group as fp32 [E],
+        without a collective call: every rank stores its row into all peers' ``[ep, E]`` table and adds the
+        rows it received (the load all-reduce of picotron/expert_parallel/expert_parallel.py:205-212).
+        Static shapes, nothing read on the host: safe inside a CUDA graph. The tables are created by
+        the first call, which must therefore be an eager one made by every rank."""
+        E = counts.numel()
+        assert counts.dtype == torch.int32 and (E * 4) % 16 == 0
+        tabs = self.load_tables.get(E)
+        if tabs is None:
+            assert not torch.cuda.is_current_stream_capturing(), "the first load sum must run eagerly"
+            tabs = self.load_tables[E] = [self.sg.alloc(self.ep * E * 4) for _ in range(2)]
+            for t in tabs:
+                t.local.zero_()
+            torch.cuda.synchronize()
+            self.sg.barrier()
+        b = self.n_load % 2
+        self.n_load += 1
+        slot = LOAD_SLOTS[b]
+        epoch = self.sg.next_epoch(slot)
+        row = counts.contiguous().view(torch.bfloat16).view(1, 2 * E)          # raw bytes of the int32 row
+        ext().push_rows(row, tabs[b].ptrs, self.sg.flags.ptrs, self.ep, self.rank, 1, 2 * E, slot, epoch, 0, 0)
+        count_launch()
+        self.sg.wait(slot, epoch, self.timeout_ms)
+        return tabs[b].view(torch.int32, (self.ep, E)).sum(dim=0).float()
 
     # expert-major result [L, ep*C, d]
     def dispatch_rows(self, tokens, row_of_slot, top_k: int, quant: bool):

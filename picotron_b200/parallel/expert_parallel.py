@@ -155,6 +155,7 @@ class MoELayer(nn.Module):
         if not (self.training and (self.router_aux_loss_coef > 0 or self.use_loss_free)):
             return
         T = probs.shape[0]
+        raw_counts = counts
         if counts is None:
             counts = torch.zeros(self.num_experts, device=probs.device, dtype=probs.dtype)
             counts.scatter_add_(0, topk_idx.reshape(-1), torch.ones(topk_idx.numel(), device=probs.device,
@@ -166,9 +167,14 @@ class MoELayer(nn.Module):
             self.aux_loss = self.router_aux_loss_coef * (f * probs.mean(dim=0)).sum()
         if self.use_loss_free:
             with torch.no_grad():
-                load = counts.clone()
-                if self.ep_world_size > 1:
-                    dist.all_reduce(load, group=self.ep_group)
+                epf = self.fused_ep
+                if self.ep_world_size > 1 and epf is not None and raw_counts is not None \
+                        and raw_counts.dtype == torch.int32 and self.num_experts % 4 == 0:
+                    load = epf.sum_over_ranks(raw_counts).to(probs.dtype)     # through peer memory
+                else:
+                    load = counts.clone()
+                    if self.ep_world_size > 1:
+                        dist.all_reduce(load, group=self.ep_group)
                 self.expert_bias += self.router_bias_update_rate * torch.sign(load.mean() - load)
 
     # ------------------------------------------------------------------------------ pieces
