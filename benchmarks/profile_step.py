@@ -2,6 +2,7 @@
 launch lists and profiler captures (the workload behind ``profiles/``).
 
     python benchmarks/profile_step.py [--layers 24] [--steps 2] [--grad-acc 1] [--seq 2048] [--mbs 4]
+    python -m torch.distributed.run --nproc-per-node 2 ... benchmarks/profile_step.py --config moe --layers 4
 
 Under ``torch.distributed.run`` with N processes the model is tensor-parallel over all of them
 (sequence parallel, vocabulary-parallel cross entropy) and the step time (CUDA events, max over ranks) is
@@ -29,6 +30,10 @@ def main():
     ap.add_argument("--grad-acc", type=int, default=1)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--mbs", type=int, default=4)
+    ap.add_argument("--config", default="smollm", choices=("smollm", "moe", "cp", "pp"),
+                    help="smollm: the flagship model, tensor parallel over all ranks; moe / cp / pp: the benchmark "
+                         "configuration of that name (benchmarks/config_specs.py) at --layers layers")
+    ap.add_argument("--variant", default=None)
     ap.add_argument("--kernel-table", action="store_true",
                     help="after the timed steps, run one more step under torch.profiler and print rank 0's "
                          "kernels by device time (shares only: a profiled step is slower than a plain one)")
@@ -45,6 +50,9 @@ def main():
                          gradient_accumulation_steps=args.grad_acc, num_samples=4096),
         "dataset": dict(name="synthetic"),
     }
+    if args.config != "smollm":
+        from benchmarks.config_specs import make_spec
+        cfg = make_spec(args.config, world, args.variant, layers=args.layers)["engine_cfg"]
     engine = TrainEngine(cfg, device=torch.device("cuda", local))
     for i in range(args.steps):
         before = ops.launches()
