@@ -531,21 +531,28 @@ class TrainEngine:
         return ok
 
     def _moe_graph_safe(self) -> bool:
-        """Mixture-of-experts layers can be captured only on the path whose routing and exchange never
-        read a device value on the host and never call a collective: capacity-limited dispatch through
-        the peer-memory kernels with routing, slot assignment, combine and the expert-load sum on the
-        device (``MoELayer._forward_device_routed``). ``PICO_MOE_GRAPH=0`` keeps eager launches."""
+        """Mixture-of-experts layers can be captured on the paths whose routing and exchange never read
+        a device value on the host and never call a collective: capacity-limited dispatch
+        (``MoELayer._forward_device_routed``) and the dropless exchange laid out on the device
+        (``MoELayer._routed_fused_var``), both through the peer-memory kernels, with the expert-load sum
+        of the bias controller through peer memory too. ``PICO_MOE_GRAPH=0`` keeps eager launches."""
         import os
         from .ops.fused_ep import EPFused
+        from .ops.fused_ep_var import EPVarFused
         from .parallel.expert_parallel import MoELayer
         if os.environ.get("PICO_MOE_GRAPH", "1") == "0" or os.environ.get("PICO_MOE_DEVICE_ROUTING", "1") == "0":
             return False
-        if not isinstance(self.fused_ep, EPFused) or self.pgm.pp_world_size > 1:
+        if self.fused_ep is None or self.pgm.pp_world_size > 1 or self.pgm.tp_world_size > 1:
             return False
         layers = [mod for mod in self.model.modules() if isinstance(mod, MoELayer)]
-        return bool(layers) and all(
-            mod.fused_ep is self.fused_ep and mod.ep_capacity_factor > 0 and not mod.ep_capacity_dropless
-            and mod.num_experts <= 256 and mod.num_experts % 4 == 0 and mod.top_k <= 8 for mod in layers)
+        if not layers or any(mod.num_experts > 256 or mod.num_experts % 4 or mod.top_k > 8 for mod in layers):
+            return False
+        if isinstance(self.fused_ep, EPFused):
+            return all(mod.fused_ep is self.fused_ep and mod.ep_capacity_factor > 0 and not mod.ep_capacity_dropless
+                       for mod in layers)
+        if isinstance(self.fused_ep, EPVarFused):
+            return all(mod.fused_ep_var is self.fused_ep and mod.ep_capacity_factor <= 0 for mod in layers)
+        return False
 
     def _graphed_micro_batches(self, device_batches) -> torch.Tensor:
         from . import ops

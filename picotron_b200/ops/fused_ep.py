@@ -25,32 +25,12 @@ SOURCE_SLOTS = (22, 23)   # flags of exchanges that land in the source-major sla
 LOAD_SLOTS = (24, 25)     # flags of the per-expert load tables
 
 
-class EPFused:
-    def __init__(self, symm_group, num_local_experts: int, capacity: int, dim: int):
-        self.sg = symm_group
-        self.ep, self.rank = symm_group.world, symm_group.rank
-        self.L, self.C, self.d = num_local_experts, capacity, dim
-        rows = self.ep * self.L * self.C
-        self.rows = rows
-        self.expert_slab = [symm_group.alloc(rows * dim * 2) for _ in range(2)]       # bf16 or fp8 payload
-        self.expert_scales = [symm_group.alloc(rows * max(1, dim // 128) * 4) for _ in range(2)]
-        self.source_slab = [symm_group.alloc(rows * dim * 2) for _ in range(2)]
-        self.n_expert = 0
-        self.n_source = 0
-        self.n_load = 0
-        self.load_tables = {}            # number of experts -> two [ep, E] int32 tables in symmetric memory
-        self.timeout_ms = int(os.environ.get("PICO_COMM_TIMEOUT_MS", "20000"))
+class PeerLoadSum:
+    """Sum of small per-rank integer rows over the group through peer memory (needs ``sg``, ``ep``,
+    ``rank``, ``timeout_ms``)."""
 
-    def _next(self, kind: str):
-        if kind == "expert":
-            b = self.n_expert % 2
-            self.n_expert += 1
-            slot = EXPERT_SLOTS[b]
-        else:
-            b = self.n_source % 2
-            self.n_source += 1
-            slot = SOURCE_SLOTS[b]
-        return b, slot, self.sg.next_epoch(slot)
+    n_load = 0
+    load_tables = None                   # number of experts -> two [ep, E] int32 tables in symmetric memory
 
     def sum_over_ranks(self, counts: torch.Tensor) -> torch.Tensor:
         """counts: [E] int32 on the device. Returns their sum over the expert-parallel group as fp32 [E],
@@ -60,6 +40,8 @@ class EPFused:
         the first call, which must therefore be an eager one made by every rank."""
         E = counts.numel()
         assert counts.dtype == torch.int32 and (E * 4) % 16 == 0
+        if self.load_tables is None:
+            self.load_tables = {}
         tabs = self.load_tables.get(E)
         if tabs is None:
             assert not torch.cuda.is_current_stream_capturing(), "the first load sum must run eagerly"
@@ -77,6 +59,32 @@ class EPFused:
         count_launch()
         self.sg.wait(slot, epoch, self.timeout_ms)
         return tabs[b].view(torch.int32, (self.ep, E)).sum(dim=0).float()
+
+
+class EPFused(PeerLoadSum):
+    def __init__(self, symm_group, num_local_experts: int, capacity: int, dim: int):
+        self.sg = symm_group
+        self.ep, self.rank = symm_group.world, symm_group.rank
+        self.L, self.C, self.d = num_local_experts, capacity, dim
+        rows = self.ep * self.L * self.C
+        self.rows = rows
+        self.expert_slab = [symm_group.alloc(rows * dim * 2) for _ in range(2)]       # bf16 or fp8 payload
+        self.expert_scales = [symm_group.alloc(rows * max(1, dim // 128) * 4) for _ in range(2)]
+        self.source_slab = [symm_group.alloc(rows * dim * 2) for _ in range(2)]
+        self.n_expert = 0
+        self.n_source = 0
+        self.timeout_ms = int(os.environ.get("PICO_COMM_TIMEOUT_MS", "20000"))
+
+    def _next(self, kind: str):
+        if kind == "expert":
+            b = self.n_expert % 2
+            self.n_expert += 1
+            slot = EXPERT_SLOTS[b]
+        else:
+            b = self.n_source % 2
+            self.n_source += 1
+            slot = SOURCE_SLOTS[b]
+        return b, slot, self.sg.next_epoch(slot)
 
     # expert-major result [L, ep*C, d]
     def dispatch_rows(self, tokens, row_of_slot, top_k: int, quant: bool):
@@ -117,22 +125,32 @@ class EPFused:
 
 class _DispatchFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, tokens, row_of_slot, top_k, epf: EPFused, quant):
+    def forward(ctx, tokens, row_of_slot, top_k, epf: EPFused, quant, idx, pos):
         ctx.epf, ctx.top_k = epf, top_k
-        ctx.save_for_backward(row_of_slot)
+        ctx.routed = idx is not None and pos is not None and epf.d % 8 == 0
+        ctx.save_for_backward(row_of_slot, *((idx, pos) if ctx.routed else ()))
         ctx.num_tokens = tokens.shape[0]
         return epf.dispatch_rows(tokens.contiguous(), row_of_slot, top_k, quant)
 
     @staticmethod
     def backward(ctx, d_expert):
-        (row_of_slot,) = ctx.saved_tensors
+        row_of_slot = ctx.saved_tensors[0]
         epf = ctx.epf
         d_slots = epf.to_source_major(d_expert.contiguous().view(epf.rows, epf.d))     # [E*C, d]
+        if ctx.routed:
+            # a token's gradient is the sum over the slots its k routed copies took: the weighted-sum
+            # kernel of the combine with unit weights (fixed order, no atomics, bf16 reads)
+            idx, pos = ctx.saved_tensors[1:]
+            d_tokens = torch.empty((ctx.num_tokens, epf.d), device=d_expert.device, dtype=torch.bfloat16)
+            ones = torch.ones(idx.shape, device=d_expert.device, dtype=torch.float32)
+            ext().moe_combine(d_slots, idx, pos, ones, d_tokens, ctx.top_k, epf.C)
+            count_launch()
+            return d_tokens, None, None, None, None, None, None
         valid = row_of_slot >= 0
         tok = torch.div(row_of_slot.clamp_min(0), ctx.top_k, rounding_mode="floor").long()
         d_tokens = torch.zeros((ctx.num_tokens, epf.d), device=d_expert.device, dtype=torch.float32)
         d_tokens.index_add_(0, tok, d_slots.float() * valid.unsqueeze(1))
-        return d_tokens.to(d_expert.dtype), None, None, None, None
+        return d_tokens.to(d_expert.dtype), None, None, None, None, None, None
 
 
 class _CombineFn(torch.autograd.Function):
@@ -147,8 +165,13 @@ class _CombineFn(torch.autograd.Function):
         return epf.to_expert_major(d_back.contiguous()), None
 
 
-def dispatch(tokens, row_of_slot, top_k, epf: EPFused, quant: bool):
-    return _DispatchFn.apply(tokens, row_of_slot, top_k, epf, quant)
+def dispatch(tokens, row_of_slot, top_k, epf: EPFused, quant: bool, idx=None, pos=None):
+    """``idx`` [T, k] / ``pos`` [T, k] (int32, optional): the routing that built ``row_of_slot``; with them
+    the backward pass gathers a token's gradient from its slots in one kernel."""
+    if idx is not None and not (idx.dtype == torch.int32 and pos.dtype == torch.int32 and idx.is_contiguous()
+                                and pos.is_contiguous() and tokens.dtype == torch.bfloat16):
+        idx = pos = None
+    return _DispatchFn.apply(tokens, row_of_slot, top_k, epf, quant, idx, pos)
 
 
 def combine(expert_out, epf: EPFused):

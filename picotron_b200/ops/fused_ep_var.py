@@ -24,6 +24,7 @@ from dataclasses import dataclass
 import torch
 
 from . import count_launch, ext
+from .fused_ep import PeerLoadSum
 from .grouped_gemm import GroupLayout
 
 COUNT_SLOTS = (50, 51)
@@ -40,7 +41,7 @@ class VarPlan:
     layout: GroupLayout            # device-side layout of the receive buffer for the grouped GEMM
 
 
-class EPVarFused:
+class EPVarFused(PeerLoadSum):
     def __init__(self, symm_group, num_local_experts: int, dim: int, rows_per_rank: int, slack: float = 1.5,
                  fp8_dispatch: bool = False):
         """``fp8_dispatch``: forward dispatch rows travel as FP8 E4M3 with 1x128 block scales (quantised in

@@ -167,7 +167,7 @@ class MoELayer(nn.Module):
             self.aux_loss = self.router_aux_loss_coef * (f * probs.mean(dim=0)).sum()
         if self.use_loss_free:
             with torch.no_grad():
-                epf = self.fused_ep
+                epf = self.fused_ep if self.fused_ep is not None else self.fused_ep_var
                 if self.ep_world_size > 1 and epf is not None and raw_counts is not None \
                         and raw_counts.dtype == torch.int32 and self.num_experts % 4 == 0:
                     load = epf.sum_over_ranks(raw_counts).to(probs.dtype)     # through peer memory
@@ -331,7 +331,7 @@ class MoELayer(nn.Module):
         shared = self._shared_start(tokens)
         latent = self.down_proj_latent(tokens) if self.latent else tokens
         pos, table = mr.slots(idx, E, epf.C)
-        x = fused_ep.dispatch(latent, table, k, epf, bool(self.ep_fp8_dispatch))      # [L, ep*C, d]
+        x = fused_ep.dispatch(latent, table, k, epf, bool(self.ep_fp8_dispatch), idx, pos.view(T, k))  # [L, ep*C, d]
         out = self.experts_uniform(x)
         back = fused_ep.combine(out, epf)                                             # [E*C, d]
         y = mr.combine(back, idx, pos.view(T, k), w, table, epf.C)

@@ -314,7 +314,7 @@ def test_fused_capacity_routing_matches_plain_path(monkeypatch):
         slot = cm.slot_assignment(expert_idx, E)
         rounds = int(((cm.expert_counts(expert_idx, E).max() + C - 1) // C).item()) if dropless else 1
 
-        def fake_dispatch(tok, row_of_slot, top_k, epf, quant):       # [E*C] rows -> [L, C, d] on one rank
+        def fake_dispatch(tok, row_of_slot, top_k, epf, quant, *routing):  # [E*C] rows -> [L, C, d] on one rank
             valid = (row_of_slot >= 0).unsqueeze(-1)
             src = tok[(row_of_slot.clamp_min(0) // top_k).long()]
             return torch.where(valid, src, torch.zeros_like(src)).view(E, C, d)

@@ -366,29 +366,31 @@ def test_engine_zero_stages_2_and_3_shard_on_gpu():
     run_gpu_ranks(_zero_stages_worker, 2)
 
 
-def _moe_engine_cfg(world, graph):
+def _moe_engine_cfg(world, graph, dropless=False):
     return {"distributed": dict(ep_size=world, ep_as_dp=True),
             "model": dict(name="moe-graph-test", init_std=0.02, dtype="bfloat16", num_hidden_layers=2, hidden_size=512,
                           intermediate_size=256, num_attention_heads=8, num_key_value_heads=8, vocab_size=4096,
                           max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=10000.0, num_experts=8, num_experts_per_tok=2, num_shared_experts=0,
                           shared_expert_intermediate_size=512, router_aux_loss_coef=1e-3, router_bias_update_rate=1e-3,
-                          ep_capacity_factor=1.25, ep_capacity_dropless=False, ep_fp8_dispatch=True, ep_backend="torch"),
+                          ep_capacity_factor=0.0 if dropless else 1.25, ep_capacity_dropless=False,
+                          ep_fp8_dispatch=True, ep_backend="fused" if dropless else "torch"),
             "training": dict(seed=1, learning_rate=1e-3, seq_length=512, micro_batch_size=2,
                              gradient_accumulation_steps=2, num_samples=512, cuda_graph=graph),
             "dataset": dict(name="synthetic")}
 
 
-def _moe_graph_worker(rank, world):
-    """Capacity-path MoE model (routing, slot assignment, dispatch, experts, combine and the expert-load
-    sum all on the device): the micro-batch replayed from a CUDA graph against eager launches of the
-    same kernels, four optimizer steps; the loss-free bias must have moved identically."""
+def _moe_graph_worker(rank, world, dropless=False):
+    """MoE model on a peer-memory path (capacity-limited: routing, slot assignment, dispatch, experts,
+    combine; dropless: layout computed on the device; the expert-load sum through peer memory in both):
+    the micro-batch replayed from a CUDA graph against eager launches of the same kernels, four optimizer
+    steps; the loss-free bias must have moved identically."""
     from picotron_b200 import ops, process_group_manager as pgm
     from picotron_b200.engine import TrainEngine
     from picotron_b200.parallel.expert_parallel import MoELayer
     out = {}
     for graph in (True, False):
         pgm.process_group_manager = None
-        eng = TrainEngine(_moe_engine_cfg(world, graph), device=torch.device("cuda", rank))
+        eng = TrainEngine(_moe_engine_cfg(world, graph, dropless), device=torch.device("cuda", rank))
         assert eng.fused_ep is not None
         losses = [eng.average_loss(eng.train_step()) for _ in range(4)]
         ops.check_status(f"moe engine graph={graph}")
@@ -407,6 +409,15 @@ def _moe_graph_worker(rank, world):
 @pytest.mark.parametrize("world", WORLDS)
 def test_engine_moe_graph_replay_matches_eager(world):
     run_gpu_ranks(_moe_graph_worker, world)
+
+
+def _moe_graph_dropless_worker(rank, world):
+    _moe_graph_worker(rank, world, dropless=True)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_engine_dropless_moe_graph_replay_matches_eager(world):
+    run_gpu_ranks(_moe_graph_dropless_worker, world)
 
 
 def _ep_worker(rank, world):
