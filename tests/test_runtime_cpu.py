@@ -123,3 +123,28 @@ def test_protocol_model_detects_the_races_the_design_rules_out():
     assert races(keep_gathered=False, barrier=False, double_buffer=False), \
         "a single copy of the gather / staging buffers must race"
     assert not races(keep_gathered=True, barrier=True)
+
+
+def test_flat_params_switch_follows_zero_stage():
+    """``training.flat_params``: unset = flat buffers unless ZeRO stage 2/3 asks for sharded gradients and
+    parameters (the per-parameter wrappers); an explicit value wins."""
+    from types import SimpleNamespace
+    from picotron_b200.engine import TrainEngine
+
+    def wanted(flat, stage):
+        stub = SimpleNamespace(cfg={"training": {"flat_params": flat}, "distributed": {"zero_stage": stage}},
+                               pgm=SimpleNamespace(global_rank=1))
+        return TrainEngine._flat_wanted(stub)
+
+    assert [wanted(None, s) for s in (0, 1, 2, 3)] == [True, True, False, False]
+    assert wanted(True, 3) is True and wanted(False, 0) is False
+
+
+def test_race_jitter_is_off_by_default_and_seeded_per_rank(monkeypatch):
+    from picotron_b200.runtime import symm
+    monkeypatch.delenv("PICO_RACE_JITTER", raising=False)
+    assert symm._Jitter().rng is None
+    monkeypatch.setenv("PICO_RACE_JITTER", "5")
+    a, b = symm._Jitter(), symm._Jitter()
+    assert a.rng is not None and [a.rng.randrange(1000) for _ in range(4)] == [b.rng.randrange(1000) for _ in range(4)]
+    a()      # no GPU, no capture: a call is a no-op
