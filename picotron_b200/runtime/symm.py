@@ -111,6 +111,8 @@ def check_all_canaries() -> None:
 
 
 class SymmGroup:
+    _jitter = None           # race-detection delays (``_Jitter``), set per instance
+
     def __init__(self, group=None, device=None):
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -191,7 +193,8 @@ class SymmGroup:
     def next_epoch(self, slot: int) -> int:
         """The next epoch of ``slot`` as kernels take it: relative to the slot's device-side base
         word (zero until a CUDA graph over this group has been replayed)."""
-        self._jitter()
+        if self._jitter is not None:
+            self._jitter()
         self._epochs[slot] += 1
         if self._recording is not None:
             self._recording[slot] = self._recording.get(slot, 0) + 1
