@@ -82,3 +82,55 @@ def test_tp2_parallel_block(mode):
 
 def test_tp4_sequence_parallel():
     run_distributed(_tp_worker, 4, "sp_vocab_ce", False)
+
+
+def _collective_count_worker(rank, world):
+    """Sequence-parallel collectives per forward + backward pass, counted at the two helpers every
+    gather / reduce-scatter along the sequence goes through: the sequential block needs two gathers and
+    two reduce-scatters per layer and direction, the parallel block one of each
+    (the counting idea of the reference's tests/test_ptb_overlap.py:71-91)."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.engine import loss_fn
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.parallel import sequence_parallel as sp
+    from picotron_b200.parallel.tensor_parallel import apply_tensor_parallel
+
+    pgm.setup_process_group_manager(tp_size=world, cp_size=1, pp_size=1, dp_size=1)
+    counts = {"gather": 0, "scatter": 0}
+    gather, scatter = sp.all_gather_along_seq, sp.reduce_scatter_along_seq
+
+    def counted_gather(x, group=None):
+        counts["gather"] += 1
+        return gather(x, group)
+
+    def counted_scatter(x, group=None):
+        counts["scatter"] += 1
+        return scatter(x, group)
+
+    sp.all_gather_along_seq, sp.reduce_scatter_along_seq = counted_gather, counted_scatter
+    seen = {}
+    for parallel_block in (False, True):
+        cfg = tiny_config(parallel_block=parallel_block, num_hidden_layers=3)
+        torch.manual_seed(7)
+        model = Llama(cfg)
+        apply_tensor_parallel(model, sequence_parallel=True, vocab_parallel_ce=True)
+        g = torch.Generator().manual_seed(3)
+        ids = torch.randint(0, cfg.vocab_size, (2, 16), generator=g)
+        tgt = torch.randint(0, cfg.vocab_size, (2, 16), generator=g)
+        counts["gather"] = counts["scatter"] = 0
+        loss_fn(model, model(ids), tgt).backward()
+        seen[parallel_block] = dict(counts)
+    layers = 3
+    # per layer, forward + backward. Sequential block: 2 gathers + 2 reduce-scatters forward; backward, each of
+    # the two column-parallel groups re-gathers its input and reduce-scatters dx, each row-parallel linear
+    # gathers dy: 6 gathers + 4 reduce-scatters. Parallel block: one gather and one reduce-scatter forward and
+    # their mirror images backward: 2 + 2.
+    assert seen[False]["gather"] - seen[True]["gather"] == 4 * layers, seen
+    assert seen[False]["scatter"] - seen[True]["scatter"] == 2 * layers, seen
+    outside = (seen[True]["gather"] - 2 * layers, seen[True]["scatter"] - 2 * layers)     # embedding and lm-head
+    assert (seen[False]["gather"], seen[False]["scatter"]) == (6 * layers + outside[0], 4 * layers + outside[1]), seen
+    assert 0 <= outside[0] <= 4 and 0 <= outside[1] <= 4, seen
+
+
+def test_parallel_block_needs_fewer_sequence_parallel_collectives():
+    run_distributed(_collective_count_worker, 2)
