@@ -30,7 +30,6 @@ import os
 import subprocess
 import sys
 import tempfile
-import time
 from types import SimpleNamespace
 
 import torch

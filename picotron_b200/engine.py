@@ -18,12 +18,10 @@ Two gradient paths exist, split by device exactly like the ops:
 from __future__ import annotations
 
 import contextlib
-from types import SimpleNamespace
 from typing import Optional
 
 import torch
 import torch.distributed as dist
-import torch.nn.functional as F
 
 from . import process_group_manager as pgm
 from .config import load_config, model_config_from

@@ -14,8 +14,6 @@ gate/up — where the reference gathers once per projection).
 """
 from __future__ import annotations
 
-from typing import Sequence
-
 import torch
 import torch.distributed as dist
 
