@@ -330,6 +330,129 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
   }
 }
 
+// The same row-group scheme with the next group's rows already in flight while the current group
+// is reduced and written: the loads of group g+1 are issued before the barriers of group g, so the
+// memory system never idles between the load and the store phase of a CTA.
+template <int NV, int R>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_rows_pf_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                           const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                           const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dh,
+                           float* __restrict__ dw_partial, int rows, int H) {
+  constexpr int kWarps = kNormThreads / 32;
+  __shared__ float red[R][kWarps];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = H / 8;                       // == NV * kNormThreads
+  float dw_acc[NV][8];
+  float wv[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[i][j] = 0.f;
+    unpack8(reinterpret_cast<const uint4*>(w)[threadIdx.x + i * kNormThreads], wv[i]);
+  }
+  const float inv_h = 1.f / (float)H;
+  uint4 dnext[R][NV], hnext[R][NV];
+  float rnext[R];
+  const int stride = gridDim.x * R;
+  int row0 = blockIdx.x * R;
+  if (row0 < rows) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = row0 + r;
+      rnext[r] = row < rows ? rstd_in[row] : 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const size_t off = (size_t)min(row, rows - 1) * nvec + threadIdx.x + i * kNormThreads;
+        dnext[r][i] = reinterpret_cast<const uint4*>(dy)[off];
+        hnext[r][i] = reinterpret_cast<const uint4*>(h)[off];
+      }
+    }
+  }
+  for (; row0 < rows; row0 += stride) {
+    uint4 draw[R][NV], hraw[R][NV];
+    float rstd[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      rstd[r] = rnext[r];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        draw[r][i] = dnext[r][i];
+        hraw[r][i] = hnext[r][i];
+      }
+    }
+    const int next0 = row0 + stride;
+    if (next0 < rows) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int row = next0 + r;
+        rnext[r] = row < rows ? rstd_in[row] : 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const size_t off = (size_t)min(row, rows - 1) * nvec + threadIdx.x + i * kNormThreads;
+          dnext[r][i] = reinterpret_cast<const uint4*>(dy)[off];
+          hnext[r][i] = reinterpret_cast<const uint4*>(h)[off];
+        }
+      }
+    }
+    float dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      dot[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float d[8], hv[8];
+        unpack8(draw[r][i], d);
+        unpack8(hraw[r][i], hv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dot[r] += d[j] * wv[i][j] * hv[j];
+          dw_acc[i][j] += d[j] * hv[j] * rstd[r];      // rstd = 0 for rows past the end
+        }
+      }
+      dot[r] = warp_sum(dot[r]);
+    }
+    __syncthreads();                            // the previous iteration's readers are done with red
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) red[r][warp] = dot[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = row0 + r;
+      if (row >= rows) break;
+      float tot = 0.f;
+#pragma unroll
+      for (int k = 0; k < kWarps; ++k) tot += red[r][k];
+      const float c = tot * inv_h * rstd[r] * rstd[r] * rstd[r];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float d[8], hv[8], o[8];
+        unpack8(draw[r][i], d);
+        unpack8(hraw[r][i], hv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd[r] * d[j] * wv[i][j] - hv[j] * c;
+        const size_t off = (size_t)row * nvec + threadIdx.x + i * kNormThreads;
+        if (dres) {
+          float rr[8];
+          unpack8(reinterpret_cast<const uint4*>(dres)[off], rr);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rr[j];
+        }
+        reinterpret_cast<uint4*>(dh)[off] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float4* out = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * H +
+                                            (size_t)(threadIdx.x + i * kNormThreads) * 8);
+    out[0] = make_float4(dw_acc[i][0], dw_acc[i][1], dw_acc[i][2], dw_acc[i][3]);
+    out[1] = make_float4(dw_acc[i][4], dw_acc[i][5], dw_acc[i][6], dw_acc[i][7]);
+  }
+}
+
 // dw[H] (=|+=) sum_p partial[p][H]; fixed summation order (deterministic)
 static __global__ void colsum_kernel(const float* __restrict__ partial, int nparts, int H,
                                      float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16,
