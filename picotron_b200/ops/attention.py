@@ -160,8 +160,8 @@ class _RopeAttentionFn(torch.autograd.Function):
         q = raw[..., :H * d].view(b, s, H, d)
         k = raw[..., H * d:(H + Hkv) * d].view(b, s, Hkv, d)
         v = raw[..., (H + Hkv) * d:].view(b, s, Hkv, d)
-        rope_inplace_(q, cos_half, sin_half, pos_offset, 1)
-        rope_inplace_(k, cos_half, sin_half, pos_offset, 1)
+        # q and k lie side by side in the fused buffer: one launch rotates the H + Hkv heads of both
+        rope_inplace_(raw[..., :(H + Hkv) * d].view(b, s, H + Hkv, d), cos_half, sin_half, pos_offset, 1)
         out, lse = flash_attention_forward(q, k, v, causal, sm_scale)
         ctx.save_for_backward(raw, out, lse, cos_half, sin_half)
         ctx.dims = (H, Hkv, d, pos_offset, causal, sm_scale)
@@ -177,11 +177,15 @@ class _RopeAttentionFn(torch.autograd.Function):
         k = raw[..., H * d:(H + Hkv) * d].view(b, s, Hkv, d)
         v = raw[..., (H + Hkv) * d:].view(b, s, Hkv, d)
         dq, dk, dv = flash_attention_backward(dout.reshape(b, s, H, d), q, k, v, out, lse, causal, sm_scale)
+        fused = dq._base
+        if fused is not None and fused.shape == raw.shape and fused.is_contiguous():
+            # dq | dk | dv of one buffer: un-rotate dq and dk in one launch
+            rope_inplace_(fused[..., :(H + Hkv) * d].view(b, s, H + Hkv, d), cos_half, sin_half, pos_offset, -1)
+            return fused, None, None, None, None, None, None, None, None
         rope_inplace_(dq, cos_half, sin_half, pos_offset, -1)
         rope_inplace_(dk, cos_half, sin_half, pos_offset, -1)
-        dqkv = dq._base if dq._base is not None else torch.cat(
-            [dq.reshape(b, s, -1), dk.reshape(b, s, -1), dv.reshape(b, s, -1)], dim=-1)
-        return dqkv.view(b, s, -1), None, None, None, None, None, None, None, None
+        dqkv = torch.cat([dq.reshape(b, s, -1), dk.reshape(b, s, -1), dv.reshape(b, s, -1)], dim=-1)
+        return dqkv, None, None, None, None, None, None, None, None
 
 
 def rope_attention_fused(qkv, H, Hkv, d, cos_half, sin_half, pos_offset, causal=True, sm_scale=None):
