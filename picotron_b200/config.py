@@ -65,7 +65,7 @@ DEFAULTS: Dict[str, Dict[str, Any]] = {
     "dataset": dict(name="roneneldan/TinyStories", subset_name=None, num_workers=0, num_proc=4, split="train"),
     "checkpoint": dict(save_dir="ckpt", save_frequency=300, load_path=""),
     "logging": dict(use_wandb=False, project_name="picotron", run_name=None, metrics_jsonl=None,
-                    step_breakdown=False),
+                    step_breakdown=False, log_frequency=1),
     "environment": dict(OMP_NUM_THREADS="1", TOKENIZERS_PARALLELISM="false", FLASH_ATTEN="1", HF_TOKEN=None),
 }
 

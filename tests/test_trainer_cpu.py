@@ -246,6 +246,7 @@ def test_create_config_and_train_cli(tmp_path):
     assert cfg["distributed"]["dp_size"] == 2 and cfg["distributed"]["zero_stage"] == 1
     cfg["checkpoint"]["save_dir"] = str(tmp_path / "ckpt")
     cfg["checkpoint"]["save_frequency"] = 2
+    cfg["logging"]["log_frequency"] = 2          # step 1 is neither synchronised nor printed
     json.dump(cfg, open(cfg_path, "w"))
     env = dict(os.environ, PICO_WATCHDOG_TIMEOUT="0")
     run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
@@ -255,6 +256,7 @@ def test_create_config_and_train_cli(tmp_path):
     log = tmp_path / "cli" / "train.log"
     log.write_text(run.stdout)
     assert "Step: 2" in run.stdout and "Tokens/s/GPU:" in run.stdout and "MFU:" in run.stdout
+    assert "Step: 1 " not in run.stdout
     assert os.path.exists(tmp_path / "ckpt" / "2" / "manifest.json")
     ex = subprocess.run([sys.executable, os.path.join(REPO, "extract_metrics.py"), str(tmp_path)],
                         capture_output=True, text=True, cwd=REPO)

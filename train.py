@@ -88,13 +88,29 @@ def main():
 
     dist.barrier()
     model_cfg = engine.model_config
+    # logging.log_frequency = N: the host synchronises with the device, reads the loss and prints only
+    # every N-th step (and at checkpoints and at the end); in between, steps are enqueued back to back
+    # and the printed step time is the mean over the window. N = 1 is the reference's behaviour
+    # (train.py:323-379 there: one loss all-reduce and .item() per step).
+    log_every = max(1, int(cfg["logging"].get("log_frequency") or 1))
+    in_window = 0
     while t["max_tokens"] is None or engine.trained_tokens < t["max_tokens"]:
-        if device.type == "cuda":
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-        else:
-            t0 = time.perf_counter()
+        if in_window == 0:
+            if device.type == "cuda":
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+            else:
+                t0 = time.perf_counter()
         loss_t = engine.train_step()
+        in_window += 1
+        step = engine.trained_steps
+        watchdog.beat(step)
+        last = step >= t["total_train_steps"] or (t["max_tokens"] is not None
+                                                  and engine.trained_tokens >= t["max_tokens"])
+        if not (step % log_every == 0 or last or step % cfg["checkpoint"]["save_frequency"] == 0):
+            if prof is not None:
+                prof.step()
+            continue
         if device.type == "cuda":
             end.record()
             end.synchronize()
@@ -103,14 +119,13 @@ def main():
             # behind is trained on or written to a checkpoint (the device is already idle, so this
             # costs one small read)
             raise_if_failed(f"train step {engine.trained_steps}")
-            step_ms = torch.tensor([start.elapsed_time(end)], device=device)
+            step_ms = torch.tensor([start.elapsed_time(end) / in_window], device=device)
         else:
-            step_ms = torch.tensor([(time.perf_counter() - t0) * 1e3])
+            step_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / in_window])
+        in_window = 0
         dist.all_reduce(step_ms, op=dist.ReduceOp.MAX)
         loss = engine.average_loss(loss_t)
         sections = engine.timer.collect() if engine.timer is not None else None
-        step = engine.trained_steps
-        watchdog.beat(step)
         step_s = float(step_ms.item()) / 1e3
         tok_s = engine.tokens_per_step / step_s
         tok_s_gpu = tok_s / world
