@@ -53,7 +53,7 @@ def create_single_config(args) -> str:
     cfg["dataset"]["subset_name"] = args.subset_name
     if args.dataset is not None:
         cfg["dataset"]["name"] = args.dataset
-    cfg["logging"].update(use_wandb=args.use_wandb, run_name=args.exp_name)
+    cfg["logging"].update(use_wandb=args.use_wandb, run_name=args.exp_name, log_frequency=args.log_frequency)
     cfg["environment"]["HF_TOKEN"] = args.hf_token
     if args.use_cpu:
         cfg["environment"]["FLASH_ATTEN"] = "0"
@@ -99,6 +99,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dataset", type=str, default=None, help="dataset name; 'synthetic' = seeded uniform tokens")
     p.add_argument("--exp_name", type=str, default="dummy_exp")
     p.add_argument("--use_wandb", action="store_true")
+    p.add_argument("--log_frequency", type=int, default=1,
+                   help="synchronise with the device and print only every N-th step")
     p.add_argument("--use_cpu", action="store_true")
     p.add_argument("--use_fused_adam", action="store_true")
     p.add_argument("--hf_token", type=str, default=None)
