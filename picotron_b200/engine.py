@@ -521,7 +521,11 @@ class TrainEngine:
         if ok and getattr(mc, "num_experts", 1) > 1:
             ok = self._moe_graph_safe()
         if ok and m.cp_world_size > 1:
-            ok = self.fused_cp is not None
+            # ring attention on zigzag shards runs the step-by-step NCCL ring: no collective library
+            # call is ever captured
+            d = self.cfg["distributed"]
+            zigzag = bool(d.get("cp_zigzag", False)) and d["cp_attention"] == "ring"
+            ok = self.fused_cp is not None and not zigzag
         if ok and m.tp_world_size > 1:
             ok = self.fused_tp is not None
         if not ok:
