@@ -21,6 +21,13 @@ Two measurements per run, both as max over ranks:
 
 The working set of a step (3.4 GB of parameters, several GB of activations) is far larger
 than the 126 MB L2, so no explicit flush runs between iterations. Rank 0 prints one JSON line.
+
+On 2 GPUs and more the same process then measures the mixture-of-experts configuration with EP = N (same
+arm, 3 steps after 3 warm-up steps) and reports it under ``"secondary"`` of that line. The headline
+cannot lose by it: the line exists before the secondary measurement starts, an exception there only
+records ``{"unavailable": ...}``, and a deadline thread prints the line and ends every rank with exit code 0
+should the secondary part hang (``PICO_BENCH_SECONDARY=0`` skips it, ``PICO_BENCH_SECONDARY_TIMEOUT`` sets the
+deadline in seconds).
 """
 from __future__ import annotations
 
@@ -30,6 +37,7 @@ import os
 import subprocess
 import sys
 import tempfile
+import threading
 from types import SimpleNamespace
 
 import torch
@@ -188,6 +196,63 @@ def result_line(args, layout, world, ms_total, e2e_ms_total, h2d, d2h, clocks, l
     return line
 
 
+class Deadline:
+    """Ends the process with exit code 0 when ``seconds`` have passed, after printing ``line`` (rank 0 holds
+    one, the other ranks hold None) unless it was printed already. Guards the part of a run that comes
+    after the headline measurement."""
+
+    def __init__(self, seconds: float, line):
+        self.line = line
+        self.lock = threading.Lock()
+        self.printed = False
+        self.timer = threading.Timer(seconds, self._fire)
+        self.timer.daemon = True
+
+    def start(self):
+        self.timer.start()
+        return self
+
+    def print_line(self, line) -> None:
+        """Print the result line once (whichever of the main thread and the deadline comes first)."""
+        with self.lock:
+            if not self.printed and line is not None:
+                print(json.dumps(line), flush=True)
+            self.printed = True
+
+    def _fire(self):
+        self.print_line(self.line)
+        sys.stdout.flush()
+        os._exit(0)
+
+    def cancel(self):
+        self.timer.cancel()
+
+
+def finish_with_secondary(args, line, rank, world, device, reference: bool, teardown) -> None:
+    """Print the headline ``line`` (rank 0; None elsewhere), adding the mixture-of-experts measurement with
+    EP = world under ``"secondary"`` when the run has 2 GPUs or more, then run ``teardown``. Everything after
+    the headline measurement happens under a deadline."""
+    wanted = world >= 2 and os.environ.get("PICO_BENCH_SECONDARY", "1") != "0"
+    timeout = float(os.environ.get("PICO_BENCH_SECONDARY_TIMEOUT", "240"))
+    fallback = dict(line, secondary={"unavailable": f"not finished within {timeout:.0f} s"}) if line is not None and wanted \
+        else line
+    deadline = Deadline(timeout, fallback).start()
+    try:
+        if wanted:
+            try:
+                sub = SimpleNamespace(gpus=world, steps=min(args.steps, 3), warmup=3, impl="reference" if reference else "ours",
+                                      config="moe", variant=None, layers=0, seq=0)
+                sec = measure_config(sub, reference)
+            except BaseException as exc:                         # noqa: BLE001  the headline must survive anything
+                sec = {"unavailable": f"{type(exc).__name__}: {str(exc).splitlines()[0][:300] if str(exc) else ''}"}
+            if line is not None:
+                line = dict(line, secondary=sec if sec is not None else {"unavailable": "no result on rank 0"})
+        deadline.print_line(line)
+        teardown()
+    finally:
+        deadline.cancel()
+
+
 # ------------------------------------------------------------------------------------------ ours
 def run_ours(args):
     rank, local_rank, world = setup_distributed(args.gpus)
@@ -230,19 +295,33 @@ def run_ours(args):
     ops.check_status("bench")
     h2d = GRAD_ACC * 2 * MBS * SEQ * 8      # input_ids + target_ids, int64, per rank
     d2h = 4                                  # the fp32 step loss
-    if rank == 0:
-        print(json.dumps(result_line(args, layout, world, ms, e2e_ms, h2d, d2h, clocks, launches, "picotron_b200",
-                                     {"final_loss": last.get("loss")})), flush=True)
+    line = result_line(args, layout, world, ms, e2e_ms, h2d, d2h, clocks, launches, "picotron_b200",
+                       {"final_loss": last.get("loss")}) if rank == 0 else None
     engine.close()
-    dist.destroy_process_group()
+    del engine, resident
+    torch.cuda.empty_cache()
+    finish_with_secondary(args, line, rank, world, device, False, dist.destroy_process_group)
 
 
 # ------------------------------------------------------------------------------------- reference
 def run_reference(args):
+    out = _reference_headline(args)
+    if out is None:
+        return
+    line, rank, world, device = out
+    import gc
+    gc.collect()                      # the headline model and optimizer are out of scope: release their memory
+    torch.cuda.empty_cache()
+    finish_with_secondary(args, line, rank, world, device, True, dist.destroy_process_group)
+
+
+def _reference_headline(args):
+    """The reference's arm of the headline configuration. Returns (result line on rank 0 else None, rank,
+    world, device), or None after printing why the reference is unavailable."""
     ref_root = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "picotron")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/picotron is not installed"}))
-        return
+        return None
     try:
         rank, local_rank, world = setup_distributed(args.gpus)
         device = torch.device("cuda", local_rank)
@@ -335,15 +414,15 @@ def run_reference(args):
         e2e_ms = timed(e2e_step, args.steps, device)
         h2d = GRAD_ACC * 2 * MBS * SEQ * 8
         d2h = GRAD_ACC * 4
-        if rank == 0:
-            print(json.dumps(result_line(args, layout, world, ms, e2e_ms, h2d, d2h, clocks, 0, "reference",
-                                         {"final_loss": last.get("loss")})), flush=True)
-        dist.destroy_process_group()
+        line = result_line(args, layout, world, ms, e2e_ms, h2d, d2h, clocks, 0, "reference",
+                           {"final_loss": last.get("loss")}) if rank == 0 else None
+        return line, rank, world, device
     except Exception as exc:  # the reference could not run on this stack: say why, exit 0
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"impl": "reference",
                               "unavailable": f"{type(exc).__name__}: {str(exc).splitlines()[0][:300] if str(exc) else ''}"}),
                   flush=True)
+        return None
 
 
 # ------------------------------------------------------------ the other configurations, both arms
@@ -394,53 +473,61 @@ def build_ours_arm(spec, device):
                 parallelism=spec["label"], close=engine.close)
 
 
-def run_config(args):
+def measure_config(args, reference: bool):
+    """One of the non-headline configurations on the running process group: returns the result line on
+    rank 0 (None elsewhere). Raises what the arm raises."""
     from benchmarks.config_specs import make_spec
-    reference = args.impl == "reference"
     ref_root = os.path.join(REPO, "baseline", "_ref")
-    if reference and not os.path.isdir(os.path.join(ref_root, "picotron")):
+    rank, local_rank, world = setup_distributed(args.gpus)
+    device = torch.device("cuda", local_rank)
+    spec = make_spec(args.config, world, args.variant, args.layers, args.seq)
+    if reference:
+        import_reference(ref_root)
+        from baseline import reference_arms
+        arm = {"moe": reference_arms.build_moe, "cp": reference_arms.build_cp,
+               "pp": reference_arms.build_pp}[args.config](spec, device, world)
+    else:
+        arm = build_ours_arm(spec, device)
+    ops = None
+    if not reference:
+        from picotron_b200 import ops
+    for _ in range(args.warmup):
+        arm["device_step"]()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    l0 = 0 if reference else ops.launches()
+    ms = timed(arm["device_step"], args.steps, device)
+    launches = 0 if reference else ops.launches() - l0
+    clocks = sampler.stop() if sampler else {}
+    last = {}
+
+    def e2e():
+        last["loss"] = arm["e2e_step"]()
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e()
+    e2e_ms = timed(e2e, args.steps, device)
+    if not reference:
+        ops.check_status("bench")
+    # under pipeline parallelism only the last stage knows the loss: report the largest value seen
+    lt = torch.tensor([float(last.get("loss") or 0.0)], device=device)
+    dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+    last["loss"] = float(lt.item())
+    line = config_line(args, spec, world, ms, e2e_ms, arm, clocks, launches,
+                       "reference" if reference else "picotron_b200", last.get("loss")) if rank == 0 else None
+    if "close" in arm:
+        arm["close"]()
+    return line
+
+
+def run_config(args):
+    reference = args.impl == "reference"
+    if reference and not os.path.isdir(os.path.join(REPO, "baseline", "_ref", "picotron")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/picotron is not installed"}))
         return
     try:
-        rank, local_rank, world = setup_distributed(args.gpus)
-        device = torch.device("cuda", local_rank)
-        spec = make_spec(args.config, world, args.variant, args.layers, args.seq)
-        if reference:
-            import_reference(ref_root)
-            from baseline import reference_arms
-            arm = {"moe": reference_arms.build_moe, "cp": reference_arms.build_cp,
-                   "pp": reference_arms.build_pp}[args.config](spec, device, world)
-        else:
-            arm = build_ours_arm(spec, device)
-        ops = None
-        if not reference:
-            from picotron_b200 import ops
-        for _ in range(args.warmup):
-            arm["device_step"]()
-        sampler = ClockSampler(local_rank) if rank == 0 else None
-        l0 = 0 if reference else ops.launches()
-        ms = timed(arm["device_step"], args.steps, device)
-        launches = 0 if reference else ops.launches() - l0
-        clocks = sampler.stop() if sampler else {}
-        last = {}
-
-        def e2e():
-            last["loss"] = arm["e2e_step"]()
-
-        for _ in range(max(1, args.warmup // 2)):
-            e2e()
-        e2e_ms = timed(e2e, args.steps, device)
-        if not reference:
-            ops.check_status("bench")
-        # under pipeline parallelism only the last stage knows the loss: report the largest value seen
-        lt = torch.tensor([float(last.get("loss") or 0.0)], device=device)
-        dist.all_reduce(lt, op=dist.ReduceOp.MAX)
-        last["loss"] = float(lt.item())
-        if rank == 0:
-            print(json.dumps(config_line(args, spec, world, ms, e2e_ms, arm, clocks, launches,
-                                         "reference" if reference else "picotron_b200", last.get("loss"))), flush=True)
-        if "close" in arm:
-            arm["close"]()
+        line = measure_config(args, reference)
+        if line is not None:
+            print(json.dumps(line), flush=True)
         dist.destroy_process_group()
     except Exception as exc:
         if not reference:
