@@ -1,4 +1,4 @@
-"""A host-side model of the peer-memory protocol of the fused tensor-parallel path.
+"""A host-side model of the peer-memory protocol of the fused tensor-parallel and expert-parallel paths.
 
 ``compute-sanitizer`` cannot be run on the GPUs this project is developed on, so the argument that the
 flag/epoch protocol is free of races is checked here instead, by brute force: the operations one
@@ -21,7 +21,8 @@ The model follows ``ops/fused_tp.py`` and ``csrc/runtime/flags.cuh``:
   used once per micro-batch and read again by the backward pass; a group barrier opens every
   micro-batch when buffers are kept.
 
-``build_program`` writes down one rank's operation list for a number of layers and micro-batches,
+``build_program`` writes down one rank's operation list for a number of layers and micro-batches
+(``build_moe_program`` does the same for the exchanges of mixture-of-experts layers, ``ops/fused_ep.py``),
 ``simulate`` runs all ranks under a seeded random schedule and returns the list of violations.
 """
 from __future__ import annotations
@@ -118,6 +119,45 @@ def build_program(layers: int, micro_batches: int, keep_gathered: bool, barrier:
                 ops.append(Op("read_all", "main", xbuf, xslot, xe, ("x", mb, layer)))
                 slot_sum(where, ("dx", mb, layer))
     ops.append(Op("join"))
+    return ops
+
+
+def build_moe_program(layers: int, micro_batches: int, double_buffer: bool = True, load_sum: bool = True,
+                      tiles: int = 1) -> List[Op]:
+    """One rank's operations for mixture-of-experts layers on the capacity path of ``ops/fused_ep.py``:
+    per layer forward the expert-load rows (every rank stores its row into all peers' table, then adds the
+    rows), the dispatch into the expert-major slabs and the combine exchange into the source-major slabs;
+    backward the two exchanges in the opposite direction. Every exchange is "each rank writes block
+    ``rank`` of every peer's buffer, raises its flag, and the consumer reads all blocks after all flags",
+    i.e. the model's scatter / slot_sum pair on the buffers and flag slots of that file; the two copies
+    of each buffer alternate per kind of exchange. ``tiles`` > 1 issues the forward dispatches of that many
+    token tiles back to back before their combines (exchanges of one kind in a row, which is what the
+    second copy of a slab is for: with kinds strictly alternating, every exchange in between already
+    orders the reuse of a slab after its last read)."""
+    ops: List[Op] = []
+    epochs: Dict[int, int] = {}
+    counts = {"load": 0, "expert": 0, "source": 0}
+    slots = {"load": 24, "expert": 20, "source": 22}
+
+    def exchange(kind, tag):
+        b = counts[kind] % 2 if double_buffer else 0
+        counts[kind] += 1
+        slot = slots[kind] + b
+        epochs[slot] = epochs.get(slot, 0) + 1
+        ops.append(Op("scatter", "main", f"{kind}{b}", slot, epochs[slot], tag))
+        ops.append(Op("slot_sum", "main", f"{kind}{b}", slot, epochs[slot], tag))
+
+    for mb in range(micro_batches):
+        for layer in range(layers):                                 # forward
+            if load_sum:
+                exchange("load", ("load", mb, layer))
+            for t in range(tiles):
+                exchange("expert", ("dispatch", mb, layer, t))
+            for t in range(tiles):
+                exchange("source", ("combine", mb, layer, t))
+        for layer in reversed(range(layers)):                       # backward: combine's, then dispatch's
+            exchange("expert", ("d_combine", mb, layer))
+            exchange("source", ("d_dispatch", mb, layer))
     return ops
 
 

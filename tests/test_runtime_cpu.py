@@ -125,6 +125,24 @@ def test_protocol_model_detects_the_races_the_design_rules_out():
     assert not races(keep_gathered=True, barrier=True)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_protocol_model_finds_no_race_in_the_expert_exchanges(world):
+    """The exchanges of a mixture-of-experts layer (expert-load rows, dispatch, combine, and their backward
+    counterparts): no schedule reads a block before it arrived or after it was overwritten. Because the
+    kinds of exchange strictly alternate, that holds even on one copy per slab; the second copy is what
+    makes two exchanges of one kind in a row safe (two token tiles dispatched back to back), and the model
+    shows the race without it."""
+    from picotron_b200.runtime.protocol_model import build_moe_program, simulate
+    for prog in (build_moe_program(layers=3, micro_batches=3), build_moe_program(layers=2, micro_batches=2, load_sum=False),
+                 build_moe_program(layers=2, micro_batches=2, double_buffer=False)):
+        for seed in range(20):
+            assert simulate(world, prog, seed) == [], seed
+    tiled = dict(layers=2, micro_batches=2, tiles=2)
+    assert not any(simulate(world, build_moe_program(**tiled), seed) for seed in range(20))
+    assert any(simulate(world, build_moe_program(double_buffer=False, **tiled), seed) for seed in range(60)), \
+        "two dispatches in a row on a single copy of the slab must race"
+
+
 def test_flat_params_switch_follows_zero_stage():
     """``training.flat_params``: unset = flat buffers unless ZeRO stage 2/3 asks for sharded gradients and
     parameters (the per-parameter wrappers); an explicit value wins."""
