@@ -1,0 +1,39 @@
+"""The documentation names many files; every such name must exist. Names are the back-quoted tokens of the
+Markdown files that look like paths into this repository (the reference's own paths, ``picotron/...``, and
+wildcards are left alone). A short name such as ``ops/fused_tp.py`` may be given relative to the package, the
+kernel tree, the profiles or the file's own folder."""
+import glob
+import os
+import re
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DOCS = ["README.md", "DESIGN.md", "picotron_b200/parallel/README.md", "profiles/README.md"] + \
+    sorted(os.path.relpath(p, REPO) for p in glob.glob(os.path.join(REPO, "docs", "*.md")))
+EXTS = (".py", ".cu", ".cuh", ".h", ".cpp", ".md", ".txt", ".json", ".toml", ".slurm")
+ROOTS = ["", "picotron_b200", "picotron_b200/parallel", "picotron_b200/ops", "picotron_b200/runtime", "picotron_b200/models",
+         "csrc", "csrc/fused", "csrc/elementwise", "csrc/runtime", "csrc/common", "csrc/gemm", "csrc/attention", "profiles",
+         "benchmarks", "tests", "docs", "template", "baseline"]
+IGNORED = ("picotron/", "/root/", "runs/", "hf_model", "baseline/_ref")
+NOT_IN_TREE = {"MEASURED_PEAKS.json", "BASELINE.json", "SURVEY.md", "VERDICT.md", "ADVICE.md", "BASELINE.md", "config.json",
+               "manifest.json", "metrics.csv", "global_metrics.csv", "status.txt"}
+
+
+def _candidates(text):
+    for token in re.findall(r"`([^`\n]+)`", text):
+        token = token.split("::")[0].split(" ")[0].strip("(),.;:")
+        if not token.endswith(EXTS) or any(c in token for c in "*{}<>|$=") or token.startswith(IGNORED):
+            continue
+        if os.path.basename(token) in NOT_IN_TREE:
+            continue
+        yield token
+
+
+def test_every_file_named_in_the_documentation_exists():
+    missing = []
+    for doc in DOCS:
+        text = open(os.path.join(REPO, doc)).read()
+        here = os.path.dirname(doc)
+        for token in set(_candidates(text)):
+            if not any(os.path.exists(os.path.join(REPO, root, token)) for root in ROOTS + [here]):
+                missing.append(f"{doc}: {token}")
+    assert not missing, "\n".join(sorted(missing))
