@@ -19,21 +19,35 @@ NOT_IN_TREE = {"MEASURED_PEAKS.json", "BASELINE.json", "SURVEY.md", "VERDICT.md"
 
 
 def _candidates(text):
+    """(path, symbol or None) for every back-quoted ``path`` or ``path::symbol``."""
     for token in re.findall(r"`([^`\n]+)`", text):
-        token = token.split("::")[0].split(" ")[0].strip("(),.;:")
-        if not token.endswith(EXTS) or any(c in token for c in "*{}<>|$=") or token.startswith(IGNORED):
+        path, _, symbol = token.partition("::")
+        path = path.split(" ")[0].strip("(),.;:")
+        if not path.endswith(EXTS) or any(c in path for c in "*{}<>|$=") or path.startswith(IGNORED):
             continue
-        if os.path.basename(token) in NOT_IN_TREE:
+        if os.path.basename(path) in NOT_IN_TREE:
             continue
-        yield token
+        name = re.match(r"[A-Za-z_][A-Za-z0-9_]*", symbol)
+        yield path, (name.group(0) if name else None)
 
 
-def test_every_file_named_in_the_documentation_exists():
+def _resolve(path, here):
+    for root in ROOTS + [here]:
+        full = os.path.join(REPO, root, path)
+        if os.path.exists(full):
+            return full
+    return None
+
+
+def test_every_file_and_symbol_named_in_the_documentation_exists():
     missing = []
     for doc in DOCS:
         text = open(os.path.join(REPO, doc)).read()
         here = os.path.dirname(doc)
-        for token in set(_candidates(text)):
-            if not any(os.path.exists(os.path.join(REPO, root, token)) for root in ROOTS + [here]):
-                missing.append(f"{doc}: {token}")
+        for path, symbol in set(_candidates(text)):
+            full = _resolve(path, here)
+            if full is None:
+                missing.append(f"{doc}: {path}")
+            elif symbol and not re.search(r"\b" + re.escape(symbol) + r"\b", open(full, errors="replace").read()):
+                missing.append(f"{doc}: {path}::{symbol}")
     assert not missing, "\n".join(sorted(missing))
