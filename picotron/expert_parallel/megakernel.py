@@ -1,0 +1,5 @@
+"""Alias of ``picotron_b200.parallel.megakernel`` under the reference's import path."""
+import importlib
+import sys
+
+sys.modules[__name__] = importlib.import_module("picotron_b200.parallel.megakernel")

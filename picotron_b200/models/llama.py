@@ -56,6 +56,45 @@ class RMSNorm(nn.Module):
 LlamaRMSNorm = RMSNorm
 
 
+class TritonRMSNorm(RMSNorm):
+    """The reference's second norm class (picotron/model.py:61-93, a Triton layer-norm call): the same
+    module here, on this library's kernel. Its optional arguments are accepted; dropout and the
+    pre-norm return are not supported (the reference's model never uses them)."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-5, device=None, dtype=None):
+        super().__init__(hidden_size, eps)
+        if device is not None or dtype is not None:
+            self.to(device=device, dtype=dtype)
+
+    def forward(self, hidden_states, residual=None, dropout_p: float = 0.0, prenorm: bool = False,
+                residual_in_fp32: bool = False, return_dropout_mask: bool = False):
+        assert dropout_p == 0.0 and not prenorm and not return_dropout_mask, "only the plain RMSNorm call is supported"
+        if residual is None:
+            return super().forward(hidden_states)
+        return super().forward(hidden_states, residual)[0]
+
+
+def get_cos_sin(seq_length: int, head_dim: int, base: float = 500000.0):
+    """Rotary tables ``[seq_length, head_dim]`` (duplicated halves) on the device and in the dtype that
+    the ``DEVICE`` / ``DTYPE`` / ``LOCAL_RANK`` environment variables name, like picotron/model.py:39-51."""
+    import os
+    dtype = torch.bfloat16 if os.environ.get("DTYPE", "bfloat16") == "bfloat16" else torch.float32
+    on_gpu = os.environ.get("DEVICE", "cuda") == "cuda" and torch.cuda.is_available()
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if on_gpu else torch.device("cpu")
+    return rope_ops.get_cos_sin(seq_length, head_dim, base, device=device, dtype=dtype)
+
+
+def apply_rotary_pos_emb(x, cos, sin):
+    """x: ``[b, heads, s, d]``; cos / sin: ``[s, d]`` (picotron/model.py:29-36)."""
+    return x * cos + rope_ops.rotate_half(x) * sin
+
+
+def flash_attention(q, k, v, causal: bool = True):
+    """q, k, v: ``[b, heads, s, d]`` -> ``[b, s, heads, d]`` (the layout flash-attn returns,
+    picotron/model.py:54-58), on this library's attention kernels when the tensors allow."""
+    return attn_ops.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal)
+
+
 class Embedding(nn.Module):
     def __init__(self, num_embeddings: int, embedding_dim: int, init_std=None):
         super().__init__()

@@ -172,6 +172,59 @@ def ring_attention(q, k, v, sm_scale, is_causal, group=None):
     return out.transpose(1, 2)
 
 
+# ------------------------------------------------------------------------------------------
+# the reference's block-level names (picotron/context_parallel/context_parallel.py:37-323), all in its
+# [b, heads, s, d] layout
+# ------------------------------------------------------------------------------------------
+def ring_attention_forward(q, k, v, sm_scale, is_causal):
+    """Attention of the local queries against ONE key/value block: ``(out [b, heads, s, d], log-sum-exp
+    [b, heads, s])``; the causal mask, if any, is the diagonal block's."""
+    out, lse = attn_ops.attention_block(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal, sm_scale)
+    return out.transpose(1, 2), lse
+
+
+def ring_attention_backward(dout, q, k, v, out, softmax_lse, sm_scale, is_causal):
+    """Gradients ``(dq, dk, dv)`` of one block's contribution, given the merged output and log-sum-exp."""
+    dq, dk, dv = attn_ops.attention_block_backward(dout.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2),
+                                                   v.transpose(1, 2), out.transpose(1, 2), softmax_lse, is_causal,
+                                                   sm_scale)
+    return tuple(g.transpose(1, 2).to(q.dtype) for g in (dq, dk, dv))
+
+
+def update_out_and_lse(out, lse, block_out, block_lse, slice_=None):
+    """Exact merge of a new block's result into the running ``(out fp32 [b, heads, s, d], lse [b, heads, s,
+    1])``; the first call (``out is None``) returns the block itself. ``slice_`` restricts the update to
+    a part of the running tensors."""
+    block_out = block_out.float()
+    block_lse = block_lse.unsqueeze(-1)
+    if out is None:
+        if slice_ is not None:
+            raise RuntimeError("the first block cannot be merged into a slice")
+        return block_out, block_lse
+
+    def merged(cur_out, cur_lse):
+        new_lse = torch.logaddexp(cur_lse, block_lse)
+        return torch.exp(cur_lse - new_lse) * cur_out + torch.exp(block_lse - new_lse) * block_out, new_lse
+
+    if slice_ is None:
+        return merged(out, lse)
+    out[slice_], lse[slice_] = merged(out[slice_], lse[slice_])
+    return out, lse
+
+
+class RingAttentionFunc:
+    """``.apply(q, k, v, sm_scale, is_causal)`` like the reference's autograd function of this name."""
+
+    @staticmethod
+    def apply(q, k, v, sm_scale, is_causal):
+        return ring_attention(q, k, v, sm_scale, is_causal)
+
+
+#: the reference keeps a second function for its flash-attention blocks; here the blocks run on the
+#: flash kernels of this library whenever the tensors allow, so both names are the same entry point
+RingFlashAttentionFunc = RingAttentionFunc
+
+
 def update_rope_for_context_parallel(cos, sin, cp_rank=None, cp_world_size=None):
     """Slice full-sequence RoPE tables to this rank's positions (context_parallel.py:326-334)."""
     m = pgm.get_pgm()

@@ -45,6 +45,30 @@ def all_to_all(x, out_splits, in_splits, group):
     return _AllToAll.apply(x, out_splits, in_splits, group)
 
 
+class _AllToAllAsync(torch.autograd.Function):
+    """Variable-size all-to-all whose forward returns before the transfer has finished; the caller waits
+    on the work handle that is put into ``box``. The backward pass is the opposite exchange, blocking."""
+
+    @staticmethod
+    def forward(ctx, x, out_splits, in_splits, group, box):
+        ctx.group, ctx.out_splits, ctx.in_splits = group, list(out_splits), list(in_splits)
+        out, work = _a2a(x, out_splits, in_splits, group, async_op=True)
+        box.append(work)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a(g.contiguous(), ctx.in_splits, ctx.out_splits, ctx.group)[0], None, None, None, None
+
+
+def all_to_all_async(x, out_splits, in_splits, group):
+    """Differentiable all-to-all launched asynchronously: returns ``(output, work)``; ``work.wait()`` before
+    the output is used (picotron/expert_parallel/ep_communications.py:155-159)."""
+    box = []
+    out = _AllToAllAsync.apply(x, out_splits, in_splits, group, box)
+    return out, box[0]
+
+
 def all_to_all_no_grad(x, out_splits, in_splits, group):
     if group_size(group) == 1:
         return x

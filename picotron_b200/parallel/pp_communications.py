@@ -132,3 +132,47 @@ def bidirectional_pipeline_communicate(operation: str, send_tensor: torch.Tensor
         req.wait()
     _sync(device)
     return recv
+
+
+def _post_and_wait(ops, device) -> None:
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+        _sync(device)
+
+
+def interleaved_pipeline_communicate(device, dtype, shapes, send_forward_tensor=None, send_backward_tensor=None,
+                                     recv_forward=False, recv_backward=False):
+    """Blocking ring exchange of the interleaved schedule as one batched group (the reference's helper of
+    this name, pp_communications.py:53-94): activations go to the next rank of the pipeline ring, gradients
+    to the previous one; returns ``(received activation or None, received gradient or None)``. Every rank
+    posts its sends before its receives and forward before backward, so the two ends of a pair agree on
+    the order even when next and previous rank are the same process (two stages)."""
+    m = pgm.get_pgm()
+    ring = m.pp_group_ids
+    nxt, prv = ring[(m.pp_rank + 1) % len(ring)], ring[(m.pp_rank - 1) % len(ring)]
+    got = {"forward": None, "backward": None}
+    ops = [dist.P2POp(dist.isend, t, peer) for t, peer in ((send_forward_tensor, nxt), (send_backward_tensor, prv))
+           if t is not None]
+    for name, wanted, peer in (("forward", recv_forward, prv), ("backward", recv_backward, nxt)):
+        if wanted:
+            got[name] = torch.empty(shapes, requires_grad=True, device=device, dtype=dtype)
+            ops.append(dist.P2POp(dist.irecv, got[name], peer))
+    _post_and_wait(ops, device)
+    return got["forward"], got["backward"]
+
+
+def vshape_pipeline_communicate(device, dtype, shape, sends, recvs):
+    """Blocking exchange with arbitrary pipeline peers in one batched group (the reference's helper for
+    the V-shaped zero-bubble schedule, pp_communications.py:97-122). ``sends``: ``(key, tensor, peer
+    pipeline rank)``; ``recvs``: ``(key, peer pipeline rank)``; returns ``{key: received tensor}``. Both lists
+    are posted in (peer, key) order, which both ends of a pair derive identically."""
+    ring = pgm.get_pgm().pp_group_ids
+    ops = [dist.P2POp(dist.isend, t, ring[peer]) for _, t, peer in sorted(sends, key=lambda e: (e[2], e[0]))]
+    received = {}
+    for key, peer in sorted(recvs, key=lambda e: (e[1], e[0])):
+        received[key] = torch.empty(shape, requires_grad=True, device=device, dtype=dtype)
+        ops.append(dist.P2POp(dist.irecv, received[key], ring[peer]))
+    _post_and_wait(ops, device)
+    return received
+

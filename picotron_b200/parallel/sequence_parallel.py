@@ -115,3 +115,12 @@ def column_linear_sequence_parallel(x: torch.Tensor, mods, group=None) -> torch.
     outputs ``[b, s, sum(out_i)]``."""
     ws = gemm_ops.WeightSet.of(mods)
     return _ColumnLinearSP.apply(x, _tp_group(group), ws, *ws.params)
+
+
+def column_parallel_linear_sp(x: torch.Tensor, weight: torch.Tensor, bias=None, group=None) -> torch.Tensor:
+    """The reference's functional entry point (picotron/sequence_parallel/sequence_parallel.py:54-55):
+    one column-parallel projection of a sequence shard, ``gather(x) @ weight.T``. Bias is not supported
+    by any layer of the model (the reference's layers pass None as well)."""
+    assert bias is None, "bias is not supported"
+    ws = gemm_ops.WeightSet([weight])
+    return _ColumnLinearSP.apply(x, _tp_group(group), ws, weight)

@@ -17,6 +17,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from .. import process_group_manager as pgm
 from ..ops import gemm as gemm_ops
 from .dist_utils import group_rank, group_size
 from .sequence_parallel import all_gather_along_seq, reduce_scatter_along_seq
@@ -119,3 +120,31 @@ def ring_all_gather_linear(x, mods, group) -> torch.Tensor:
 
 def linear_pipelined_reduce_scatter(x, weight, group, addend=None):
     return _LinearPipelinedReduceScatter.apply(x, weight, group, addend)
+
+
+# ------------------------------------------------------------------------------------------
+# the reference's functional names (picotron/sequence_parallel/overlap.py:121-183)
+# ------------------------------------------------------------------------------------------
+def overlapped_column_parallel_linear_sp(x, weight, bias=None, group=None):
+    """Column-parallel projection of a sequence shard with the all-gather overlapped chunk by chunk."""
+    assert bias is None, "bias is not supported"
+    group = group if group is not None else pgm.get_pgm().tp_group
+    return _RingAllGatherLinear.apply(x, group, 1, weight)
+
+
+def overlapped_row_parallel_linear_sp(x, weight, addend=None, group=None):
+    """Row-parallel projection whose reduce-scatter is pipelined over sequence chunks; ``addend`` is a
+    second full-sequence partial sum folded into the same reduction (parallel transformer block)."""
+    group = group if group is not None else pgm.get_pgm().tp_group
+    return _LinearPipelinedReduceScatter.apply(x, weight, group, addend)
+
+
+class OverlappedColumnParallelLinearSP:
+    """``.apply(x_shard, weight, bias)`` like the reference's autograd function of this name."""
+    apply = staticmethod(overlapped_column_parallel_linear_sp)
+
+
+class OverlappedRowParallelLinearSP:
+    """``.apply(x_full, weight, addend)`` like the reference's autograd function of this name."""
+    apply = staticmethod(overlapped_row_parallel_linear_sp)
+

@@ -18,6 +18,18 @@ from ..ops import gemm as gemm_ops
 from .dist_utils import all_gather_cat, group_rank, group_size
 
 
+def merge_first_two_dims(grad_output: torch.Tensor, input_: torch.Tensor):
+    """Both tensors as 2-D ``[b*s, ...]`` views (tp_communications.py:8-10 of the reference)."""
+    return grad_output.contiguous().flatten(0, 1), input_.contiguous().flatten(0, 1)
+
+
+def split_tensor_along_last_dim(tensor: torch.Tensor, num_partitions: int):
+    """``num_partitions`` equal slices of the last dimension (tp_communications.py:13-20 of the reference)."""
+    width = tensor.shape[-1]
+    assert width % num_partitions == 0, f"{width} is not divisible by {num_partitions}"
+    return tensor.split(width // num_partitions, dim=-1)
+
+
 def _tp_group(group=None):
     return group if group is not None else pgm.get_pgm().tp_group
 
