@@ -96,8 +96,9 @@ def flash_attention(q, k, v, causal: bool = True):
 
 
 class Embedding(nn.Module):
-    def __init__(self, num_embeddings: int, embedding_dim: int, init_std=None):
+    def __init__(self, num_embeddings: int, embedding_dim: int, init_std=None, padding_idx=None):
         super().__init__()
+        assert padding_idx is None, "padding_idx is not supported"
         self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
         self.init_std = init_std
         self.weight = nn.Parameter(torch.empty(num_embeddings, embedding_dim))
@@ -113,6 +114,9 @@ class Embedding(nn.Module):
 
 class FinalProjection(Linear):
     """The lm head: hidden -> vocabulary logits."""
+
+    def __init__(self, hidden_size: int, vocab_size: int, init_std=None, bias: bool = False):
+        super().__init__(hidden_size, vocab_size, init_std, bias)
 
 
 def _local_attention(q, k, v, causal, sm_scale=None):

@@ -19,8 +19,8 @@ import torch.distributed as dist
 from . import ep_communications as epc
 
 
-def compute_capacity(num_tokens: int, top_k: int, num_experts: int, factor: float) -> int:
-    return max(1, int(factor * num_tokens * top_k / num_experts + 0.999))
+def compute_capacity(num_tokens: int, top_k: int, num_experts: int, capacity_factor: float) -> int:
+    return max(1, int(capacity_factor * num_tokens * top_k / num_experts + 0.999))
 
 
 def expert_counts(expert_idx: torch.Tensor, num_experts: int) -> torch.Tensor:

@@ -39,10 +39,10 @@ class _AllToAll(torch.autograd.Function):
         return _a2a(grad, ctx.in_splits, ctx.out_splits, ctx.group)[0], None, None, None
 
 
-def all_to_all(x, out_splits, in_splits, group):
+def all_to_all(x, output_split_sizes, input_split_sizes, group):
     if group_size(group) == 1:
         return x
-    return _AllToAll.apply(x, out_splits, in_splits, group)
+    return _AllToAll.apply(x, output_split_sizes, input_split_sizes, group)
 
 
 class _AllToAllAsync(torch.autograd.Function):
@@ -61,23 +61,23 @@ class _AllToAllAsync(torch.autograd.Function):
         return _a2a(g.contiguous(), ctx.in_splits, ctx.out_splits, ctx.group)[0], None, None, None, None
 
 
-def all_to_all_async(x, out_splits, in_splits, group):
+def all_to_all_async(x, output_split_sizes, input_split_sizes, group):
     """Differentiable all-to-all launched asynchronously: returns ``(output, work)``; ``work.wait()`` before
     the output is used (picotron/expert_parallel/ep_communications.py:155-159)."""
     box = []
-    out = _AllToAllAsync.apply(x, out_splits, in_splits, group, box)
+    out = _AllToAllAsync.apply(x, output_split_sizes, input_split_sizes, group, box)
     return out, box[0]
 
 
-def all_to_all_no_grad(x, out_splits, in_splits, group):
+def all_to_all_no_grad(x, output_split_sizes, input_split_sizes, group):
     if group_size(group) == 1:
         return x
-    return _a2a(x, out_splits, in_splits, group)[0]
+    return _a2a(x, output_split_sizes, input_split_sizes, group)[0]
 
 
-def all_to_all_no_grad_async(x, out_splits, in_splits, group):
+def all_to_all_no_grad_async(x, output_split_sizes, input_split_sizes, group):
     """Returns (output, work); the output is valid after ``work.wait()``."""
-    return _a2a(x, out_splits, in_splits, group, async_op=True)
+    return _a2a(x, output_split_sizes, input_split_sizes, group, async_op=True)
 
 
 class _AllToAllFP8(torch.autograd.Function):
@@ -94,11 +94,11 @@ class _AllToAllFP8(torch.autograd.Function):
         return _a2a(grad, ctx.in_splits, ctx.out_splits, ctx.group)[0], None, None, None, None
 
 
-def all_to_all_fp8(x, out_splits, in_splits, group, granularity: str = "block"):
+def all_to_all_fp8(x, output_split_sizes, input_split_sizes, group, granularity: str = "block"):
     """Dispatch with an FP8 payload; wire bytes per row: d + 4*ceil(d/128) (block) or d + 4 (row)."""
     if group_size(group) == 1:
         return x
-    return _AllToAllFP8.apply(x, out_splits, in_splits, group, granularity)
+    return _AllToAllFP8.apply(x, output_split_sizes, input_split_sizes, group, granularity)
 
 
 def exchange_counts(send_counts: torch.Tensor, group) -> torch.Tensor:
@@ -111,6 +111,6 @@ def exchange_counts(send_counts: torch.Tensor, group) -> torch.Tensor:
     return recv
 
 
-def exchange_split_sizes(input_splits: torch.Tensor, group) -> torch.Tensor:
+def exchange_split_sizes(input_split_sizes: torch.Tensor, group) -> torch.Tensor:
     """Per-rank row counts: what each peer will send me (ep_communications.py:170-178)."""
-    return exchange_counts(input_splits.view(-1, 1), group).view(-1)
+    return exchange_counts(input_split_sizes.view(-1, 1), group).view(-1)

@@ -70,3 +70,38 @@ def fused_moe_backward(x_sorted, counts, gate_w, up_w, down_w, dy):
         leaves = [t.detach().requires_grad_(True) for t in (x_sorted, gate_w, up_w, down_w)]
         y = fused_moe(leaves[0], counts, leaves[1], leaves[2], leaves[3], None)
         return torch.autograd.grad(y, leaves, dy)
+
+
+def fused_moe_dgrad(x_sorted, counts, gate_w, up_w, down_w, dy):
+    """Input gradient with the intermediates the weight gradients need: ``(dx, a, d_inter13)`` where
+    ``a = silu(gate(x)) * up(x)`` and ``d_inter13 = [d gate(x) | d up(x)]`` (megakernel.py:332-347)."""
+    dxs, acts, dinters, lo = [], [], [], 0
+    for e, n in enumerate(_counts_list(counts)):
+        seg, dseg = x_sorted[lo:lo + n], dy[lo:lo + n]
+        g, u = F.linear(seg, gate_w[e]), F.linear(seg, up_w[e])
+        sig = torch.sigmoid(g)
+        acts.append(g * sig * u)
+        da = dseg @ down_w[e]                                   # [n, I]
+        dg = da * u * sig * (1 + g * (1 - sig))                 # d silu(g) = sig * (1 + g * (1 - sig))
+        du = da * g * sig
+        dinters.append(torch.cat([dg, du], dim=-1))
+        dxs.append(dg @ gate_w[e] + du @ up_w[e])
+        lo += n
+    cat = lambda parts, width: torch.cat(parts) if parts else x_sorted.new_empty((0, width))    # noqa: E731
+    inter = gate_w.shape[1]
+    return cat(dxs, x_sorted.shape[1]), cat(acts, inter), cat(dinters, 2 * inter)
+
+
+def fused_moe_wgrad(x_sorted, counts, a, d_inter13, dy):
+    """Weight gradients ``(dgate_w, dup_w, ddown_w)`` from the intermediates of ``fused_moe_dgrad``
+    (megakernel.py:350-357)."""
+    inter = a.shape[1]
+    dg, du, dd, lo = [], [], [], 0
+    for n in _counts_list(counts):
+        seg = slice(lo, lo + n)
+        dd.append(dy[seg].T @ a[seg])                            # [H, I]
+        d13 = d_inter13[seg].T @ x_sorted[seg]                   # [2I, H]
+        dg.append(d13[:inter])
+        du.append(d13[inter:])
+        lo += n
+    return torch.stack(dg), torch.stack(du), torch.stack(dd)

@@ -23,9 +23,12 @@ from .dist_utils import group_rank, group_size
 from .sequence_parallel import all_gather_along_seq, reduce_scatter_along_seq
 
 
-def ring_all_gather_matmul(x_shard: torch.Tensor, weights, group) -> torch.Tensor:
+def ring_all_gather_matmul(x_shard: torch.Tensor, weight, group=None) -> torch.Tensor:
     """[b, s/tp, in] -> [b, s, sum(out)] with the ring transfer of shard i+1 overlapping the
-    matmul of shard i. ``weights``: list of [out_i, in]."""
+    matmul of shard i. ``weight``: one ``[out, in]`` tensor (the reference's call, overlap.py:40 there)
+    or a list of them sharing the input."""
+    weights = [weight] if torch.is_tensor(weight) else list(weight)
+    group = group if group is not None else pgm.get_pgm().tp_group
     n = group_size(group)
     rank = group_rank(group)
     b, s_loc, _ = x_shard.shape
@@ -54,9 +57,10 @@ def ring_all_gather_matmul(x_shard: torch.Tensor, weights, group) -> torch.Tenso
     return out
 
 
-def pipelined_matmul_reduce_scatter(x_full: torch.Tensor, weight: torch.Tensor, group, addend_full=None):
+def pipelined_matmul_reduce_scatter(x_full: torch.Tensor, weight: torch.Tensor, addend_full=None, group=None):
     """x_full [b, s, in/tp] @ weight.T summed over ranks, sequence-scattered: chunk i is reduced to
     rank i while chunk i+1 is being multiplied. Returns this rank's [b, s/tp, out]."""
+    group = group if group is not None else pgm.get_pgm().tp_group
     n = group_size(group)
     rank = group_rank(group)
     b, s, _ = x_full.shape
@@ -100,7 +104,7 @@ class _LinearPipelinedReduceScatter(torch.autograd.Function):
         ctx.group = group
         ctx.has_addend = addend is not None
         ctx.save_for_backward(x, weight)
-        return pipelined_matmul_reduce_scatter(x, weight, group, addend)
+        return pipelined_matmul_reduce_scatter(x, weight, addend, group)
 
     @staticmethod
     def backward(ctx, dy):

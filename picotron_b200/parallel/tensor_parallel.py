@@ -43,8 +43,9 @@ def _uniform_fan_in_(tensor: torch.Tensor, init_std=None) -> None:
 class Linear(nn.Module):
     """Bias-free linear on the GEMM kernel; the unsharded building block of the model."""
 
-    def __init__(self, in_features: int, out_features: int, init_std=None):
+    def __init__(self, in_features: int, out_features: int, init_std=None, bias: bool = False):
         super().__init__()
+        assert not bias, "bias is not supported"
         self.in_features, self.out_features = in_features, out_features
         self.init_std = init_std
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
@@ -66,7 +67,9 @@ class ColumnParallelLinear(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, bias: bool = False, gather_output: bool = False,
                  async_all_reduce: bool = False, sequence_parallel: bool = False, overlap_comm: bool = False,
-                 group=None, init_std=None):
+                 group=None, init_std=None, ptb: bool = False):
+        """``ptb`` (the reference's name, tensor_parallel.py:188-191 there): start in the no-collective mode of
+        the parallel transformer block, which ``DecoderLayer.configure_tensor_parallel`` otherwise sets."""
         super().__init__()
         assert not bias, "bias is not supported"
         self.init_std = init_std
@@ -80,7 +83,7 @@ class ColumnParallelLinear(nn.Module):
         self.async_all_reduce = async_all_reduce
         self.sequence_parallel = sequence_parallel
         self.overlap_comm = overlap_comm
-        self.raw = False  # parallel-block mode: caller owns the input collective
+        self.raw = bool(ptb)  # parallel-block mode: caller owns the input collective
         self.weight = nn.Parameter(torch.empty(self.output_size_per_partition, in_features))
         self.reset_parameters()
 
@@ -136,7 +139,7 @@ def multi_linear(mods: Sequence[nn.Module], x: torch.Tensor, cat: bool = False):
         else:
             y = sp.column_linear_sequence_parallel(x, mods, group)
     elif first.async_all_reduce:
-        y = torch.cat([tpc.linear_with_async_all_reduce(x, m.weight, group) for m in mods], dim=-1)
+        y = torch.cat([tpc.linear_with_async_all_reduce(x, m.weight, group=group) for m in mods], dim=-1)
     else:
         y = gemm_ops.multi_linear_cat(tpc.CopyToModelParallelRegion.apply(x, group), mods)
     if cat:
@@ -167,7 +170,8 @@ class RowParallelLinear(nn.Module):
     (all-reduce, or reduce-scatter along the sequence under sequence parallelism)."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = False, sequence_parallel: bool = False,
-                 overlap_comm: bool = False, group=None, init_std=None):
+                 overlap_comm: bool = False, group=None, init_std=None, ptb: bool = False):
+        """``ptb`` (the reference's name): start in the mode that returns the un-reduced partial sum."""
         super().__init__()
         assert not bias, "bias is not supported"
         self.init_std = init_std
@@ -179,7 +183,7 @@ class RowParallelLinear(nn.Module):
         self.input_size_per_partition = in_features // self.tp_world_size
         self.sequence_parallel = sequence_parallel
         self.overlap_comm = overlap_comm
-        self.raw = False  # parallel-block mode: return the un-reduced partial sum
+        self.raw = bool(ptb)  # parallel-block mode: return the un-reduced partial sum
         self.weight = nn.Parameter(torch.empty(out_features, self.input_size_per_partition))
         self.reset_parameters()
 
@@ -226,8 +230,13 @@ class VocabParallelEmbedding(nn.Module):
     partial lookups are summed (all-reduce, or reduce-scatter under sequence parallelism)."""
 
     def __init__(self, num_embeddings: int, embedding_dim: int, sequence_parallel: bool = False, group=None,
-                 init_std=None):
+                 init_std=None, padding_idx=None, max_norm=None, norm_type: float = 2.0,
+                 scale_grad_by_freq: bool = False, sparse: bool = False):
+        """The ``nn.Embedding`` options that the reference's signature lists (tensor_parallel.py:296-306 there)
+        are accepted by keyword at their defaults; none of them is implemented by either framework."""
         super().__init__()
+        assert padding_idx is None and max_norm is None and not scale_grad_by_freq and not sparse, \
+            "padding_idx / max_norm / scale_grad_by_freq / sparse are not supported"
         self.init_std = init_std
         self.group = group if group is not None else pgm.get_pgm().tp_group
         self.tp_world_size = group_size(self.group)

@@ -115,18 +115,21 @@ class LinearWithAsyncAllReduce(torch.autograd.Function):
         return dx, dw, None
 
 
-def linear_with_all_reduce(x, w, group=None):
-    """Plain tensor-parallel column linear: f(x) @ w.T."""
-    return gemm_ops.linear(CopyToModelParallelRegion.apply(x, group), w)
+def linear_with_all_reduce(x, weight, bias=None, group=None):
+    """Plain tensor-parallel column linear: f(x) @ weight.T (``bias`` must be None, as in every layer)."""
+    assert bias is None, "bias is not supported"
+    return gemm_ops.linear(CopyToModelParallelRegion.apply(x, group), weight)
 
 
-def linear_with_async_all_reduce(x, w, group=None):
-    return LinearWithAsyncAllReduce.apply(x, w, group)
+def linear_with_async_all_reduce(x, weight, bias=None, group=None):
+    assert bias is None, "bias is not supported"
+    return LinearWithAsyncAllReduce.apply(x, weight, group)
 
 
-def vocab_parallel_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, group=None) -> torch.Tensor:
+def vocab_parallel_cross_entropy(vocab_parallel_logits: torch.Tensor, target: torch.Tensor, group=None) -> torch.Tensor:
     """Per-token loss from vocabulary-sharded logits ``[..., V/tp]``; rank r owns columns
     ``[r*V/tp, (r+1)*V/tp)``. Callers take the mean. (tp_communications.py:137-192)"""
+    logits, targets = vocab_parallel_logits, target
     group = _tp_group(group)
     v_local = logits.shape[-1]
     start = group_rank(group) * v_local

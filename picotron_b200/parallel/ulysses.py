@@ -77,7 +77,10 @@ def ulysses_attention_bshd(q, k, v, causal: bool = True, sm_scale=None, group=No
     return _SeqAllToAll.apply(out, 1, 2, group)
 
 
-def ulysses_attention(q, k, v, is_causal, group=None):
-    """Reference-layout entry point on ``[b, heads, s_local, d]`` tensors."""
-    out = ulysses_attention_bshd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal, None, group)
+def ulysses_attention(q, k, v, causal=None, group=None, is_causal=None):
+    """Reference-layout entry point on ``[b, heads, s_local, d]`` tensors (``causal`` is the reference's
+    parameter name, ulysses.py:86 there; ``is_causal`` the name its ring counterpart uses)."""
+    causal = is_causal if causal is None else causal
+    assert causal is not None, "pass causal=True/False"
+    out = ulysses_attention_bshd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), bool(causal), None, group)
     return out.transpose(1, 2)

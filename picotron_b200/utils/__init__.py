@@ -71,16 +71,17 @@ def flops_per_token(num_params: float, num_layers: int, hidden_size: int, seq_le
     return 6.0 * num_params + 12.0 * num_layers * hidden_size * seq_len
 
 
-def get_mfu(tokens_per_second_per_gpu: float, num_params: float, model_config=None,
+def get_mfu(tokens_per_second: float, num_params: float, model_config=None,
             theoretical_flops: float = H100_BF16_PEAK_FLOPS, num_layers=None, hidden_size=None, seq_len=None) -> float:
-    """Model FLOPs utilisation in percent. Defaults to the reference's H100 constant; pass
-    ``theoretical_flops=measured_peak_flops()`` for the B200 figure."""
+    """Model FLOPs utilisation in percent of ONE GPU's peak: ``tokens_per_second`` is the per-GPU rate (the
+    parameter keeps the reference's name, utils.py:51 there; its trainer passes tokens/s/GPU). Defaults to the
+    reference's H100 constant; pass ``theoretical_flops=measured_peak_flops()`` for the B200 figure."""
     if model_config is not None:
         num_layers = model_config.num_hidden_layers
         hidden_size = model_config.hidden_size
         seq_len = model_config.max_position_embeddings
     fpt = flops_per_token(num_params, num_layers, hidden_size, seq_len)
-    return tokens_per_second_per_gpu * fpt / theoretical_flops * 100.0
+    return tokens_per_second * fpt / theoretical_flops * 100.0
 
 
 def get_num_params(model) -> int:

@@ -40,8 +40,9 @@ def test_every_public_name_of_the_reference_modules_resolves():
                                                        "update_out_and_lse", "update_rope_for_context_parallel"],
         "picotron.expert_parallel.ep_communications": ["all_to_all", "all_to_all_async", "all_to_all_no_grad_async",
                                                        "exchange_split_sizes"],
-        "picotron.expert_parallel.megakernel": ["fused_moe", "fused_moe_forward", "fused_moe_backward", "torch_fused_ffn",
-                                                "torch_moe_backward", "cuda_available"],
+        "picotron.expert_parallel.megakernel": ["fused_moe", "fused_moe_forward", "fused_moe_backward", "fused_moe_dgrad",
+                                                "fused_moe_wgrad", "torch_fused_ffn", "torch_moe_backward",
+                                                "cuda_available"],
         "picotron.expert_parallel.deepep_backend": ["deepep_available", "dispatch", "combine"],
     }
     for mod, wanted in names.items():
@@ -125,6 +126,9 @@ def test_grouped_expert_functions_match_an_expert_loop():
     got = mk.fused_moe_backward(x, counts, gw, uw, dw, dy)
     ref = mk.torch_moe_backward(x, counts, gw, uw, dw, dy)
     assert all(torch.allclose(a, b) for a, b in zip(got, ref)) and got[1][1].abs().max() == 0   # empty expert: zero grad
+    dx, act, d13 = mk.fused_moe_dgrad(x, counts, gw, uw, dw, dy)              # the explicit two-step backward
+    assert act.shape == (x.shape[0], I) and d13.shape == (x.shape[0], 2 * I)
+    assert all(torch.allclose(a, b) for a, b in zip((dx, *mk.fused_moe_wgrad(x, counts, act, d13, dy)), ref))
     assert deepep_backend.deepep_available() is False
     with pytest.raises(RuntimeError):
         deepep_backend.dispatch(None, x, None, None, E)
@@ -225,3 +229,57 @@ def _exchange_helpers_worker(rank, world):
 @pytest.mark.parametrize("world", [2, 3])
 def test_pipeline_exchange_helpers_and_async_all_to_all(world):
     run_distributed(_exchange_helpers_worker, world)
+
+
+def test_call_signatures_accept_the_reference_parameter_names():
+    """Parameter names of the reference's public entry points (read off its sources), so that calls by
+    keyword keep working. ``capacity_moe.capacity_moe`` is the one deliberate exception: here it takes the
+    layer instead of the reference's thirteen loose arguments."""
+    import importlib
+    import inspect
+    table = {
+        "picotron.model.FinalProjection": ["hidden_size", "vocab_size", "bias"],
+        "picotron.model.Embedding": ["num_embeddings", "embedding_dim", "padding_idx"],
+        "picotron.model.TritonRMSNorm": ["hidden_size", "eps", "device", "dtype"],
+        "picotron.utils.get_mfu": ["tokens_per_second", "num_params", "model_config", "theoretical_flops"],
+        "picotron.tensor_parallel.tensor_parallel.ColumnParallelLinear":
+            ["in_features", "out_features", "bias", "gather_output", "async_all_reduce", "sequence_parallel",
+             "overlap_comm", "ptb"],
+        "picotron.tensor_parallel.tensor_parallel.RowParallelLinear":
+            ["in_features", "out_features", "bias", "sequence_parallel", "overlap_comm", "ptb"],
+        "picotron.tensor_parallel.tensor_parallel.VocabParallelEmbedding":
+            ["num_embeddings", "embedding_dim", "padding_idx", "max_norm", "norm_type", "scale_grad_by_freq", "sparse",
+             "sequence_parallel"],
+        "picotron.tensor_parallel.tensor_parallel.apply_tensor_parallel":
+            ["model", "async_tp", "sequence_parallel", "vocab_parallel_ce", "overlap_comm"],
+        "picotron.context_parallel.ulysses.ulysses_attention": ["q", "k", "v", "causal"],
+        "picotron.context_parallel.context_parallel.ring_attention": ["q", "k", "v", "sm_scale", "is_causal"],
+        "picotron.context_parallel.context_parallel.update_out_and_lse": ["out", "lse", "block_out", "block_lse", "slice_"],
+        "picotron.expert_parallel.capacity_moe.compute_capacity": ["num_tokens", "top_k", "num_experts", "capacity_factor"],
+        "picotron.expert_parallel.ep_communications.all_to_all": ["x", "output_split_sizes", "input_split_sizes", "group"],
+        "picotron.expert_parallel.ep_communications.all_to_all_fp8": ["x", "output_split_sizes", "input_split_sizes", "group"],
+        "picotron.expert_parallel.ep_communications.all_to_all_no_grad_async":
+            ["x", "output_split_sizes", "input_split_sizes", "group"],
+        "picotron.expert_parallel.ep_communications.all_to_all_async":
+            ["x", "output_split_sizes", "input_split_sizes", "group"],
+        "picotron.sequence_parallel.sequence_parallel.column_parallel_linear_sp": ["x", "weight", "bias"],
+        "picotron.sequence_parallel.overlap.overlapped_row_parallel_linear_sp": ["x", "weight", "addend"],
+        "picotron.sequence_parallel.overlap.ring_all_gather_matmul": ["x_shard", "weight"],
+        "picotron.sequence_parallel.overlap.pipelined_matmul_reduce_scatter": ["x_full", "weight", "addend_full"],
+        "picotron.tensor_parallel.tp_communications.linear_with_all_reduce": ["x", "weight", "bias"],
+        "picotron.tensor_parallel.tp_communications.linear_with_async_all_reduce": ["x", "weight", "bias"],
+        "picotron.tensor_parallel.tp_communications.vocab_parallel_cross_entropy": ["vocab_parallel_logits", "target"],
+        "picotron.expert_parallel.ep_communications.exchange_split_sizes": ["input_split_sizes", "group"],
+        "picotron.pipeline_parallel.pp_communications.interleaved_pipeline_communicate":
+            ["device", "dtype", "shapes", "send_forward_tensor", "send_backward_tensor", "recv_forward", "recv_backward"],
+        "picotron.pipeline_parallel.pp_communications.vshape_pipeline_communicate":
+            ["device", "dtype", "shape", "sends", "recvs"],
+        "picotron.expert_parallel.megakernel.fused_moe":
+            ["x_sorted", "counts", "gate_w", "up_w", "down_w", "row_weight"],
+    }
+    wrong = []
+    for path, names in table.items():
+        mod, _, attr = path.rpartition(".")
+        params = inspect.signature(getattr(importlib.import_module(mod), attr)).parameters
+        wrong += [f"{path}: {n}" for n in names if n not in params]
+    assert not wrong, wrong
