@@ -92,6 +92,14 @@ class InitializationManager:
             tp_world_size = m.tp_world_size if m is not None else 1
         self.tp_rank, self.tp_world_size = tp_rank, tp_world_size
 
+    def add_missing_params_as_zeros(self, state_dict) -> None:
+        """Zero placeholders (fp32) for the model's parameters that ``state_dict`` lacks: what a dense
+        checkpoint cannot provide (experts, router, shared expert); ``reset_parameters`` initialises them
+        afterwards (picotron/checkpoint.py:132-141)."""
+        for name, param in self.model.named_parameters():
+            if name not in state_dict:
+                state_dict[name] = torch.zeros(param.shape, dtype=torch.float32)
+
     # ---------------------------------------------------------------------------------- names
     def hf_name(self, param_name: str) -> Optional[str]:
         """Checkpoint name of one of this model's parameters, or None when the dense checkpoint has

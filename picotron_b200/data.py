@@ -58,6 +58,7 @@ class MicroBatchDataLoader:
         self.cp_world_size = cp_world_size if cp_world_size is not None else m.cp_world_size
         self.cp_rank = cp_rank if cp_rank is not None else m.cp_rank
         self.micro_batch_size = micro_batch_size
+        self.tokenizer_name = tokenizer_name
         #: zigzag context parallelism: this rank's tokens are chunks r and 2*cp-1-r of the sequence
         self.cp_zigzag = bool(cp_zigzag) and self.cp_world_size > 1
         self.seq_length = seq_length
@@ -120,6 +121,33 @@ class MicroBatchDataLoader:
 
     def __next__(self):
         return self.collate(self.dataset.rows(self._next_indices()))
+
+    # -- the reference's method names (picotron/data.py:76-123) -------------------------------------
+    def collate_batch(self, batch):
+        """``batch``: a list of ``{"input_ids": seq+1 tokens}`` items, as a ``torch`` ``DataLoader`` hands
+        them to its ``collate_fn``."""
+        return self.collate(torch.stack([torch.as_tensor(item["input_ids"]) for item in batch]))
+
+    @staticmethod
+    def tokenizer_group_text(examples, tokenizer, sequence_length: int):
+        """Tokenise a list of texts, concatenate the tokens and cut them into rows of ``sequence_length + 1``
+        tokens that start every ``sequence_length`` tokens (neighbouring rows share one token: the last
+        target of a row is the first input of the next)."""
+        encoded = tokenizer.batch_encode_plus(examples, return_attention_mask=False, return_token_type_ids=False)
+        tokens = [t for doc in encoded["input_ids"] for t in doc]
+        rows = max(0, (len(tokens) - 1) // sequence_length)
+        return {"input_ids": [tokens[r * sequence_length:(r + 1) * sequence_length + 1] for r in range(rows)]}
+
+    def tokenize_dataset(self, dataset, text_column_name: str, sequence_length: int, num_proc: int):
+        """``dataset.map`` of ``tokenizer_group_text`` over the text column of a Hugging Face dataset."""
+        from functools import partial
+        tokenizer = getattr(self, "tokenizer", None)
+        if tokenizer is None:
+            from transformers import AutoTokenizer
+            tokenizer = self.tokenizer = AutoTokenizer.from_pretrained(self.tokenizer_name)
+        return dataset.map(partial(self.tokenizer_group_text, tokenizer=tokenizer, sequence_length=sequence_length),
+                           input_columns=text_column_name, remove_columns=dataset.column_names, batched=True,
+                           num_proc=num_proc, desc=f"Grouping texts in chunks of {sequence_length + 1}")
 
 
 class _HFPackedDataset:

@@ -104,6 +104,24 @@ class PipelineParallel(nn.Module):
     def backward(self, input_tensor, output_tensor, output_tensor_grad):
         return pp_autograd_backward(input_tensor, output_tensor, output_tensor_grad)
 
+    def distribute_layers(self, num_layers: int) -> List[int]:
+        """Layer indices of this rank's contiguous stage (the reference's method, pipeline_parallel.py:123-127)."""
+        m = pgm.get_pgm()
+        return distribute_layers(num_layers, m.pp_world_size)[m.pp_rank]
+
+    # Zero-bubble split for callers that drive a stage by hand (the executor does the same per action):
+    # B = input gradient now, weight-gradient GEMMs queued; W = run one micro-batch's queue. On the CPU
+    # restatement the forward pass must have run under ``ops.gemm.set_zero_bubble(True)`` for its linears
+    # to be deferrable; otherwise B computes everything and W finds an empty queue.
+    def backward_input(self, input_tensor, output_tensor, output_tensor_grad):
+        with gemm_ops.defer_wgrad() as queue:
+            grad_in = pp_autograd_backward(input_tensor, output_tensor, output_tensor_grad)
+        self.__dict__.setdefault("_zb_pending", []).append(list(queue))
+        return grad_in
+
+    def backward_weight(self, output_tensor=None, output_tensor_grad=None):
+        gemm_ops.run_deferred(self.__dict__["_zb_pending"].pop(0))
+
 
 class InterleavedPipelineParallel(PipelineParallel):
     def __init__(self, model, config, num_virtual_stages: int = 2, **kw):

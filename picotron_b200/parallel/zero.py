@@ -11,6 +11,7 @@ bit-identical to plain data parallelism, which is what the tests assert.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Dict, List
 
 import torch
@@ -56,6 +57,16 @@ class DataParallelZero(nn.Module):
 
     def backward(self, *args, **kwargs):
         return self.module.backward(*args, **kwargs)
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """No gradient reduction inside the block (micro-batches before the last one of a step)."""
+        prev = self.require_backward_grad_sync
+        self.require_backward_grad_sync = False
+        try:
+            yield
+        finally:
+            self.require_backward_grad_sync = prev
 
     def owns(self, p) -> bool:
         return self.owners[p] == self.rank

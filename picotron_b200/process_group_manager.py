@@ -19,6 +19,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
+import torch
 import torch.distributed as dist
 
 AXES = ("dp", "pp", "cp", "ep", "tp")
@@ -88,6 +89,8 @@ class ProcessGroupManager:
             f"world size ({self.world_size}) != tp({tp_size}) x cp({cp_size}) x ep({ep_size}) x "
             f"pp({pp_size}) x dp({dp_size})")
         self.topology = topo
+        #: ranks as a [dp, pp, cp, ep, tp] tensor, the reference's view of the grid (process_group_manager.py:24-26)
+        self.grid = torch.arange(self.world_size).view(dp_size, pp_size, cp_size, ep_size, tp_size)
         c = topo.coords(self.global_rank)
         self.dp_rank, self.pp_rank, self.cp_rank, self.ep_rank, self.tp_rank = (
             c["dp"], c["pp"], c["cp"], c["ep"], c["tp"])

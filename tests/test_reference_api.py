@@ -283,3 +283,90 @@ def test_call_signatures_accept_the_reference_parameter_names():
         params = inspect.signature(getattr(importlib.import_module(mod), attr)).parameters
         wrong += [f"{path}: {n}" for n in names if n not in params]
     assert not wrong, wrong
+
+
+def test_class_members_named_by_the_reference():
+    """Attributes and methods that reference scripts reach for on the grid manager, the pipeline stage
+    wrapper, the ZeRO wrapper, the loader and the checkpoint initialiser."""
+    from types import SimpleNamespace
+    from picotron.checkpoint import InitializationManager
+    from picotron.data import MicroBatchDataLoader
+    from picotron.data_parallel.zero import DataParallelZero
+    from picotron.pipeline_parallel.pipeline_parallel import PipelineParallel
+    from picotron.process_group_manager import ProcessGroupManager
+    m = ProcessGroupManager(1, 1, 1, 1, 1, create_groups=False)
+    assert tuple(m.grid.shape) == (1, 1, 1, 1, 1) and int(m.grid.flatten()[0]) == 0
+    for cls, names in ((PipelineParallel, ("distribute_layers", "backward", "backward_input", "backward_weight")),
+                       (DataParallelZero, ("no_sync", "full_parameters")),
+                       (MicroBatchDataLoader, ("collate_batch", "tokenizer_group_text", "tokenize_dataset")),
+                       (InitializationManager, ("add_missing_params_as_zeros", "get_layer_names_in_sft_format"))):
+        assert all(hasattr(cls, n) for n in names), (cls.__name__, names)
+
+    class Tok:                                     # 'a b c' -> [1, 2, 3]
+        def batch_encode_plus(self, texts, **kw):
+            return {"input_ids": [[ord(ch) - 96 for ch in t.split()] for t in texts]}
+
+    rows = MicroBatchDataLoader.tokenizer_group_text(["a b c d", "e f g"], Tok(), 3)["input_ids"]
+    assert rows == [[1, 2, 3, 4], [4, 5, 6, 7]]                     # rows of 3 + 1 tokens sharing their boundary token
+    assert MicroBatchDataLoader.tokenizer_group_text(["a b c"], Tok(), 3)["input_ids"] == []
+
+    class Data:
+        column_names = ["text"]
+
+        def map(self, fn, input_columns, remove_columns, batched, num_proc, desc):
+            assert input_columns == "text" and remove_columns == ["text"] and batched
+            return fn(["a b c d e f g"])
+
+    loader = MicroBatchDataLoader(micro_batch_size=2, seq_length=3, dataset_name="synthetic", vocab_size=32,
+                                  num_samples=8, pin_memory=False)
+    loader.tokenizer = Tok()
+    assert loader.tokenize_dataset(Data(), "text", 3, 1)["input_ids"] == [[1, 2, 3, 4], [4, 5, 6, 7]]
+    batch = loader.collate_batch([{"input_ids": [1, 2, 3, 4]}, {"input_ids": [4, 5, 6, 7]}])
+    assert batch["input_ids"].tolist() == [[1, 2, 3], [4, 5, 6]] and batch["target_ids"].tolist() == [[2, 3, 4], [5, 6, 7]]
+    assert batch["position_ids"].tolist() == [[0, 1, 2], [0, 1, 2]] and batch["hidden_states"] is None
+
+    model = torch.nn.Linear(3, 2)
+    sd = {"weight": torch.ones(2, 3)}
+    InitializationManager(model, SimpleNamespace(num_experts=1), tp_rank=0, tp_world_size=1).add_missing_params_as_zeros(sd)
+    assert set(sd) == {"weight", "bias"} and sd["bias"].abs().sum() == 0 and sd["weight"].sum() == 6
+
+
+def _pp_split_backward_worker(rank, world):
+    """``backward_input`` + ``backward_weight`` of a stage wrapper give what ``backward`` gives: the input
+    gradient at once, the weight gradients of the linears when the queue is drained."""
+    import types
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.ops import gemm as gemm_ops
+    from picotron.pipeline_parallel.pipeline_parallel import PipelineParallel
+    pgm.setup_process_group_manager(tp_size=1, cp_size=1, pp_size=world, dp_size=1)
+    cfg = types.SimpleNamespace(hidden_size=32, num_attention_heads=4, num_key_value_heads=2, intermediate_size=64,
+                                vocab_size=64, num_hidden_layers=2, max_position_embeddings=16, rms_norm_eps=1e-5,
+                                rope_theta=10000.0, parallel_block=False)
+    torch.manual_seed(0)
+    stage = PipelineParallel(Llama(cfg), cfg)
+    assert stage.distribute_layers(5) == [0, 1, 2, 3, 4]
+    ids = torch.randint(0, 64, (2, 8))
+    grads = {}
+    for split in (False, True):
+        stage.zero_grad()
+        gemm_ops.set_zero_bubble(split)
+        try:
+            out = stage(input_ids=ids)
+            go = torch.ones_like(out) / out.numel()
+            if split:
+                stage.backward_input(None, out, go)
+                lin = stage.decoder_layers["0"].mlp.down_proj.weight
+                assert lin.grad is None, "a linear's weight gradient must wait for the W pass"
+                stage.backward_weight()
+            else:
+                stage.backward(None, out, go)
+        finally:
+            gemm_ops.set_zero_bubble(False)
+        grads[split] = {n: p.grad.clone() for n, p in stage.named_parameters()}
+    for n in grads[False]:
+        assert torch.allclose(grads[True][n], grads[False][n], atol=1e-6), n
+
+
+def test_pipeline_stage_split_backward():
+    run_distributed(_pp_split_backward_worker, 1)
