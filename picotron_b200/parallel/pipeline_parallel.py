@@ -129,6 +129,19 @@ class InterleavedPipelineParallel(PipelineParallel):
         p = kw.get("pp_size") or m.pp_world_size
         super().__init__(model, config, stage_map=sched.StageMap(p, num_virtual_stages), **kw)
         self.num_virtual_stages = num_virtual_stages
+        self.num_global_stages = self.stage_map.num_stages
+        #: global stage of each local chunk (chunk c of rank r is stage c * p + r)
+        self.chunk_global_id = list(self.stages)
+
+    def is_first_stage(self, chunk_id: int) -> bool:
+        return self.stages[chunk_id] == 0
+
+    def is_last_stage(self, chunk_id: int) -> bool:
+        return self.stages[chunk_id] == self.stage_map.num_stages - 1
+
+    def forward(self, input_ids=None, position_ids=None, hidden_states=None, chunk_id: int = 0):
+        """One local chunk (the reference's call: ``forward(input_ids, position_ids, hidden_states, chunk_id)``)."""
+        return self.forward_chunk(chunk_id, input_ids=input_ids, hidden_states=hidden_states)
 
 
 class VShapePipelineParallel(PipelineParallel):
@@ -136,6 +149,24 @@ class VShapePipelineParallel(PipelineParallel):
         m = pgm.get_pgm()
         p = kw.get("pp_size") or m.pp_world_size
         super().__init__(model, config, stage_map=sched.StageMap(p, 2, vshape=True), **kw)
+        self.p = p
+        self.num_global_stages = self.stage_map.num_stages
+
+    def dev(self, g: int) -> int:
+        """Pipeline rank that hosts global stage ``g``: ``g`` on the way down, ``2p - 1 - g`` on the way up."""
+        return self.stage_map.rank_of(g)
+
+    def is_first(self, g: int) -> bool:
+        return g == 0
+
+    def is_last(self, g: int) -> bool:
+        return g == self.stage_map.num_stages - 1
+
+    def forward(self, gid=None, input_ids=None, position_ids=None, hidden_states=None):
+        """One of this rank's two stages by its global id (the reference's call: ``forward(gid, input_ids,
+        position_ids, hidden_states)``)."""
+        gid = self.stages[0] if gid is None else gid
+        return self.forward_chunk(self.stages.index(gid), input_ids=input_ids, hidden_states=hidden_states)
 
 
 def wrap_pipeline(model, config, engine: str, num_virtual_stages: int = 2):

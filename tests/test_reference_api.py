@@ -366,6 +366,18 @@ def _pp_split_backward_worker(rank, world):
         grads[split] = {n: p.grad.clone() for n, p in stage.named_parameters()}
     for n in grads[False]:
         assert torch.allclose(grads[True][n], grads[False][n], atol=1e-6), n
+    # the multi-chunk wrappers answer the reference's questions about their chunks
+    from picotron.pipeline_parallel.pp_schedules import InterleavedPipelineParallel, VShapePipelineParallel
+    cfg4 = types.SimpleNamespace(**{**vars(cfg), "num_hidden_layers": 4})
+    torch.manual_seed(0)
+    inter = InterleavedPipelineParallel(Llama(cfg4), cfg4, num_virtual_stages=2)
+    assert inter.chunk_global_id == [0, 1] and inter.num_global_stages == 2
+    assert inter.is_first_stage(0) and not inter.is_first_stage(1) and inter.is_last_stage(1)
+    hidden = inter(input_ids=ids, chunk_id=0)
+    assert hidden.shape == (2, 8, 32) and inter(hidden_states=hidden, chunk_id=1).shape == (2, 8, 64)
+    vee = VShapePipelineParallel(Llama(cfg4), cfg4)
+    assert vee.dev(0) == 0 and vee.dev(1) == 0 and vee.is_first(0) and vee.is_last(1) and not vee.is_last(0)
+    assert vee(1, hidden_states=vee(0, input_ids=ids)).shape == (2, 8, 64)
 
 
 def test_pipeline_stage_split_backward():
