@@ -236,7 +236,7 @@ def update_rope_for_context_parallel(cos, sin, cp_rank=None, cp_world_size=None)
     return cos[cp_rank * per:(cp_rank + 1) * per], sin[cp_rank * per:(cp_rank + 1) * per]
 
 
-def apply_context_parallel(model, attention: str = "ring", group=None, seq_length: int = None,
+def apply_context_parallel(model, attention: str = None, group=None, seq_length: int = None,
                            zigzag: bool = False):
     """Install ring or Ulysses attention on every layer and offset RoPE positions to this rank's
     slice of the sequence: rank r holds positions ``[r * s_local, (r + 1) * s_local)`` with
@@ -246,7 +246,15 @@ def apply_context_parallel(model, attention: str = "ring", group=None, seq_lengt
     attention only; the data loader must slice the same way, ``MicroBatchDataLoader(cp_zigzag=True)``)
     gives rank r chunks r and 2n-1-r of the sequence instead, so that causal attention costs every
     rank the same (with contiguous shards rank r computes r+1 blocks and the last rank paces the ring,
-    as the reference's README notes, context_parallel/README.md:146-148). Returns the model."""
+    as the reference's README notes, context_parallel/README.md:146-148). Returns the model.
+
+    ``attention`` = None takes the strategy from the ``CP_ATTENTION`` environment variable (the reference's
+    switch, read by its model in every forward pass; here it is read once, by this call), default ring.
+    The reference's one-argument call ``apply_context_parallel(model)`` therefore does the same job."""
+    if attention is None:
+        import os
+        attention = os.environ.get("CP_ATTENTION", "ring")
+    assert attention in ("ring", "ulysses"), f"unknown context-parallel attention {attention!r}"
     m = pgm.get_pgm()
     group = group if group is not None else m.cp_group
     n, rank = group_size(group), group_rank(group)
