@@ -228,16 +228,24 @@ class Deadline:
         self.timer.cancel()
 
 
-def finish_with_secondary(args, line, rank, world, device, reference: bool, teardown) -> None:
+def finish_with_secondary(args, line, rank, world, device, reference: bool, teardown, release=None) -> None:
     """Print the headline ``line`` (rank 0; None elsewhere), adding the mixture-of-experts measurement with
-    EP = world under ``"secondary"`` when the run has 2 GPUs or more, then run ``teardown``. Everything after
-    the headline measurement happens under a deadline."""
+    EP = world under ``"secondary"`` when the run has 2 GPUs or more, then run ``teardown``. ``release``
+    frees what the headline measurement held (it runs first; if it fails the secondary part is skipped).
+    Everything after the headline measurement happens under a deadline."""
     wanted = world >= 2 and os.environ.get("PICO_BENCH_SECONDARY", "1") != "0"
     timeout = float(os.environ.get("PICO_BENCH_SECONDARY_TIMEOUT", "240"))
     fallback = dict(line, secondary={"unavailable": f"not finished within {timeout:.0f} s"}) if line is not None and wanted \
         else line
     deadline = Deadline(timeout, fallback).start()
     try:
+        if release is not None:
+            try:
+                release()
+            except BaseException as exc:                         # noqa: BLE001
+                if line is not None and wanted:
+                    line = dict(line, secondary={"unavailable": f"release failed: {type(exc).__name__}: {exc}"[:300]})
+                wanted = False
         if wanted:
             try:
                 sub = SimpleNamespace(gpus=world, steps=min(args.steps, 3), warmup=3, impl="reference" if reference else "ours",
@@ -297,10 +305,15 @@ def run_ours(args):
     d2h = 4                                  # the fp32 step loss
     line = result_line(args, layout, world, ms, e2e_ms, h2d, d2h, clocks, launches, "picotron_b200",
                        {"final_loss": last.get("loss")}) if rank == 0 else None
-    engine.close()
+    held = [engine, resident]
     del engine, resident
-    torch.cuda.empty_cache()
-    finish_with_secondary(args, line, rank, world, device, False, dist.destroy_process_group)
+
+    def release():
+        held[0].close()
+        held.clear()
+        torch.cuda.empty_cache()
+
+    finish_with_secondary(args, line, rank, world, device, False, dist.destroy_process_group, release)
 
 
 # ------------------------------------------------------------------------------------- reference
@@ -309,10 +322,13 @@ def run_reference(args):
     if out is None:
         return
     line, rank, world, device = out
-    import gc
-    gc.collect()                      # the headline model and optimizer are out of scope: release their memory
-    torch.cuda.empty_cache()
-    finish_with_secondary(args, line, rank, world, device, True, dist.destroy_process_group)
+
+    def release():                    # the headline model and optimizer are out of scope: release their memory
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    finish_with_secondary(args, line, rank, world, device, True, dist.destroy_process_group, release)
 
 
 def _reference_headline(args):

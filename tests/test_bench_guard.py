@@ -69,3 +69,25 @@ def test_one_gpu_has_no_secondary_part():
     assert out.returncode == 0, out.stderr
     (line,) = _lines(out)
     assert line == {"metric": "m", "value": 1.0}
+
+
+def test_a_failing_or_hanging_release_keeps_the_headline():
+    for rel, timeout, needle in (("def bad():\n    raise RuntimeError('close failed')\n", "30", "release failed: RuntimeError: close failed"),
+                                 ("def bad():\n    time.sleep(60)\n", "1", "not finished")):
+        script = textwrap.dedent(f"""
+            import sys, time
+            sys.path.insert(0, {REPO!r})
+            import bench
+            from types import SimpleNamespace
+            args = SimpleNamespace(steps=5, warmup=3)
+            line = {{"metric": "m", "value": 1.0}}
+            def never(a, ref):
+                raise AssertionError("the secondary part must not run after a failed release")
+            bench.measure_config = never
+        """) + rel + "bench.finish_with_secondary(args, line, 0, 2, None, False, lambda: None, bad)\n"
+        out = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=120,
+                             env=dict(os.environ, PICO_BENCH_SECONDARY_TIMEOUT=timeout))
+        assert out.returncode == 0, out.stderr
+        (got,) = _lines(out)
+        assert got["value"] == 1.0 and needle in got["secondary"]["unavailable"], got
+
