@@ -346,13 +346,21 @@ class MoELayer(nn.Module):
         if self._device_routed_ok(tokens):
             return self._forward_device_routed(tokens).view(shape)
         topk_idx, topk_w = self._route(tokens)
+        return self._moe_given_routing(tokens, topk_idx, topk_w, self.ep_capacity_factor > 0).view(shape)
+
+    def _moe_given_routing(self, tokens, topk_idx, topk_w, capped: bool, force_plain: bool = False):
+        """``tokens`` [T, hidden] through the experts named by ``topk_idx`` [T, k] with weights ``topk_w``:
+        the capacity-limited exchange when ``capped``, otherwise the variable-size one (peer-memory layout,
+        tiled pipeline or plain all-to-all, whichever the layer is configured for; ``force_plain`` = the
+        plain one). Returns [T, hidden]."""
+        T = tokens.shape[0]
         shared = self._shared_start(tokens)
         latent = self.down_proj_latent(tokens) if self.latent else tokens
         token_idx = torch.arange(T, device=tokens.device).repeat_interleave(self.top_k, output_size=T * self.top_k)
         routed = latent[token_idx]                       # [T*k, d] token-major
         expert_idx = topk_idx.reshape(-1)
         weights = topk_w.reshape(-1)
-        if self.ep_capacity_factor > 0:
+        if capped:
             from .capacity_moe import capacity_moe, compute_capacity
             cap = compute_capacity(T, self.top_k, self.num_experts, self.ep_capacity_factor)
             y, dropped = capacity_moe(self, routed, expert_idx, weights, token_idx, T, cap,
@@ -360,16 +368,24 @@ class MoELayer(nn.Module):
             self.last_dropped_fraction = dropped
         else:
             epv = self.fused_ep_var
-            if epv is not None and routed.is_cuda and routed.dtype == torch.bfloat16 \
+            if not force_plain and epv is not None and routed.is_cuda and routed.dtype == torch.bfloat16 \
                     and routed.shape[0] == epv.rows_per_rank and self._grouped_ok(routed):
                 y_rows = self._routed_fused_var(routed, expert_idx)
-            elif self.ep_world_size > 1 and self.ep_num_tiles > 1:
+            elif not force_plain and self.ep_world_size > 1 and self.ep_num_tiles > 1:
                 from .tiled_moe import tiled_moe
                 y_rows = tiled_moe(self, routed, expert_idx, self.ep_num_tiles)
             else:
                 y_rows = self._routed_naive(routed, expert_idx)
             y = (y_rows * weights.unsqueeze(-1)).view(T, self.top_k, self.expert_dim).sum(dim=1)
-        return self._finalize(y, shared).view(shape)
+        return self._finalize(y, shared)
+
+    # the reference's per-path methods (expert_parallel.py:271-341 there), which its benchmark and ablation
+    # scripts call with a routing of their own
+    def _moe_naive(self, tokens, topk_idx, topk_weights):
+        return self._moe_given_routing(tokens, topk_idx, topk_weights, False, force_plain=True)
+
+    def _moe_capped(self, tokens, topk_idx, topk_weights):
+        return self._moe_given_routing(tokens, topk_idx, topk_weights, True)
 
 
 def collect_aux_loss(model):
