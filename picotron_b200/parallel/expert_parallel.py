@@ -342,7 +342,6 @@ class MoELayer(nn.Module):
     def forward(self, x):
         shape = x.shape
         tokens = x.reshape(-1, self.hidden_size)
-        T = tokens.shape[0]
         if self._device_routed_ok(tokens):
             return self._forward_device_routed(tokens).view(shape)
         topk_idx, topk_w = self._route(tokens)
