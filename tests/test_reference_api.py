@@ -382,3 +382,20 @@ def _pp_split_backward_worker(rank, world):
 
 def test_pipeline_stage_split_backward():
     run_distributed(_pp_split_backward_worker, 1)
+
+
+def test_the_reference_template_config_is_accepted():
+    """A config file written for the reference (its ``template/base_config.json``, where a copy of the
+    reference is at hand) validates here unchanged: this framework's schema is a superset."""
+    import json
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    root = os.environ.get("PICOTRON_REFERENCE_ROOT", os.path.join(os.path.dirname(repo), "reference"))
+    path = os.path.join(root, "template", "base_config.json")
+    if not os.path.exists(path):
+        pytest.skip("no copy of the reference on this machine")
+    from picotron_b200.config import load_config
+    theirs = json.load(open(path))
+    ours = load_config(theirs)
+    for section, keys in theirs.items():
+        assert section in ours and not set(keys) - set(ours[section]), section
+        assert all(ours[section][k] == v for k, v in keys.items() if v is not None), section
