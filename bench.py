@@ -256,7 +256,10 @@ def finish_with_secondary(args, line, rank, world, device, reference: bool, tear
             if line is not None:
                 line = dict(line, secondary=sec if sec is not None else {"unavailable": "no result on rank 0"})
         deadline.print_line(line)
-        teardown()
+        try:
+            teardown()
+        except Exception as exc:                                 # noqa: BLE001  the result is out: report, do not fail
+            print(f"tear-down failed: {type(exc).__name__}: {exc}", file=sys.stderr, flush=True)
     finally:
         deadline.cancel()
 
