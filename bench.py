@@ -248,8 +248,8 @@ def finish_with_secondary(args, line, rank, world, device, reference: bool, tear
                 wanted = False
         if wanted:
             try:
-                sub = SimpleNamespace(gpus=world, steps=min(args.steps, 3), warmup=3, impl="reference" if reference else "ours",
-                                      config="moe", variant=None, layers=0, seq=0)
+                sub = SimpleNamespace(gpus=world, steps=min(args.steps, 3), warmup=3, config="moe", variant=None,
+                                      layers=0, seq=0, impl="reference" if reference else "ours")
                 sec = measure_config(sub, reference)
             except BaseException as exc:                         # noqa: BLE001  the headline must survive anything
                 sec = {"unavailable": f"{type(exc).__name__}: {str(exc).splitlines()[0][:300] if str(exc) else ''}"}
