@@ -53,7 +53,7 @@ def run_gpu_ranks(fn, world):
     for p in procs:
         p.start()
     for p in procs:
-        p.join(180)
+        p.join(360)         # several engines per test (symmetric-memory set-up, graph capture) on up to 8 ranks
     msgs = []
     while not errors.empty():
         r, tb = errors.get()
